@@ -1,0 +1,125 @@
+/*
+ * C ABI of libtritonblas_b200.so: the B200 (sm_100a) GEMM hot path behind the tritonBLAS Python API.
+ *
+ * Conventions
+ *   - every entry point returns 0 on success or a positive TB_ERR_* code; tb_status_string() explains a code;
+ *   - pointers are raw device pointers, sizes and strides are in ELEMENTS unless a name ends in _bytes;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued, never synchronised, unless stated;
+ *   - the library neither allocates nor frees caller memory: outputs and workspaces are caller-owned;
+ *   - citations name the reference interface (path inside the tritonBLAS tree : line) an entry point stands in for.
+ */
+#ifndef TRITONBLAS_B200_H_
+#define TRITONBLAS_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+enum {
+  TB_DTYPE_F16 = 0,
+  TB_DTYPE_BF16 = 1,
+  TB_DTYPE_F32 = 2,
+  TB_DTYPE_E4M3 = 3,
+  TB_DTYPE_E5M2 = 4,
+  TB_DTYPE_U8 = 5, /* packed e2m1 pairs / e8m0 scale bytes */
+  TB_DTYPE_F4 = 6  /* selector only: 4-bit e2m1 operand */
+};
+
+/* host-side error codes; codes >= 100 are device-side wait time-outs reported through tb_device_status() */
+enum {
+  TB_OK = 0,
+  TB_ERR_INVALID = 1,     /* bad argument (shape, dtype, null pointer) */
+  TB_ERR_UNSUPPORTED = 2, /* valid request this build has no kernel for */
+  TB_ERR_ALIGNMENT = 3,   /* pointer or stride not usable by TMA and no fallback applies */
+  TB_ERR_WORKSPACE = 4,   /* workspace missing or too small */
+  TB_ERR_CUDA = 5,        /* a CUDA runtime / driver call failed; see tb_last_cuda_error() */
+  TB_ERR_NO_DEVICE = 6
+};
+
+/* GEMM problem as the selector sees it. Replaces the argument list of
+ * OrigamiMatmulSelector.__init__ (include/tritonblas/origami.py:98-112). */
+typedef struct tb_problem {
+  int32_t m, n, k;
+  int32_t a_dtype, b_dtype, c_dtype;
+  int32_t a_mn_major;    /* 1: A stored with M contiguous (reference "N" layout); 0: K contiguous */
+  int32_t b_mn_major;    /* 1: B stored with N contiguous; 0: K contiguous */
+  int32_t streamk;       /* 1: caller asked for stream-K scheduling */
+  int32_t mx_block_size; /* 0, or 32 for MXFP4 */
+  int32_t num_sms;       /* 0: all SMs of the device; else restrict the model and the grid to this many */
+  int32_t device;
+} tb_problem;
+
+/* Launch configuration chosen by the analytical model. Replaces the attribute surface of the selector
+ * (block_m/block_n/block_k/group_m/num_stages/sk_grid, include/tritonblas/origami.py:313-347) and the hybrid
+ * split computed in streamk_matmul_lt (include/tritonblas/matmul.py:225-254). */
+typedef struct tb_config {
+  int32_t block_m;   /* output tile rows (128 per CTA, 256 for a CTA pair) */
+  int32_t block_n;   /* output tile columns */
+  int32_t block_k;   /* K elements per shared-memory stage */
+  int32_t group_m;   /* tile-order swizzle: tiles_m grouped per column sweep */
+  int32_t stages;    /* shared-memory ring depth */
+  int32_t cta_pair;  /* 1: one CTA per tile; 2: two CTAs (one cluster) per tile */
+  int32_t grid;      /* programs (CTAs or CTA pairs) of the data-parallel launch */
+  int32_t sk_grid;   /* programs of the stream-K launch */
+  int32_t num_sms;   /* SMs of the device */
+  int32_t smem_bytes;
+  int32_t tmem_cols;
+  float predicted_us;     /* model estimate for the data-parallel schedule */
+  float predicted_sk_us;  /* model estimate for the stream-K schedule */
+} tb_config;
+
+/* One dense GEMM: C = cast( (A . B) [* a_scale[:,None]] [* b_scale[None,:]] [+ bias[None,:]] ).
+ * Replaces persistent_matmul_lt / streamk_matmul_lt and the Triton kernels they launch
+ * (include/tritonblas/matmul.py:69-366, kernels/persistent_gemm.py:26-126, kernels/streamk_gemm.py:7-384). */
+typedef struct tb_gemm_args {
+  int32_t m, n, k;
+  int32_t a_dtype, b_dtype, c_dtype;
+  const void* a; int64_t a_stride_m, a_stride_k;
+  const void* b; int64_t b_stride_k, b_stride_n;
+  void* c;       int64_t c_stride_m, c_stride_n;
+  const float* a_scale;  /* (m,) fp32 contiguous or NULL */
+  const float* b_scale;  /* (n,) fp32 contiguous or NULL */
+  const void* bias;      /* (n,) or NULL */
+  int64_t bias_stride; int32_t bias_dtype;
+  int32_t allow_tf32;    /* fp32 operands: 1 = tensor-core tf32 products, 0 = exact fp32 products */
+  int32_t streamk;       /* 0: data-parallel persistent; 1: hybrid stream-K */
+  int32_t sk_grid;       /* >0 overrides the configuration's stream-K grid */
+  void* workspace;       /* stream-K: partial tiles + flags; see tb_gemm_workspace_bytes() */
+  int64_t workspace_bytes;
+  uint32_t epoch;        /* stream-K: a value never used before on this workspace (start at 1, add 1 per launch;
+                            the workspace must be zero-filled once when it is created) */
+} tb_gemm_args;
+
+/* Fill `cfg` for `p`. Stands in for origami.select_config + OrigamiMatmulSelector._compute_sk_grid
+ * (include/tritonblas/origami.py:232-247,349-416); the model itself is derived for B200, not transcribed. */
+int tb_select(const tb_problem* p, tb_config* cfg);
+
+/* Bytes of stream-K workspace a launch with `cfg` (and optional grid override) needs.
+ * Stands in for the locks/P sizing of matmul_preamble (include/tritonblas/config.py:104-110). */
+int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override);
+
+/* Enqueue one GEMM. `cfg` may be NULL (the library selects). */
+int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);
+
+/* Reads (synchronously: waits for the device) and clears the per-device status word that kernels set when a bounded
+ * wait gives up. 0 = no failure since the last call. No reference counterpart (its waits are unbounded,
+ * kernels/streamk_gemm.py:295-300). */
+int tb_device_status(int32_t device, int32_t* status_out);
+
+/* Number of SMs, shared memory per block (opt-in) of a device. Stands in for origami.get_hardware_for_device
+ * (include/tritonblas/origami.py:166). */
+int tb_device_info(int32_t device, int32_t* num_sms, int32_t* smem_optin_bytes);
+
+const char* tb_status_string(int code);
+const char* tb_last_cuda_error(void);
+
+/* Number of kernels this library has launched in this process (bench bookkeeping). */
+int64_t tb_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRITONBLAS_B200_H_ */

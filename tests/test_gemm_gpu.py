@@ -1,0 +1,200 @@
+"""GPU parity of the dense GEMM family against the CPU oracle, through the public API (which calls the C ABI).
+
+Tolerance (stated by the task): rtol 1e-2 for fp16/bf16 outputs against the fp32-accumulate product; an absolute term of
+1e-2 * rms(reference) covers elements that cancel to near zero.
+"""
+import pytest
+import torch
+
+import tritonblas_b200 as tb
+from tests._util import assert_close_to_oracle, make_operands
+from tests.conftest import EDGE_CASE_DIMS, STANDARD_DIMS
+
+pytestmark = pytest.mark.gpu
+
+LAYOUTS = [("T", "T"), ("T", "N"), ("N", "T"), ("N", "N")]
+
+
+def _selector(m, n, k, dt, out_dt=None, streamk=False, **override):
+    s = tb.OrigamiMatmulSelector(m, n, k, dt, dt, out_dt or dt, torch.device("cuda", 0), streamk=streamk)
+    if override:
+        s.override(**override)
+    return s
+
+
+@pytest.fixture(autouse=True)
+def _no_device_failure():
+    yield
+    assert tb.device_status() == 0
+
+
+@pytest.mark.parametrize("pair", [1, 2])
+@pytest.mark.parametrize("ta,tb_", LAYOUTS)
+def test_fp16_1024_all_layouts(ta, tb_, pair):
+    """BASELINE config 1: fp16 1024^3, N(0,1) inputs, fp32 accumulate, fp16 out, every operand layout."""
+    a, b = make_operands(1024, 1024, 1024, torch.float16, ta, tb_)
+    c = torch.empty(1024, 1024, dtype=torch.float16, device="cuda")
+    sel = _selector(1024, 1024, 1024, torch.float16, cta_pair=pair, block_n=128)
+    tb.matmul_lt(a, b, c, sel, None)
+    assert_close_to_oracle(c, a, b, what=f"fp16 1024 {ta}{tb_} pair={pair}")
+
+
+@pytest.mark.parametrize("pair,bn", [(1, 32), (1, 64), (1, 128), (1, 256), (2, 64), (2, 128), (2, 256)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_tile_shapes(dt, pair, bn):
+    m, n, k = 640, 768, 512
+    a, b = make_operands(m, n, k, dt, "T", "T", seed=3)
+    c = torch.empty(m, n, dtype=dt, device="cuda")
+    tb.matmul_lt(a, b, c, _selector(m, n, k, dt, cta_pair=pair, block_n=bn), None)
+    assert_close_to_oracle(c, a, b, what=f"{dt} pair={pair} bn={bn}")
+
+
+@pytest.mark.parametrize("m,n,k", STANDARD_DIMS + EDGE_CASE_DIMS)
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_matmul_default_selector(m, n, k, dt):
+    """tritonblas.matmul with the library's own choice of configuration, row-major A and B (N-contiguous B)."""
+    a, b = make_operands(m, n, k, dt, "T", "N", seed=42)
+    c = tb.matmul(a, b)
+    assert c.dtype == dt and tuple(c.shape) == (m, n)
+    assert_close_to_oracle(c, a, b, what=f"{(m, n, k)} {dt}")
+
+
+@pytest.mark.parametrize("ta,tb_", LAYOUTS)
+@pytest.mark.parametrize("m,n,k", [(257, 129, 200), (15, 17, 512), (130, 260, 72), (4864 // 8, 8192 // 8, 4160 // 8)])
+def test_ragged_shapes_all_layouts(m, n, k, ta, tb_):
+    a, b = make_operands(m, n, k, torch.bfloat16, ta, tb_, seed=9)
+    c = tb.matmul(a, b)
+    assert_close_to_oracle(c, a, b, what=f"{(m, n, k)} {ta}{tb_}")
+
+
+@pytest.mark.parametrize("pair", [1, 2])
+def test_strided_output_and_out_argument(pair):
+    m, n, k = 300, 200, 256
+    a, b = make_operands(m, n, k, torch.bfloat16, "T", "T")
+    big = torch.zeros(m, n + 56, dtype=torch.bfloat16, device="cuda")
+    c = big[:, 8:8 + n]
+    tb.matmul_lt(a, b, c, _selector(m, n, k, torch.bfloat16, cta_pair=pair, block_n=64), None)
+    assert_close_to_oracle(c, a, b)
+    assert big[:, :8].abs().sum() == 0 and big[:, 8 + n:].abs().sum() == 0
+    ct = torch.empty(n, m, dtype=torch.bfloat16, device="cuda").T  # column-major output
+    assert tb.matmul(a, b, out=ct) is None
+    assert_close_to_oracle(ct, a, b)
+
+
+def test_fp32_output_from_bf16_inputs():
+    m, n, k = 256, 384, 320
+    a, b = make_operands(m, n, k, torch.bfloat16, "T", "T")
+    c = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    tb.matmul_lt(a, b, c, _selector(m, n, k, torch.bfloat16, torch.float32), None)
+    assert_close_to_oracle(c, a, b, rtol=1e-4)
+
+
+@pytest.mark.parametrize("ta,tb_", LAYOUTS)
+@pytest.mark.parametrize("allow_tf32", [True, False])
+def test_fp32_inputs(ta, tb_, allow_tf32):
+    """fp32 operands: tf32 tensor-core products when torch allows them (rtol 1e-2 like the 16-bit types; tf32 keeps 10
+    mantissa bits), exact fp32 multiply-add otherwise (rtol 1e-5)."""
+    m, n, k = 384, 320, 288
+    a, b = make_operands(m, n, k, torch.float32, ta, tb_)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = allow_tf32
+    try:
+        c = tb.matmul(a, b)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    assert_close_to_oracle(c, a, b, rtol=1e-2 if allow_tf32 else 1e-5, what=f"fp32 {ta}{tb_} tf32={allow_tf32}")
+
+
+def test_bf16_8192_cubed_sampled_rows():
+    """BASELINE config 2a at full size: bf16 8192^3 TN, values N(0,1)*0.02; the oracle checks 48 sampled rows, and
+    linearity (A@B with A doubled equals twice the product, exactly, since scaling by 2 is exact) covers the rest."""
+    m = n = k = 8192
+    a, b = make_operands(m, n, k, torch.bfloat16, "T", "T", seed=1, scale=0.02)
+    c = tb.matmul(a, b)
+    rows = torch.randint(0, m, (48,), generator=torch.Generator().manual_seed(5)).tolist() + [0, 127, 128, 255, 256, m - 1]
+    assert_close_to_oracle(c, a, b, rows=rows, what="bf16 8192^3")
+    c2 = tb.matmul(a * 2, b)
+    assert torch.equal(c2, c * 2)
+
+
+@pytest.mark.parametrize("pair", [1, 2])
+@pytest.mark.parametrize("m,n,k,sk_grid", [(256, 512, 2048, 0), (384, 640, 4096, 37), (128, 256, 8192, 148),
+                                           (1024, 1024, 1024, 50), (130, 100, 1000, 7), (16, 2048, 4096, 0)])
+def test_streamk_matches_oracle_and_is_deterministic(m, n, k, sk_grid, pair):
+    a, b = make_operands(m, n, k, torch.bfloat16, "T", "T", seed=11)
+    sel = _selector(m, n, k, torch.bfloat16, streamk=True, cta_pair=pair, block_n=128)
+    cfg = tb.matmul_preamble(sel)
+    outs = []
+    for _ in range(3):
+        c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        if sk_grid:
+            tb.streamk_matmul_lt(a, b, c, sel, cfg, sk_grid=sk_grid)
+        else:
+            tb.matmul_lt(a, b, c, sel, cfg, enable_streamk=True)
+        outs.append(c)
+    assert_close_to_oracle(outs[0], a, b, what=f"stream-K {(m, n, k)} grid={sk_grid} pair={pair}")
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])  # fix-up order is fixed
+
+
+@pytest.mark.parametrize("m", [1, 16, 128])
+def test_streamk_skinny_decode_shapes(m):
+    """BASELINE config 2b: M in {1,16,128}, N=28672, K=8192, stream-K enabled; sampled columns checked."""
+    n, k = 28672, 8192
+    a, b = make_operands(m, n, k, torch.bfloat16, "T", "T", seed=2, scale=0.02)
+    c = tb.matmul(a, b, enable_streamk=True)
+    cols = torch.randint(0, n, (512,), generator=torch.Generator().manual_seed(6))
+    cols = torch.cat([cols, torch.tensor([0, 127, 128, n - 1])]).to("cuda")
+    assert_close_to_oracle(c[:, cols], a, b[:, cols], what=f"skinny m={m}")
+
+
+def test_matmul_streamk_via_matmul_global_workspace():
+    a, b = make_operands(512, 768, 1024, torch.float16, "T", "N")
+    c1 = tb.matmul(a, b, enable_streamk=True, sk_grid=61)
+    c2 = tb.matmul(a, b, enable_streamk=True, sk_grid=61)
+    assert_close_to_oracle(c1, a, b)
+    assert torch.equal(c1, c2)
+
+
+@pytest.mark.parametrize("streamk", [False, True])
+def test_addmm_bias_broadcast_over_rows(streamk):
+    m, n, k = 200, 330, 512
+    a, b = make_operands(m, n, k, torch.bfloat16, "T", "N")
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda() * 4
+    c = tb.addmm(bias, a, b, enable_streamk=streamk)
+    assert_close_to_oracle(c, a, b, bias=bias, what="addmm")
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    assert tb.addmm(bias, a, b, out=out) is None
+    assert torch.equal(out, tb.addmm(bias, a, b))
+
+
+def test_errors_match_reference_behaviour():
+    a = torch.randn(8, 16, device="cuda", dtype=torch.float16)
+    b = torch.randn(32, 8, device="cuda", dtype=torch.float16)
+    with pytest.raises(AssertionError, match="Incompatible"):
+        tb.matmul(a, b)
+    a = torch.randn(8, 32, device="cuda", dtype=torch.float16, requires_grad=True)
+    out = torch.empty(8, 8, device="cuda", dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="don't support automatic differentiation"):
+        tb.matmul(a, b, out=out)
+    with pytest.raises(RuntimeError, match="don't support automatic differentiation"):
+        tb.addmm(torch.zeros(8, device="cuda", dtype=torch.float16), a, b, out=out)
+
+
+def test_backward_matches_torch_autograd_formulas():
+    m, n, k = 128, 192, 256
+    a, b = make_operands(m, n, k, torch.bfloat16, "T", "N", seed=4)
+    a.requires_grad_(True)
+    b.requires_grad_(True)
+    bias = torch.zeros(n, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    c = tb.addmm(bias, a, b)
+    g = torch.randn(m, n, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16).cuda()
+    c.backward(g)
+    assert_close_to_oracle(a.grad, g, b.detach().T, what="grad_a")
+    assert_close_to_oracle(b.grad, a.detach().T, g, what="grad_b")
+    assert torch.allclose(bias.grad.float().cpu(), g.float().sum(0).cpu(), rtol=1e-2, atol=1e-1)
+
+
+def test_torch_compile_fullgraph():
+    a, b = make_operands(256, 256, 256, torch.bfloat16, "T", "N")
+    fn = torch.compile(lambda x, y: tb.matmul(x, y), fullgraph=True)
+    assert_close_to_oracle(fn(a, b), a, b, what="compiled")

@@ -1,0 +1,111 @@
+"""ctypes binding of libtritonblas_b200.so (the C ABI declared in include/tritonblas_b200.h).
+
+There is no fallback: if the shared library has not been built, importing the package raises with the build command.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtritonblas_b200.so")
+
+# element type codes (TB_DTYPE_* in the header)
+F16, BF16, F32, E4M3, E5M2, U8, F4 = range(7)
+
+DTYPE_CODE = {
+    torch.float16: F16,
+    torch.bfloat16: BF16,
+    torch.float32: F32,
+    torch.float8_e4m3fn: E4M3,
+    torch.float8_e5m2: E5M2,
+    torch.uint8: U8,
+}
+
+
+class Problem(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "m", "n", "k", "a_dtype", "b_dtype", "c_dtype", "a_mn_major", "b_mn_major", "streamk", "mx_block_size",
+        "num_sms", "device")]
+
+
+class Config(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "block_m", "block_n", "block_k", "group_m", "stages", "cta_pair", "grid", "sk_grid", "num_sms", "smem_bytes",
+        "tmem_cols")] + [("predicted_us", ctypes.c_float), ("predicted_sk_us", ctypes.c_float)]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+class GemmArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32),
+        ("a_dtype", ctypes.c_int32), ("b_dtype", ctypes.c_int32), ("c_dtype", ctypes.c_int32),
+        ("a", ctypes.c_void_p), ("a_stride_m", ctypes.c_int64), ("a_stride_k", ctypes.c_int64),
+        ("b", ctypes.c_void_p), ("b_stride_k", ctypes.c_int64), ("b_stride_n", ctypes.c_int64),
+        ("c", ctypes.c_void_p), ("c_stride_m", ctypes.c_int64), ("c_stride_n", ctypes.c_int64),
+        ("a_scale", ctypes.c_void_p), ("b_scale", ctypes.c_void_p),
+        ("bias", ctypes.c_void_p), ("bias_stride", ctypes.c_int64), ("bias_dtype", ctypes.c_int32),
+        ("allow_tf32", ctypes.c_int32), ("streamk", ctypes.c_int32), ("sk_grid", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("epoch", ctypes.c_uint32),
+    ]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m tritonblas_b200.csrc.build` "
+            "(nvcc, sm_100a). tritonblas_b200 has no CPU or PyTorch fallback path.")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.tb_select.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(Config)]
+    lib.tb_select.restype = ctypes.c_int
+    lib.tb_gemm_workspace_bytes.argtypes = [ctypes.POINTER(Config), ctypes.c_int32]
+    lib.tb_gemm_workspace_bytes.restype = ctypes.c_int64
+    lib.tb_gemm.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p]
+    lib.tb_gemm.restype = ctypes.c_int
+    lib.tb_device_status.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)]
+    lib.tb_device_status.restype = ctypes.c_int
+    lib.tb_device_info.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
+    lib.tb_device_info.restype = ctypes.c_int
+    lib.tb_status_string.argtypes = [ctypes.c_int]
+    lib.tb_status_string.restype = ctypes.c_char_p
+    lib.tb_last_cuda_error.argtypes = []
+    lib.tb_last_cuda_error.restype = ctypes.c_char_p
+    lib.tb_launch_count.argtypes = []
+    lib.tb_launch_count.restype = ctypes.c_int64
+    return lib
+
+
+lib = _load()
+
+
+class TritonBlasError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+
+def check(rc, what="tritonblas_b200"):
+    if rc != 0:
+        msg = lib.tb_status_string(rc).decode()
+        if rc == 5:
+            msg += f" ({lib.tb_last_cuda_error().decode()})"
+        raise TritonBlasError(f"{what}: {msg} [code {rc}]")
+
+
+def device_status(device=None):
+    """Synchronise `device` and return (then clear) the failure code kernels record when a bounded wait gives up."""
+    if device is None:
+        device = torch.cuda.current_device()
+    out = ctypes.c_int32(0)
+    check(lib.tb_device_status(int(device), ctypes.byref(out)), "tb_device_status")
+    return out.value
+
+
+def raise_on_device_failure(device=None):
+    code = device_status(device)
+    if code != 0:
+        raise TritonBlasError(f"device-side failure: {lib.tb_status_string(code).decode()} [code {code}]")
+
+
+def current_stream_ptr(device=None):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)

@@ -1,0 +1,384 @@
+// C ABI of libtritonblas_b200.so: argument checking, tensor-map construction, kernel launches.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/tritonblas_b200.h"
+#include "common_host.h"
+#include "gemm_sm100.cuh"
+#include "selector.h"
+
+namespace tb {
+
+static thread_local char g_cuda_err[256] = "";
+std::atomic<long long> g_launches{0};
+
+int cuda_fail(cudaError_t e, const char* what) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+  return TB_ERR_CUDA;
+}
+int cu_fail(int code, const char* what) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: CUresult %d", what, code);
+  return TB_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------- per-device state
+struct DeviceState {
+  bool ready = false;
+  int num_sms = 0;
+  int smem_optin = 0;
+  int* status = nullptr;  // device word kernels write a failure code into
+};
+static DeviceState g_dev[64];
+static std::mutex g_mu;
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+int device_state(int device, DeviceState** out) {
+  if (device < 0 || device >= 64) return TB_ERR_INVALID;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[device];
+  if (!d.ready) {
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || device >= count) {
+      cudaGetLastError();
+      return TB_ERR_NO_DEVICE;
+    }
+    int cur = 0;
+    cudaGetDevice(&cur);
+    if ((e = cudaSetDevice(device)) != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, device);
+    cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    if ((e = cudaMalloc(&d.status, 256)) != cudaSuccess) return cuda_fail(e, "cudaMalloc(status)");
+    if ((e = cudaMemset(d.status, 0, 256)) != cudaSuccess) return cuda_fail(e, "cudaMemset(status)");
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+      if (e != cudaSuccess || fn == nullptr) return cuda_fail(e, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    }
+    cudaSetDevice(cur);
+    d.ready = true;
+  }
+  *out = &d;
+  return TB_OK;
+}
+
+int current_device_state(DeviceState** out, int* device) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return TB_ERR_NO_DEVICE;
+  }
+  if (device) *device = dev;
+  return device_state(dev, out);
+}
+
+int* device_status_word(int device) {
+  DeviceState* d = nullptr;
+  if (device_state(device, &d) != TB_OK) return nullptr;
+  return d->status;
+}
+
+static CUtensorMapDataType tmap_dtype(int dtype) {
+  switch (dtype) {
+    case TB_DTYPE_F16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    case TB_DTYPE_BF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    case TB_DTYPE_F32: return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    default: return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  }
+}
+
+// 2-D row-major view [outer][inner] with `outer_stride_bytes` between rows; box = box_inner x box_outer elements.
+int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer, uint64_t outer_stride_bytes,
+              uint32_t box_inner, uint32_t box_outer, bool swizzle128) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (outer_stride_bytes & 15) != 0) return TB_ERR_ALIGNMENT;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {outer_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, tmap_dtype(dtype), 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cu_fail(static_cast<int>(r), "cuTensorMapEncodeTiled");
+  return TB_OK;
+}
+
+static int esize_of(int dtype) {
+  switch (dtype) {
+    case TB_DTYPE_F16:
+    case TB_DTYPE_BF16: return 2;
+    case TB_DTYPE_F32: return 4;
+    case TB_DTYPE_E4M3:
+    case TB_DTYPE_E5M2:
+    case TB_DTYPE_U8: return 1;
+    default: return 0;
+  }
+}
+
+MachineModel machine_for(const DeviceState* d) {
+  MachineModel hw;
+  if (d != nullptr) {
+    hw.num_sms = d->num_sms;
+    hw.smem_optin = d->smem_optin;
+  }
+  const char* env = getenv("TB_DISABLE_CTA_PAIR");
+  if (env != nullptr && env[0] == '1') hw.allow_pair = false;
+  return hw;
+}
+
+template <int KIND, int CTAS>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const GemmParams& p, int programs, int smem_bytes,
+                       cudaStream_t stream) {
+  auto kernel = gemm_kernel<KIND, CTAS>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(static_cast<unsigned>(programs * CTAS), 1, 1);
+  lc.blockDim = dim3(kGemmThreads, 1, 1);
+  lc.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  e = cudaLaunchKernelEx(&lc, kernel, ta, tb_, p);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemm)");
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return TB_OK;
+}
+
+int gemm_fp32_exact(const tb_gemm_args& a, cudaStream_t stream);                 // simt_gemm.cu
+int gemm_generic_loader(const tb_gemm_args& a, const tb_config& cfg, cudaStream_t stream, int* status);  // unaligned operands
+
+static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStream_t stream) {
+  if (a.m < 0 || a.n < 0 || a.k < 0) return TB_ERR_INVALID;
+  if (a.m == 0 || a.n == 0) return TB_OK;
+  if (a.a == nullptr || a.b == nullptr || a.c == nullptr) return TB_ERR_INVALID;
+  if (a.a_dtype != a.b_dtype) return TB_ERR_UNSUPPORTED;
+  if (a.k == 0) return TB_ERR_UNSUPPORTED;
+  const int es = esize_of(a.a_dtype);
+  if (es == 0 || a.a_dtype == TB_DTYPE_U8) return TB_ERR_UNSUPPORTED;
+  if (a.c_dtype != TB_DTYPE_F16 && a.c_dtype != TB_DTYPE_BF16 && a.c_dtype != TB_DTYPE_F32 && a.c_dtype != TB_DTYPE_E4M3)
+    return TB_ERR_UNSUPPORTED;
+
+  DeviceState* dev = nullptr;
+  int device = 0;
+  int rc = current_device_state(&dev, &device);
+  if (rc != TB_OK) return rc;
+
+  if (a.a_dtype == TB_DTYPE_F32 && !a.allow_tf32) return gemm_fp32_exact(a, stream);
+
+  // operand majors from strides
+  int a_mn, b_mn;
+  if (a.a_stride_k == 1 || a.k == 1) a_mn = 0;
+  else if (a.a_stride_m == 1 || a.m == 1) a_mn = 1;
+  else return TB_ERR_UNSUPPORTED;
+  if (a.b_stride_k == 1 || a.k == 1) b_mn = 0;
+  else if (a.b_stride_n == 1 || a.n == 1) b_mn = 1;
+  else return TB_ERR_UNSUPPORTED;
+  if (a.a_stride_k == 1 && a.a_stride_m == 1 && a.m > 1 && a.k > 1) return TB_ERR_INVALID;
+
+  tb_config cfg;
+  if (user_cfg != nullptr) {
+    cfg = *user_cfg;
+  } else {
+    tb_problem pr = {};
+    pr.m = a.m; pr.n = a.n; pr.k = a.k;
+    pr.a_dtype = a.a_dtype; pr.b_dtype = a.b_dtype; pr.c_dtype = a.c_dtype;
+    pr.a_mn_major = a_mn; pr.b_mn_major = b_mn;
+    pr.streamk = a.streamk;
+    pr.device = device;
+    rc = select_config(pr, machine_for(dev), &cfg);
+    if (rc != TB_OK) return rc;
+  }
+  const int pair = cfg.cta_pair == 2 ? 2 : 1;
+  const int bn = cfg.block_n;
+  const int mn_atom = 128 / es;
+  if (bn < 32 || bn > 256 || (bn % 32) != 0 || cfg.block_m != 128 * pair) return TB_ERR_INVALID;
+  if ((bn / pair) % 16 != 0) return TB_ERR_INVALID;
+  if (b_mn && ((bn / pair) % mn_atom) != 0) return TB_ERR_INVALID;
+  const int bk = 128 / es;
+  int stages = cfg.stages;
+  if (stages < 2) stages = 2;
+  while (stages > 2 && smem_bytes_for(bn, pair, stages) > dev->smem_optin) --stages;
+  const int smem_bytes = smem_bytes_for(bn, pair, stages);
+  if (smem_bytes > dev->smem_optin) return TB_ERR_INVALID;
+
+  GemmParams p = {};
+  p.M = a.m; p.N = a.n; p.K = a.k;
+  p.block_n = bn;
+  p.k_per_stage = bk;
+  p.num_k_blocks = (a.k + bk - 1) / bk;
+  p.tiles_m = (a.m + 128 * pair - 1) / (128 * pair);
+  p.tiles_n = (a.n + bn - 1) / bn;
+  p.group_m = cfg.group_m > 0 ? cfg.group_m : 8;
+  p.stages = stages;
+  p.esize = es;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  int tc = 32;
+  while (tc < 2 * bn) tc <<= 1;
+  p.tmem_cols = static_cast<uint32_t>(tc);
+  p.C = a.c; p.ldc_m = a.c_stride_m; p.ldc_n = a.c_stride_n; p.c_dtype = a.c_dtype;
+  p.a_scale = a.a_scale; p.b_scale = a.b_scale;
+  p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
+  p.status = dev->status;
+  p.timeout_ns = 2000000000ull;
+
+  // instruction descriptor: fp32 accumulate; operand formats; majors; N >> 3; M >> 4
+  int kind;
+  uint32_t fmt;
+  switch (a.a_dtype) {
+    case TB_DTYPE_F16: kind = 0; fmt = 0; break;
+    case TB_DTYPE_BF16: kind = 0; fmt = 1; break;
+    case TB_DTYPE_F32: kind = 1; fmt = 2; break;
+    case TB_DTYPE_E4M3: kind = 2; fmt = 0; break;
+    case TB_DTYPE_E5M2: kind = 2; fmt = 1; break;
+    default: return TB_ERR_UNSUPPORTED;
+  }
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
+            (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>((128 * pair) >> 4) << 24);
+
+  // schedule
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const int max_programs = dev->num_sms / pair;
+  int programs;
+  if (a.streamk) {
+    programs = a.sk_grid > 0 ? a.sk_grid : cfg.sk_grid;
+    if (programs <= 0) programs = max_programs;
+    // All programs of a stream-K launch must be resident at once: owners wait for peers.
+    if (programs > max_programs) programs = max_programs;
+    const long long total_iters = tiles * p.num_k_blocks;
+    if (programs > total_iters) programs = static_cast<int>(total_iters);
+    p.sk_tiles = static_cast<int>(tiles % programs);
+    p.dp_tiles = static_cast<int>(tiles - p.sk_tiles);
+    if (p.sk_tiles > 0) {
+      const int64_t need = tb_gemm_workspace_bytes(&cfg, programs);
+      if (a.workspace == nullptr || a.workspace_bytes < need) return TB_ERR_WORKSPACE;
+      if (a.epoch == 0) return TB_ERR_INVALID;
+      p.flags = reinterpret_cast<unsigned*>(a.workspace);
+      p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(a.workspace) + 4096);
+      p.epoch = a.epoch;
+    }
+  } else {
+    programs = cfg.grid > 0 ? cfg.grid : max_programs;
+    if (programs > max_programs) programs = max_programs;
+    if (programs > tiles) programs = static_cast<int>(tiles);
+    p.dp_tiles = static_cast<int>(tiles);
+    p.sk_tiles = 0;
+  }
+  if (programs < 1) programs = 1;
+
+  // tensor maps
+  CUtensorMap ta, tbm;
+  const void* A = a.a;
+  const void* B = a.b;
+  if (!a_mn) rc = encode_2d(&ta, a.a_dtype, A, a.k, a.m, static_cast<uint64_t>(a.a_stride_m) * es, bk, 128, true);
+  else rc = encode_2d(&ta, a.a_dtype, A, a.m, a.k, static_cast<uint64_t>(a.a_stride_k) * es, mn_atom, bk, true);
+  if (rc == TB_OK) {
+    if (!b_mn) rc = encode_2d(&tbm, a.b_dtype, B, a.k, a.n, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, true);
+    else rc = encode_2d(&tbm, a.b_dtype, B, a.n, a.k, static_cast<uint64_t>(a.b_stride_k) * es, mn_atom, bk, true);
+  }
+  if (rc == TB_ERR_ALIGNMENT) return gemm_generic_loader(a, cfg, stream, dev->status);
+  if (rc != TB_OK) return rc;
+
+#define TB_LAUNCH(K, C) return launch_gemm<K, C>(ta, tbm, p, programs, smem_bytes, stream)
+  if (pair == 1) {
+    if (kind == 0) TB_LAUNCH(0, 1);
+    if (kind == 1) TB_LAUNCH(1, 1);
+    TB_LAUNCH(2, 1);
+  } else {
+    if (kind == 0) TB_LAUNCH(0, 2);
+    if (kind == 1) TB_LAUNCH(1, 2);
+    TB_LAUNCH(2, 2);
+  }
+#undef TB_LAUNCH
+}
+
+}  // namespace tb
+
+// ====================================================================== exported C ABI
+extern "C" {
+
+int tb_select(const tb_problem* p, tb_config* cfg) {
+  if (p == nullptr || cfg == nullptr) return TB_ERR_INVALID;
+  tb::DeviceState* dev = nullptr;
+  // Without a usable device the model falls back to the B200 constants, so the selector also works on a CPU host.
+  if (tb::device_state(p->device, &dev) != TB_OK) dev = nullptr;
+  return tb::select_config(*p, tb::machine_for(dev), cfg);
+}
+
+int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override) {
+  if (cfg == nullptr) return 0;
+  const int64_t programs = sk_grid_override > 0 ? sk_grid_override : (cfg->sk_grid > 0 ? cfg->sk_grid : cfg->num_sms);
+  const int64_t pair = cfg->cta_pair == 2 ? 2 : 1;
+  // 4 KB of flags, then one fp32 partial tile of 128 x block_n per CTA
+  return 4096 + programs * pair * 128 * static_cast<int64_t>(cfg->block_n) * 4;
+}
+
+int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream) {
+  if (args == nullptr) return TB_ERR_INVALID;
+  return tb::gemm_impl(*args, cfg, static_cast<cudaStream_t>(stream));
+}
+
+int tb_device_status(int32_t device, int32_t* status_out) {
+  tb::DeviceState* d = nullptr;
+  int rc = tb::device_state(device, &d);
+  if (rc != TB_OK) return rc;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaSetDevice(device);
+  int v = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(&v, d->status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && v != 0) e = cudaMemset(d->status, 0, sizeof(int));
+  cudaSetDevice(cur);
+  if (e != cudaSuccess) return tb::cuda_fail(e, "tb_device_status");
+  if (status_out) *status_out = v;
+  return TB_OK;
+}
+
+int tb_device_info(int32_t device, int32_t* num_sms, int32_t* smem_optin_bytes) {
+  tb::DeviceState* d = nullptr;
+  int rc = tb::device_state(device, &d);
+  if (rc != TB_OK) return rc;
+  if (num_sms) *num_sms = d->num_sms;
+  if (smem_optin_bytes) *smem_optin_bytes = d->smem_optin;
+  return TB_OK;
+}
+
+const char* tb_status_string(int code) {
+  switch (code) {
+    case TB_OK: return "ok";
+    case TB_ERR_INVALID: return "invalid argument";
+    case TB_ERR_UNSUPPORTED: return "unsupported dtype, layout or shape";
+    case TB_ERR_ALIGNMENT: return "pointer or stride not 16-byte aligned";
+    case TB_ERR_WORKSPACE: return "stream-K workspace missing or too small";
+    case TB_ERR_CUDA: return "CUDA call failed";
+    case TB_ERR_NO_DEVICE: return "no usable CUDA device";
+    case tb::TB_DEV_TIMEOUT_SMEM_EMPTY: return "device: producer timed out waiting for a free shared-memory stage";
+    case tb::TB_DEV_TIMEOUT_SMEM_FULL: return "device: MMA issuer timed out waiting for a TMA-filled stage";
+    case tb::TB_DEV_TIMEOUT_TMEM_EMPTY: return "device: MMA issuer timed out waiting for a drained accumulator";
+    case tb::TB_DEV_TIMEOUT_TMEM_FULL: return "device: epilogue timed out waiting for an accumulator";
+    case tb::TB_DEV_TIMEOUT_PEER_FLAG: return "device: stream-K owner timed out waiting for a peer's partial tile";
+    case tb::TB_DEV_TIMEOUT_SCALE: return "device: timed out waiting for block scales";
+    case tb::TB_DEV_TIMEOUT_STORE: return "device: timed out publishing a partial tile";
+    default: return "unknown status";
+  }
+}
+
+const char* tb_last_cuda_error(void) { return tb::g_cuda_err; }
+
+int64_t tb_launch_count(void) { return tb::g_launches.load(); }
+
+}  // extern "C"

@@ -1,0 +1,481 @@
+// Persistent, warp-specialised GEMM for sm_100a: TMA -> shared-memory ring -> tcgen05.mma -> TMEM -> epilogue.
+//
+// One kernel covers the dense family (fp16 / bf16 / tf32 / fp8 operands, all four operand layouts, data-parallel and
+// stream-K scheduling, optional per-row x per-column scales and N-broadcast bias). Tile width, operand majors, stage
+// count and the schedule are run-time values; only the MMA kind and the CTA-pair width are compile-time.
+//
+// Roles inside a CTA of 192 threads:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocator + MMA issuer (one elected lane; in a CTA pair only the even CTA issues)
+//   warps 2..5  epilogue: TMEM -> registers -> (stream-K fix-up) -> scale, bias, cast -> global
+// The accumulator is double-buffered in TMEM so the epilogue of one work item overlaps the main loop of the next.
+//
+// Semantics follow the reference kernels: tile order with GROUP_SIZE_M swizzle (kernels/stages/schedule.py:124-145),
+// epilogue order scale -> bias -> cast -> masked store (kernels/stages/matrix_view.py:263-301), hybrid stream-K with
+// fp32 partial tiles reduced by the tile owner in increasing program order (kernels/streamk_gemm.py:175-324).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include "ptx.cuh"
+
+namespace tb {
+
+constexpr int kTileM = 128;          // accumulator rows per CTA (TMEM lanes)
+constexpr int kStageRowBytes = 128;  // one swizzle row: K extent of a stage in bytes for K-major operands
+constexpr int kGemmThreads = 192;
+constexpr int kATileBytes = kTileM * kStageRowBytes;  // 16 KB
+
+enum : int { TB_F16 = 0, TB_BF16 = 1, TB_F32 = 2, TB_E4M3 = 3, TB_E5M2 = 4, TB_U8 = 5 };
+
+struct GemmParams {
+  int M, N, K;
+  int block_n;       // output tile width (columns), multiple of 32, <= 256. For a CTA pair: the pair's tile width.
+  int num_k_blocks;  // ceil(K / k elements per stage)
+  int k_per_stage;   // K elements per stage
+  int tiles_m, tiles_n, group_m;
+  int stages;
+  int esize;       // operand element size in bytes
+  int a_mn, b_mn;  // 1 if the operand is stored with M (resp. N) contiguous instead of K
+  uint32_t idesc;  // tcgen05 instruction descriptor
+  uint32_t tmem_cols;
+  // output and epilogue
+  void* C;
+  long long ldc_m, ldc_n;
+  int c_dtype;
+  const float* a_scale;  // (M,) or null
+  const float* b_scale;  // (N,) or null
+  const void* bias;      // (N,) or null
+  long long bias_stride;
+  int bias_dtype;
+  // schedule
+  int dp_tiles;  // tiles [0, dp_tiles) are data-parallel: tile = program + i * programs
+  int sk_tiles;  // tiles [dp_tiles, dp_tiles + sk_tiles) have their K iterations split evenly over all programs
+  float* partials;   // [programs * CTAS][block_n][128] fp32
+  unsigned* flags;   // [programs * CTAS]
+  unsigned epoch;    // value that marks a partial as published for this launch
+  // failure reporting
+  int* status;
+  unsigned long long timeout_ns;
+};
+
+struct WorkItem {
+  int tile, kb0, kb1;
+  bool valid;
+};
+
+// Enumerates the work of one program: first its data-parallel tiles, then its slice of the stream-K iteration space.
+struct WorkIter {
+  int pid, nprog, nkb, dp_tiles, sk_tiles;
+  int dp_next;
+  long long it, it_end;
+  __device__ WorkIter(const GemmParams& p, int pid_, int nprog_)
+      : pid(pid_), nprog(nprog_), nkb(p.num_k_blocks), dp_tiles(p.dp_tiles), sk_tiles(p.sk_tiles) {
+    dp_next = pid;
+    range(pid, it, it_end);
+  }
+  __device__ void range(int q, long long& b, long long& e) const {
+    const long long total = static_cast<long long>(sk_tiles) * nkb;
+    const long long base = total / nprog, rem = total % nprog;
+    b = q * base + (q < rem ? q : rem);
+    e = b + base + (q < rem ? 1 : 0);
+  }
+  __device__ WorkItem next() {
+    WorkItem w;
+    if (dp_next < dp_tiles) {
+      w.tile = dp_next;
+      w.kb0 = 0;
+      w.kb1 = nkb;
+      w.valid = true;
+      dp_next += nprog;
+      return w;
+    }
+    if (it < it_end) {
+      const int t = static_cast<int>(it / nkb);
+      const long long tile_end = static_cast<long long>(t + 1) * nkb;
+      const long long e = it_end < tile_end ? it_end : tile_end;
+      w.tile = dp_tiles + t;
+      w.kb0 = static_cast<int>(it - static_cast<long long>(t) * nkb);
+      w.kb1 = static_cast<int>(e - static_cast<long long>(t) * nkb);
+      w.valid = true;
+      it = e;
+      return w;
+    }
+    w.valid = false;
+    w.tile = w.kb0 = w.kb1 = 0;
+    return w;
+  }
+};
+
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+  const int width = p.group_m * p.tiles_n;
+  const int group = tile / width;
+  const int first_m = group * p.group_m;
+  const int gsz = min(p.tiles_m - first_m, p.group_m);
+  const int r = tile - group * width;
+  tm = first_m + r % gsz;
+  tn = r / gsz;
+}
+
+__device__ __forceinline__ float load_as_float(const void* p, long long idx, int dtype) {
+  switch (dtype) {
+    case TB_F16: return __half2float(reinterpret_cast<const __half*>(p)[idx]);
+    case TB_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
+    default: return reinterpret_cast<const float*>(p)[idx];
+  }
+}
+
+// Store 32 consecutive columns of one output row. `v` holds fp32 values after scale and bias.
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, int col0, const float (&v)[32]) {
+  const int ncols = min(32, p.N - col0);
+  if (ncols <= 0) return;
+  if (p.c_dtype == TB_BF16 || p.c_dtype == TB_F16) {
+    unsigned short* base = reinterpret_cast<unsigned short*>(p.C) + row * p.ldc_m + col0 * p.ldc_n;
+    if (p.ldc_n == 1 && ncols == 32 && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
+      uint4* dst = reinterpret_cast<uint4*>(base);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const float lo = v[j * 8 + h * 2], hi = v[j * 8 + h * 2 + 1];
+          if (p.c_dtype == TB_BF16) {
+            __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+            w[h] = *reinterpret_cast<uint32_t*>(&t);
+          } else {
+            __half2 t = __floats2half2_rn(lo, hi);
+            w[h] = *reinterpret_cast<uint32_t*>(&t);
+          }
+        }
+        dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < ncols) {
+          unsigned short bits;
+          if (p.c_dtype == TB_BF16) {
+            __nv_bfloat16 t = __float2bfloat16_rn(v[j]);
+            bits = *reinterpret_cast<unsigned short*>(&t);
+          } else {
+            __half t = __float2half_rn(v[j]);
+            bits = *reinterpret_cast<unsigned short*>(&t);
+          }
+          base[j * p.ldc_n] = bits;
+        }
+      }
+    }
+  } else if (p.c_dtype == TB_F32) {
+    float* base = reinterpret_cast<float*>(p.C) + row * p.ldc_m + col0 * p.ldc_n;
+    if (p.ldc_n == 1 && ncols == 32 && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
+      float4* dst = reinterpret_cast<float4*>(base);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) base[j * p.ldc_n] = v[j];
+    }
+  } else {  // fp8 e4m3 output, saturating
+    unsigned char* base = reinterpret_cast<unsigned char*>(p.C) + row * p.ldc_m + col0 * p.ldc_n;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) base[j * p.ldc_n] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(v[j], __NV_SATFINITE, __NV_E4M3));
+  }
+}
+
+template <int KIND, int CTAS>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment is what the 128-byte swizzle pattern and the matrix descriptors assume.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
+  const int pid = (CTAS == 2) ? (blockIdx.x >> 1) : blockIdx.x;
+  const int nprog = (CTAS == 2) ? (gridDim.x >> 1) : gridDim.x;
+
+  const int bn_local = p.block_n / CTAS;  // B rows this CTA stages
+  const int b_tile_bytes = bn_local * kStageRowBytes;
+  const int stage_bytes = kATileBytes + b_tile_bytes;
+  const int stages = p.stages;
+
+  uint8_t* ring = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(stages) * stage_bytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + stages;
+  uint64_t* tmem_full = bars + 2 * stages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint64_t* publish_bar = tmem_empty + 2;  // the four epilogue warps have all written their part of a partial tile
+  uint32_t* tmem_ptr_slot = reinterpret_cast<uint32_t*>(publish_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_slot + 1);
+
+  WaitCtx wctx{abort_flag, p.status, p.timeout_ns};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4 * CTAS);  // one arrival per epilogue warp of every CTA that shares the accumulator
+    }
+    mbar_init(publish_bar, 4);
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc<CTAS>(tmem_ptr_slot, p.tmem_cols);
+    tmem_relinquish<CTAS>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (CTAS == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  const int acc_stride = p.block_n;  // TMEM columns per accumulator stage
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      WorkIter wi(p, pid, nprog);
+      int s = 0;
+      uint32_t ph = 0;
+      const int a_atom = kStageRowBytes / p.esize;  // elements per 128-byte row
+      // In a pair, transaction bytes of both CTAs land on the even CTA's barrier, which expects the sum.
+      const uint32_t expect = static_cast<uint32_t>(stage_bytes) * CTAS;
+      bool ok = true;
+      for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
+        int tm, tn;
+        tile_coords(p, w.tile, tm, tn);
+        const int m0 = tm * (kTileM * CTAS) + static_cast<int>(cta_rank) * kTileM;
+        const int n0 = tn * p.block_n + static_cast<int>(cta_rank) * bn_local;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, wctx, TB_DEV_TIMEOUT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = ring + static_cast<size_t>(s) * stage_bytes;
+          uint8_t* sb = sa + kATileBytes;
+          const int k0 = kb * p.k_per_stage;
+          if constexpr (CTAS == 1) {
+            mbar_arrive_expect_tx(&full_bar[s], expect);
+            if (!p.a_mn) {
+              tma_load_2d(sa, &tmap_a, &full_bar[s], k0, m0);
+            } else {
+              for (int j = 0; j < kTileM / a_atom; ++j)
+                tma_load_2d(sa + j * (p.k_per_stage * kStageRowBytes), &tmap_a, &full_bar[s], m0 + j * a_atom, k0);
+            }
+            if (!p.b_mn) {
+              tma_load_2d(sb, &tmap_b, &full_bar[s], k0, n0);
+            } else {
+              for (int j = 0; j < bn_local / a_atom; ++j)
+                tma_load_2d(sb + j * (p.k_per_stage * kStageRowBytes), &tmap_b, &full_bar[s], n0 + j * a_atom, k0);
+            }
+          } else {
+            const uint32_t bar = mapa_cluster(smem_u32(&full_bar[s]), 0);
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], expect);
+            if (!p.a_mn) {
+              tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
+            } else {
+              for (int j = 0; j < kTileM / a_atom; ++j)
+                tma_load_2d_pair(sa + j * (p.k_per_stage * kStageRowBytes), &tmap_a, bar, m0 + j * a_atom, k0);
+            }
+            if (!p.b_mn) {
+              tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
+            } else {
+              for (int j = 0; j < bn_local / a_atom; ++j)
+                tma_load_2d_pair(sb + j * (p.k_per_stage * kStageRowBytes), &tmap_b, bar, n0 + j * a_atom, k0);
+            }
+          }
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && cta_rank == 0) {
+      WorkIter wi(p, pid, nprog);
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      // Byte distances inside one operand tile (see make_smem_desc).
+      const uint32_t mn_atom_stride = static_cast<uint32_t>(p.k_per_stage) * kStageRowBytes;
+      const uint32_t a_lead = p.a_mn ? mn_atom_stride : 16u, b_lead = p.b_mn ? mn_atom_stride : 16u;
+      // K advance per MMA (32 bytes of K): 32 bytes inside the swizzle row, or (32/esize) rows of 128 bytes.
+      const uint32_t a_kstep = p.a_mn ? (32u / p.esize) * kStageRowBytes : 32u;
+      const uint32_t b_kstep = p.b_mn ? (32u / p.esize) * kStageRowBytes : 32u;
+      bool ok = true;
+      for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, wctx, TB_DEV_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * acc_stride);
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph, wctx, TB_DEV_TIMEOUT_SMEM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(ring + static_cast<size_t>(s) * stage_bytes);
+          const uint32_t sb = sa + kATileBytes;
+          const uint64_t adesc = make_smem_desc(sa, a_lead, 1024);
+          const uint64_t bdesc = make_smem_desc(sb, b_lead, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            umma<KIND, CTAS>(d_tmem, adesc + ((k * a_kstep) >> 4), bdesc + ((k * b_kstep) >> 4), p.idesc,
+                             (kb > w.kb0 || k > 0) ? 1u : 0u);
+          }
+          // Free the stage once these MMAs have read it.
+          if constexpr (CTAS == 1) umma_commit(&empty_bar[s]);
+          else umma_commit_pair(&empty_bar[s], 3);
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        if (!ok) break;
+        if constexpr (CTAS == 1) umma_commit(&tmem_full[acc]);
+        else umma_commit_pair(&tmem_full[acc], 3);
+        if (++acc == 2) {
+          acc = 0;
+          acc_ph ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const int row_in_tile = q * 32 + lane;
+    WorkIter wi(p, pid, nprog);
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    const int slot = pid * CTAS + static_cast<int>(cta_rank);
+    const size_t slot_elems = static_cast<size_t>(p.block_n) * kTileM;
+    const uint32_t tmem_empty_remote = (CTAS == 2) ? mapa_cluster(smem_u32(&tmem_empty[0]), 0) : 0u;
+    bool ok = true;
+    for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
+      int tm, tn;
+      tile_coords(p, w.tile, tm, tn);
+      const int m0 = tm * (kTileM * CTAS) + static_cast<int>(cta_rank) * kTileM;
+      const int n0 = tn * p.block_n;
+      const int row = m0 + row_in_tile;
+      const bool owner = (w.kb0 == 0);
+      const bool complete = owner && (w.kb1 == p.num_k_blocks);
+      // Every decision to unwind is made warp-uniform: the TMEM loads below need the whole warp.
+      ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_ph, wctx, TB_DEV_TIMEOUT_TMEM_FULL));
+      if (!ok) break;
+      tc_fence_after();
+
+      // Peers that hold the rest of this tile's K range: programs after this one whose slice starts inside the tile.
+      int peer_end = pid + 1;
+      if (owner && !complete) {
+        const long long tile_end = static_cast<long long>(w.tile - p.dp_tiles + 1) * p.num_k_blocks;
+        long long b, e;
+        while (peer_end < nprog) {
+          wi.range(peer_end, b, e);
+          if (b >= tile_end || b >= e) break;
+          ++peer_end;
+        }
+        for (int pp = pid + 1; pp < peer_end && ok; ++pp)
+          ok = flag_wait(&p.flags[pp * CTAS + static_cast<int>(cta_rank)], p.epoch, wctx, TB_DEV_TIMEOUT_PEER_FLAG);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+
+      const float a_s = (p.a_scale != nullptr && row < p.M) ? p.a_scale[row] : 1.0f;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * acc_stride);
+      for (int c = 0; c < p.block_n / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (!owner) {
+          // Publish a partial tile: column-major inside the slot so that a warp writes 128 contiguous bytes.
+          float* dst = p.partials + slot * slot_elems + static_cast<size_t>(c * 32) * kTileM + row_in_tile;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) dst[j * kTileM] = v[j];
+          continue;
+        }
+        for (int pp = pid + 1; pp < peer_end; ++pp) {
+          const float* src =
+              p.partials + (pp * CTAS + static_cast<int>(cta_rank)) * slot_elems + static_cast<size_t>(c * 32) * kTileM + row_in_tile;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * kTileM);
+        }
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          if (p.a_scale != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= a_s;
+          }
+          if (p.b_scale != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= (col0 + j < p.N) ? p.b_scale[col0 + j] : 1.0f;
+          }
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += load_as_float(p.bias, (col0 + j) * p.bias_stride, p.bias_dtype);
+          }
+          store_row_chunk(p, row, col0, v);
+        }
+      }
+      // Hand the accumulator back to the MMA issuer.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CTAS == 1) mbar_arrive(&tmem_empty[acc]);
+        else mbar_arrive_remote(tmem_empty_remote + acc * 8);
+      }
+      if (!owner) {
+        // A program publishes at most one partial tile per launch (only its first stream-K segment can start
+        // inside a tile), so this barrier is used for a single phase.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(publish_bar);
+        if (warp == 2 && lane == 0) {
+          if (mbar_wait(publish_bar, 0, wctx, TB_DEV_TIMEOUT_STORE)) flag_release(&p.flags[slot], p.epoch);
+        }
+      }
+      if (++acc == 2) {
+        acc = 0;
+        acc_ph ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    // A wait gave up: let copies and MMAs already in flight land before shared memory and TMEM are released.
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (CTAS == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<CTAS>(tmem_base, p.tmem_cols);
+  }
+}
+
+}  // namespace tb

@@ -1,0 +1,134 @@
+// Analytical tile / schedule selector for B200, the native counterpart of the reference's external `origami`
+// model (call sites include/tritonblas/origami.py:166,232-262) and of its stream-K grid rule (:349-416).
+//
+// The model is derived for the machine, not transcribed: a CTA owns 128 accumulator rows (TMEM lanes) and a tile
+// width BN in {32..256}; two CTAs of a cluster may pair up on a 256 x BN tile so each stages only half of B. Every
+// shared-memory stage holds 128 bytes of K per operand row, so for every operand type one stage costs
+//     mma clocks   = 2 * BN                      (4 MMAs of 128 x BN x 32 bytes-of-K, BN/2 clocks each)
+//     fill bytes   = (128 + BN / pair) * 128     (this CTA's A rows + its share of B rows)
+// and a tile costs num_k_blocks * max(mma, fill / fabric bytes-per-clock) clocks. A data-parallel launch runs
+// ceil(tiles / programs) waves of that; a stream-K launch runs tiles * num_k_blocks / programs stages per program
+// plus the fix-up of one partial tile. Whole-problem HBM time is a floor under both.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+
+#include "../../include/tritonblas_b200.h"
+#include "selector.h"
+
+namespace tb {
+
+static int esize_of(int dtype) {
+  switch (dtype) {
+    case TB_DTYPE_F16:
+    case TB_DTYPE_BF16: return 2;
+    case TB_DTYPE_F32: return 4;
+    case TB_DTYPE_E4M3:
+    case TB_DTYPE_E5M2:
+    case TB_DTYPE_U8: return 1;
+    default: return 0;
+  }
+}
+
+static int next_pow2(int v) {
+  int r = 32;
+  while (r < v) r <<= 1;
+  return r;
+}
+
+int smem_bytes_for(int block_n, int cta_pair, int stages) {
+  const int stage = 128 * 128 + (block_n / cta_pair) * 128;
+  return stages * stage + (2 * stages + 8) * 8 + 64 + 1024;  // ring + barriers + slots + alignment slack
+}
+
+struct Candidate {
+  int bn, pair;
+  double dp_us, sk_us;
+  int grid, sk_grid, stages, group_m;
+};
+
+int select_config(const tb_problem& p, const MachineModel& hw, tb_config* out) {
+  if (p.m <= 0 || p.n <= 0 || p.k <= 0) return TB_ERR_INVALID;
+  const bool mx = p.mx_block_size == 32 || p.a_dtype == TB_DTYPE_F4;
+  const int es = mx ? 1 : esize_of(p.a_dtype);
+  if (es == 0) return TB_ERR_UNSUPPORTED;
+  const int sms = (p.num_sms > 0 && p.num_sms <= hw.num_sms) ? p.num_sms : hw.num_sms;
+  // K elements per stage: 128 bytes of K; packed fp4 carries two elements per byte.
+  const int bk = mx ? 256 : 128 / es;
+  const int nkb = (p.k + bk - 1) / bk;
+  const int mn_atom = 128 / es;  // an N-contiguous B is staged in boxes of this many columns
+  const double c_bytes = static_cast<double>(p.m) * p.n * esize_of(p.c_dtype);
+  const double ab_bytes = (static_cast<double>(p.m) * p.k + static_cast<double>(p.n) * p.k) * (mx ? 0.5 : es);
+  const double hbm_us = (c_bytes + ab_bytes) / (hw.hbm_gbs * 1e3);
+  // fp4 MMAs retire 64 bytes of K per instruction at the clocks an 8/16-bit MMA needs for 32.
+  const double mma_clk_per_stage_per_bn = mx ? 1.0 : 2.0;
+
+  Candidate best{};
+  double best_cost = 1e30;
+  static const int kBN[] = {256, 128, 64, 32};
+  for (int pair = 2; pair >= 1; --pair) {
+    if (pair == 2 && (sms < 2 || !hw.allow_pair)) continue;
+    for (int bn : kBN) {
+      const int bn_local = bn / pair;
+      if (p.b_mn_major && (bn_local % mn_atom) != 0) continue;
+      if (bn_local < 16) continue;
+      if (mx && bn < 128) continue;  // block-scale copies move 128 scale rows at a time
+      const int tile_m = 128 * pair;
+      const long long tiles_m = (p.m + tile_m - 1) / tile_m, tiles_n = (p.n + bn - 1) / bn;
+      const long long tiles = tiles_m * tiles_n;
+      const int programs = std::max(1, sms / pair);
+      int stages = (hw.smem_optin - 2048) / (128 * 128 + bn_local * 128 + (mx ? (128 + bn_local) * 8 : 0));
+      stages = std::min(stages, 8);
+      if (stages < 2) continue;
+      const double mma_clk = mma_clk_per_stage_per_bn * bn;
+      const double fill_clk = (128.0 + bn_local) * 128.0 / hw.fabric_bytes_per_clk;
+      const double stage_clk = std::max(mma_clk, fill_clk);
+      const double ramp_clk = hw.tile_ramp_clk;  // first-stage latency + epilogue drain not hidden by the next tile
+      const double clk_to_us = 1.0 / (hw.sm_mhz);
+      // data-parallel
+      const long long waves = (tiles + programs - 1) / programs;
+      double dp = (waves * nkb * stage_clk + ramp_clk + bn * 8.0) * clk_to_us;
+      dp = std::max(dp, hbm_us) + hw.launch_us;
+      // stream-K: stages per program, plus one partial tile written and read back through L2, plus the flag hop
+      const int sk_grid = static_cast<int>(std::min<long long>(programs, tiles * nkb));
+      const double per_prog = std::ceil(static_cast<double>(tiles) * nkb / sk_grid);
+      const bool needs_fix = (tiles % sk_grid) != 0;
+      double sk = (per_prog * stage_clk + ramp_clk + bn * 8.0) * clk_to_us;
+      if (needs_fix) sk += 2.0 * 128.0 * bn * 4.0 / (hw.fabric_bytes_per_clk * hw.sm_mhz) + hw.flag_us;
+      sk = std::max(sk, hbm_us) + hw.launch_us;
+      const double cost = p.streamk ? sk : dp;
+      // Prefer, on ties, the wider tile and the pair (fewer fabric bytes per flop).
+      if (cost < best_cost * 0.995) {
+        best_cost = cost;
+        best.bn = bn;
+        best.pair = pair;
+        best.dp_us = dp;
+        best.sk_us = sk;
+        best.grid = static_cast<int>(std::min<long long>(programs, tiles));
+        best.sk_grid = sk_grid;
+        best.stages = stages;
+        const double g = std::sqrt(static_cast<double>(programs) * bn / tile_m);
+        best.group_m = static_cast<int>(std::max<long long>(1, std::min<long long>(tiles_m, std::llround(g))));
+      }
+    }
+  }
+  if (best_cost >= 1e30) return TB_ERR_UNSUPPORTED;
+  std::memset(out, 0, sizeof(*out));
+  out->block_m = 128 * best.pair;
+  out->block_n = best.bn;
+  out->block_k = bk;
+  out->group_m = best.group_m;
+  out->stages = best.stages;
+  out->cta_pair = best.pair;
+  out->grid = best.grid;
+  out->sk_grid = best.sk_grid;
+  out->num_sms = sms;
+  out->smem_bytes = smem_bytes_for(best.bn, best.pair, best.stages) + (mx ? best.stages * (128 + best.bn / best.pair) * 8 : 0);
+  out->tmem_cols = next_pow2(2 * best.bn + (mx ? 64 : 0));
+  out->predicted_us = static_cast<float>(best.dp_us);
+  out->predicted_sk_us = static_cast<float>(best.sk_us);
+  return TB_OK;
+}
+
+}  // namespace tb

@@ -1,0 +1,288 @@
+"""Host API of the GEMM family: same names, argument order and error behaviour as the reference's
+include/tritonblas/matmul.py, implemented as thin marshalling over the C ABI (tb_gemm and friends).
+
+No kernel is written here and nothing falls back to torch: a missing library or an unsupported request raises.
+"""
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .config import MatmulConfig, matmul_preamble, workspace_bytes
+from .origami import OrigamiMatmulSelector
+
+# Per-device stream-K workspace used when the caller passes no MatmulConfig; like the reference's module-level
+# locks/P buffers (matmul.py:20-26) it serves one stream at a time.
+_global_workspaces = {}
+
+
+class _GlobalWorkspace:
+    def __init__(self, device, nbytes):
+        self.workspace = torch.zeros(nbytes, device=device, dtype=torch.uint8)
+        self.epoch = 0
+
+    def next_epoch(self):
+        self.epoch = (self.epoch % 0xFFFFFFF0) + 1
+        if self.epoch == 1:
+            self.workspace[:4096].zero_()
+        return self.epoch
+
+
+def _workspace_for(device, nbytes):
+    key = (device.type, device.index)
+    ws = _global_workspaces.get(key)
+    if ws is None or ws.workspace.numel() < nbytes:
+        ws = _GlobalWorkspace(device, max(nbytes, 4096 + 148 * 128 * 256 * 4))
+        _global_workspaces[key] = ws
+    return ws
+
+
+def _make_matmul_selector(M, N, K, a_dtype, b_dtype, c_dtype, device, mx_block_size=0, streamk=False, num_stages=2,
+                          a_mn_major=False, b_mn_major=False):
+    return OrigamiMatmulSelector(M, N, K, a_dtype, b_dtype, c_dtype, device, mx_block_size=mx_block_size,
+                                 streamk=streamk, num_stages=num_stages, a_mn_major=a_mn_major, b_mn_major=b_mn_major)
+
+
+def _unit_stride_2d(t):
+    """Kernels take any 2-D view with one unit stride; anything else is materialised row-major."""
+    if t.stride(1) == 1 or t.stride(0) == 1:
+        return t
+    return t.contiguous()
+
+
+def _is_mn_major(t, contiguous_axis_is_k_index):
+    """True when the K axis (index given) of a 2-D operand is NOT its unit-stride axis."""
+    other = 1 - contiguous_axis_is_k_index
+    if t.stride(contiguous_axis_is_k_index) == 1 or t.shape[contiguous_axis_is_k_index] == 1:
+        return False
+    return t.stride(other) == 1 or t.shape[other] == 1
+
+
+def _strides(t):
+    """Element strides with any extent-1 axis given its dense stride (such an axis may carry an arbitrary one)."""
+    s0, s1 = t.stride()
+    if t.shape[0] == 1 and s1 == 1:
+        s0 = t.shape[1]
+    if t.shape[1] == 1 and s0 == 1:
+        s1 = t.shape[0]
+    return s0, s1
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, streamk=False, sk_grid=None):
+    assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
+    if not (a.is_cuda and b.is_cuda and c.is_cuda):
+        raise RuntimeError("tritonblas_b200 runs on CUDA tensors only (no CPU path)")
+    M, K = a.shape
+    _, N = b.shape
+    if tuple(c.shape) != (M, N):
+        raise RuntimeError(f"output has shape {tuple(c.shape)}, expected {(M, N)}")
+    if M == 0 or N == 0:
+        return c
+    if K == 0:
+        c.zero_()
+        if bias is not None:
+            c.add_(bias.to(c.dtype))
+        return c
+    a = _unit_stride_2d(a)
+    b = _unit_stride_2d(b)
+    a_mn, b_mn = _is_mn_major(a, 1), _is_mn_major(b, 0)
+    cfg = selector.config_for(a_mn, b_mn)
+
+    args = _lib.GemmArgs()
+    args.m, args.n, args.k = M, N, K
+    args.a_dtype, args.b_dtype, args.c_dtype = (_lib.DTYPE_CODE[a.dtype], _lib.DTYPE_CODE[b.dtype], _lib.DTYPE_CODE[c.dtype])
+    args.a, (args.a_stride_m, args.a_stride_k) = _ptr(a), _strides(a)
+    args.b, (args.b_stride_k, args.b_stride_n) = _ptr(b), _strides(b)
+    args.c, (args.c_stride_m, args.c_stride_n) = _ptr(c), _strides(c)
+    if a_scale is not None:
+        a_scale = a_scale.to(torch.float32).contiguous().view(-1)
+        b_scale = b_scale.to(torch.float32).contiguous().view(-1)
+        assert a_scale.numel() == M and b_scale.numel() == N, "scale vectors must be (M,) and (N,)"
+        args.a_scale, args.b_scale = _ptr(a_scale), _ptr(b_scale)
+    if bias is not None:
+        assert bias.numel() == N, "bias must have N elements"
+        bias = bias.view(-1)
+        args.bias, args.bias_stride, args.bias_dtype = _ptr(bias), bias.stride(0), _lib.DTYPE_CODE[bias.dtype]
+    args.allow_tf32 = int(torch.backends.cuda.matmul.allow_tf32)
+    args.streamk = int(bool(streamk))
+    args.sk_grid = int(sk_grid) if sk_grid else 0
+    if streamk:
+        need = workspace_bytes(cfg, args.sk_grid)
+        holder = config if (config is not None and config.workspace.numel() >= need) else _workspace_for(a.device, need)
+        args.workspace, args.workspace_bytes = _ptr(holder.workspace), holder.workspace.numel()
+        args.epoch = holder.next_epoch()
+    with torch.cuda.device(a.device):
+        rc = _lib.lib.tb_gemm(ctypes.byref(args), ctypes.byref(cfg), _lib.current_stream_ptr(a.device))
+    _lib.check(rc, "tb_gemm")
+    return c
+
+
+def persistent_matmul_lt(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, quantized=False,
+                         work_stealing=False):
+    """Data-parallel persistent GEMM (reference: matmul.py:69-200). ``work_stealing`` is accepted; tiles are
+    scheduled statically."""
+    return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=False)
+
+
+def streamk_matmul_lt(a, b, c, selector, config=None, bias=None, sk_grid=None, a_scale=None, b_scale=None,
+                      quantized=False, work_stealing=False):
+    """Hybrid stream-K GEMM (reference: matmul.py:202-366)."""
+    return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=True, sk_grid=sk_grid)
+
+
+def matmul_lt(a, b, c, selector, config: Optional[MatmulConfig] = None, enable_streamk=False, work_stealing=False):
+    assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
+    if enable_streamk:
+        return streamk_matmul_lt(a, b, c, selector, config, work_stealing=work_stealing)
+    return persistent_matmul_lt(a, b, c, selector, config, work_stealing=work_stealing)
+
+
+def matmul_a8w8_lt(a, b, a_scale, b_scale, c, selector, config: Optional[MatmulConfig] = None, enable_streamk=False,
+                   work_stealing=False):
+    assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
+    if enable_streamk:
+        return streamk_matmul_lt(a, b, c, selector, config, a_scale=a_scale, b_scale=b_scale, quantized=True)
+    return persistent_matmul_lt(a, b, c, selector, config, a_scale=a_scale, b_scale=b_scale, quantized=True,
+                                work_stealing=work_stealing)
+
+
+def _selector_for(a, b, c_dtype, streamk):
+    M, K = a.shape
+    _, N = b.shape
+    return _make_matmul_selector(M, N, K, a.dtype, b.dtype, c_dtype, a.device, streamk=bool(streamk),
+                                 a_mn_major=_is_mn_major(_unit_stride_2d(a), 1), b_mn_major=_is_mn_major(_unit_stride_2d(b), 0))
+
+
+# ---------------------------------------------------------------------------------------------- custom ops
+@torch.library.custom_op("tritonblas::_matmul", mutates_args=())
+def _matmul(a: torch.Tensor, b: torch.Tensor, enable_streamk: Optional[bool] = False, sk_grid: Optional[int] = None,
+            work_stealing: Optional[bool] = False) -> torch.Tensor:
+    assert a.shape[1] == b.shape[0], "Incompatible A-B Dimensions"
+    out = a.new_empty(a.shape[0], b.shape[1])
+    selector = _selector_for(a, b, out.dtype, enable_streamk)
+    if enable_streamk:
+        streamk_matmul_lt(a, b, out, selector, None, sk_grid=sk_grid, work_stealing=work_stealing)
+    else:
+        persistent_matmul_lt(a, b, out, selector, None, work_stealing=work_stealing)
+    return out
+
+
+@_matmul.register_fake
+def _(a, b, enable_streamk=False, sk_grid=None, work_stealing=False):
+    return a.new_empty(a.shape[0], b.shape[1])
+
+
+def _setup_context_matmul_backwards(ctx, inputs, output):
+    a, b, enable_streamk, sk_grid, work_stealing = inputs
+    ctx.save_for_backward(a, b)
+    ctx.enable_streamk, ctx.sk_grid, ctx.work_stealing = enable_streamk, sk_grid, work_stealing
+
+
+def _matmul_backwards(ctx, grad_output):
+    # Two more forward GEMMs on materialised transposes, as the reference does (matmul.py:427-444).
+    a, b = ctx.saved_tensors
+    kw = dict(enable_streamk=ctx.enable_streamk, sk_grid=ctx.sk_grid, work_stealing=ctx.work_stealing)
+    g = grad_output.contiguous()
+    grad_a = matmul(g, b.T.contiguous(), **kw) if ctx.needs_input_grad[0] else None
+    grad_b = matmul(a.T.contiguous(), g, **kw) if ctx.needs_input_grad[1] else None
+    return grad_a, grad_b, None, None, None
+
+
+_matmul.register_autograd(_matmul_backwards, setup_context=_setup_context_matmul_backwards)
+
+
+@torch.library.custom_op("tritonblas::_matmul_out", mutates_args={"out"})
+def _matmul_out(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, enable_streamk: Optional[bool] = False,
+                sk_grid: Optional[int] = None, work_stealing: Optional[bool] = False) -> None:
+    assert a.shape[1] == b.shape[0], "Incompatible A-B Dimensions"
+    selector = _selector_for(a, b, out.dtype, enable_streamk)
+    if enable_streamk:
+        streamk_matmul_lt(a, b, out, selector, None, sk_grid=sk_grid, work_stealing=work_stealing)
+    else:
+        persistent_matmul_lt(a, b, out, selector, None, work_stealing=work_stealing)
+    return None
+
+
+def matmul(a, b, out=None, enable_streamk=False, sk_grid=None, work_stealing=False):
+    """C = A @ B. Returns the product, or None when ``out`` is given (the result is written into it)."""
+    if out is None:
+        return _matmul(a, b, enable_streamk, sk_grid, work_stealing)
+    if torch.is_grad_enabled() and (a.requires_grad or b.requires_grad or out.requires_grad):
+        raise RuntimeError("tritonblas.matmul(): functions with out=... arguments don't support "
+                           "automatic differentiation, but one of the arguments requires grad.")
+    return _matmul_out(a, b, out, enable_streamk, sk_grid, work_stealing)
+
+
+def matmul_a8w8(a, b, a_scale, b_scale, c, enable_streamk=False, work_stealing=False, sk_grid=None):
+    """C = cast((A8 . B8 in fp32) * a_scale[:, None] * b_scale[None, :]) (reference: matmul.py:498-517, intended
+    semantics tests/test_matmul_a8w8_lt.py:11-38)."""
+    assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
+    selector = _selector_for(a, b, c.dtype, enable_streamk)
+    if enable_streamk:
+        return streamk_matmul_lt(a, b, c, selector, None, sk_grid=sk_grid, a_scale=a_scale, b_scale=b_scale, quantized=True)
+    return persistent_matmul_lt(a, b, c, selector, None, a_scale=a_scale, b_scale=b_scale, quantized=True)
+
+
+@torch.library.custom_op("tritonblas::_addmm", mutates_args=())
+def _addmm(bias: torch.Tensor, a: torch.Tensor, b: torch.Tensor, enable_streamk: Optional[bool] = False,
+           sk_grid: Optional[int] = None, work_stealing: Optional[bool] = False) -> torch.Tensor:
+    assert a.shape[1] == b.shape[0], "Incompatible A-B Dimensions"
+    out = a.new_empty(a.shape[0], b.shape[1])
+    selector = _selector_for(a, b, bias.dtype, enable_streamk)
+    if enable_streamk:
+        streamk_matmul_lt(a, b, out, selector, None, bias=bias, sk_grid=sk_grid, work_stealing=work_stealing)
+    else:
+        persistent_matmul_lt(a, b, out, selector, None, bias=bias, work_stealing=work_stealing)
+    return out
+
+
+@_addmm.register_fake
+def _(bias, a, b, enable_streamk=False, sk_grid=None, work_stealing=False):
+    return a.new_empty(a.shape[0], b.shape[1])
+
+
+def _setup_context_addmm_backwards(ctx, inputs, output):
+    bias, a, b, enable_streamk, sk_grid, work_stealing = inputs
+    ctx.save_for_backward(a, b)
+    ctx.enable_streamk, ctx.sk_grid, ctx.work_stealing = enable_streamk, sk_grid, work_stealing
+
+
+def _addmm_backwards(ctx, grad_output):
+    a, b = ctx.saved_tensors
+    kw = dict(enable_streamk=ctx.enable_streamk, sk_grid=ctx.sk_grid, work_stealing=ctx.work_stealing)
+    g = grad_output.contiguous()
+    grad_bias = grad_output.sum(dim=0) if ctx.needs_input_grad[0] else None
+    grad_a = matmul(g, b.T.contiguous(), **kw) if ctx.needs_input_grad[1] else None
+    grad_b = matmul(a.T.contiguous(), g, **kw) if ctx.needs_input_grad[2] else None
+    return grad_bias, grad_a, grad_b, None, None, None
+
+
+_addmm.register_autograd(_addmm_backwards, setup_context=_setup_context_addmm_backwards)
+
+
+@torch.library.custom_op("tritonblas::_addmm_out", mutates_args={"out"})
+def _addmm_out(bias: torch.Tensor, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor,
+               enable_streamk: Optional[bool] = False, sk_grid: Optional[int] = None,
+               work_stealing: Optional[bool] = False) -> None:
+    assert a.shape[1] == b.shape[0], "Incompatible A-B Dimensions"
+    selector = _selector_for(a, b, bias.dtype, enable_streamk)
+    if enable_streamk:
+        streamk_matmul_lt(a, b, out, selector, None, bias=bias, sk_grid=sk_grid, work_stealing=work_stealing)
+    else:
+        persistent_matmul_lt(a, b, out, selector, None, bias=bias, work_stealing=work_stealing)
+    return None
+
+
+def addmm(bias, a, b, out=None, enable_streamk=False, sk_grid=None, work_stealing=False):
+    """bias(N,) + A @ B, bias added in fp32 before the output cast."""
+    if out is None:
+        return _addmm(bias, a, b, enable_streamk, sk_grid, work_stealing)
+    if torch.is_grad_enabled() and (bias.requires_grad or a.requires_grad or b.requires_grad or out.requires_grad):
+        raise RuntimeError("tritonblas.addmm(): functions with out=... arguments don't support "
+                           "automatic differentiation, but one of the arguments requires grad.")
+    return _addmm_out(bias, a, b, out, enable_streamk, sk_grid, work_stealing)
