@@ -98,14 +98,16 @@ static CUtensorMapDataType tmap_dtype(int dtype) {
 
 // 2-D row-major view [outer][inner] with `outer_stride_bytes` between rows; box = box_inner x box_outer elements.
 int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer, uint64_t outer_stride_bytes,
-              uint32_t box_inner, uint32_t box_outer, bool swizzle128) {
+              uint32_t box_inner, uint32_t box_outer, int swizzle) {
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (outer_stride_bytes & 15) != 0) return TB_ERR_ALIGNMENT;
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {outer_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(map, tmap_dtype(dtype), 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                     : (swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE),
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cu_fail(static_cast<int>(r), "cuTensorMapEncodeTiled");
   return TB_OK;
@@ -234,6 +236,11 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
   p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
   p.status = dev->status;
   p.timeout_ns = 2000000000ull;
+  {
+    const char* dbg = getenv("TB_DEBUG_FLAGS");
+    p.debug_flags = dbg != nullptr ? atoi(dbg) : 0;
+    p.debug_out = (p.debug_flags & 2) ? reinterpret_cast<long long*>(a.workspace) : nullptr;
+  }
 
   // instruction descriptor: fp32 accumulate; operand formats; majors; N >> 3; M >> 4
   int kind;
@@ -283,11 +290,13 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
   CUtensorMap ta, tbm;
   const void* A = a.a;
   const void* B = a.b;
-  if (!a_mn) rc = encode_2d(&ta, a.a_dtype, A, a.k, a.m, static_cast<uint64_t>(a.a_stride_m) * es, bk, 128, true);
-  else rc = encode_2d(&ta, a.a_dtype, A, a.m, a.k, static_cast<uint64_t>(a.a_stride_k) * es, mn_atom, bk, true);
+  // swizzle: 1 = 128-byte rows of 16-byte chunks; 2 = 128-byte rows of 32-byte chunks (MN-major 32-bit operands)
+  const int mn_swz = es == 4 ? 2 : 1;
+  if (!a_mn) rc = encode_2d(&ta, a.a_dtype, A, a.k, a.m, static_cast<uint64_t>(a.a_stride_m) * es, bk, 128, 1);
+  else rc = encode_2d(&ta, a.a_dtype, A, a.m, a.k, static_cast<uint64_t>(a.a_stride_k) * es, mn_atom, bk, mn_swz);
   if (rc == TB_OK) {
-    if (!b_mn) rc = encode_2d(&tbm, a.b_dtype, B, a.k, a.n, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, true);
-    else rc = encode_2d(&tbm, a.b_dtype, B, a.n, a.k, static_cast<uint64_t>(a.b_stride_k) * es, mn_atom, bk, true);
+    if (!b_mn) rc = encode_2d(&tbm, a.b_dtype, B, a.k, a.n, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, 1);
+    else rc = encode_2d(&tbm, a.b_dtype, B, a.n, a.k, static_cast<uint64_t>(a.b_stride_k) * es, mn_atom, bk, mn_swz);
   }
   if (rc == TB_ERR_ALIGNMENT) return gemm_generic_loader(a, cfg, stream, dev->status);
   if (rc != TB_OK) return rc;

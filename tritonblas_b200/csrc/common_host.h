@@ -19,6 +19,6 @@ int* device_status_word(int device);
 
 // 2-D row-major tensor map [outer][inner]; box = box_inner x box_outer elements.
 int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer, uint64_t outer_stride_bytes,
-              uint32_t box_inner, uint32_t box_outer, bool swizzle128);
+              uint32_t box_inner, uint32_t box_outer, int swizzle);  // swizzle: 0 none, 1 128B, 2 128B with 32-byte chunks
 
 }  // namespace tb

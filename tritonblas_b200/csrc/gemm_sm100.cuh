@@ -58,6 +58,8 @@ struct GemmParams {
   // failure reporting
   int* status;
   unsigned long long timeout_ns;
+  long long* debug_out;  // bit 1 of debug_flags: per-CTA cycle counters of each role are written here
+  int debug_flags;  // measurement-only knobs (results are wrong when set): bit 0 = do not reload B on odd K blocks
 };
 
 struct WorkItem {
@@ -214,6 +216,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_slot + 1);
 
   WaitCtx wctx{abort_flag, p.status, p.timeout_ns};
+  const bool prof = (p.debug_flags & 2) != 0;  // measurement builds: per-role cycle counters
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -247,67 +250,81 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // The whole warp walks the schedule (warp-uniform control flow); one elected lane issues the copies.
+    {
       WorkIter wi(p, pid, nprog);
       int s = 0;
       uint32_t ph = 0;
       const int a_atom = kStageRowBytes / p.esize;  // elements per 128-byte row
       // In a pair, transaction bytes of both CTAs land on the even CTA's barrier, which expects the sum.
       const uint32_t expect = static_cast<uint32_t>(stage_bytes) * CTAS;
+      const int mn_box_bytes = p.k_per_stage * kStageRowBytes;
       bool ok = true;
+      long long prof_wait = 0, prof_t0 = clock64();
       for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
         int tm, tn;
         tile_coords(p, w.tile, tm, tn);
         const int m0 = tm * (kTileM * CTAS) + static_cast<int>(cta_rank) * kTileM;
         const int n0 = tn * p.block_n + static_cast<int>(cta_rank) * bn_local;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, wctx, TB_DEV_TIMEOUT_SMEM_EMPTY)) {
-            ok = false;
-            break;
-          }
+          const long long pw0 = prof ? clock64() : 0;
+          ok = mbar_wait_warp(&empty_bar[s], ph ^ 1, wctx, TB_DEV_TIMEOUT_SMEM_EMPTY);
+          if (!ok) break;
+          if (prof) prof_wait += clock64() - pw0;
           uint8_t* sa = ring + static_cast<size_t>(s) * stage_bytes;
           uint8_t* sb = sa + kATileBytes;
           const int k0 = kb * p.k_per_stage;
-          if constexpr (CTAS == 1) {
-            mbar_arrive_expect_tx(&full_bar[s], expect);
-            if (!p.a_mn) {
-              tma_load_2d(sa, &tmap_a, &full_bar[s], k0, m0);
+          const bool skip_b = (p.debug_flags & 1) && (kb & 1);
+          if (elect_one()) {
+            if constexpr (CTAS == 1) {
+              mbar_arrive_expect_tx(&full_bar[s], skip_b ? static_cast<uint32_t>(kATileBytes) : expect);
+              if (!p.a_mn) {
+                tma_load_2d(sa, &tmap_a, &full_bar[s], k0, m0);
+              } else {
+                for (int j = 0; j < kTileM / a_atom; ++j)
+                  tma_load_2d(sa + j * mn_box_bytes, &tmap_a, &full_bar[s], m0 + j * a_atom, k0);
+              }
+              if (skip_b) {
+              } else if (!p.b_mn) {
+                tma_load_2d(sb, &tmap_b, &full_bar[s], k0, n0);
+              } else {
+                for (int j = 0; j < bn_local / a_atom; ++j)
+                  tma_load_2d(sb + j * mn_box_bytes, &tmap_b, &full_bar[s], n0 + j * a_atom, k0);
+              }
             } else {
-              for (int j = 0; j < kTileM / a_atom; ++j)
-                tma_load_2d(sa + j * (p.k_per_stage * kStageRowBytes), &tmap_a, &full_bar[s], m0 + j * a_atom, k0);
-            }
-            if (!p.b_mn) {
-              tma_load_2d(sb, &tmap_b, &full_bar[s], k0, n0);
-            } else {
-              for (int j = 0; j < bn_local / a_atom; ++j)
-                tma_load_2d(sb + j * (p.k_per_stage * kStageRowBytes), &tmap_b, &full_bar[s], n0 + j * a_atom, k0);
-            }
-          } else {
-            const uint32_t bar = mapa_cluster(smem_u32(&full_bar[s]), 0);
-            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], expect);
-            if (!p.a_mn) {
-              tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
-            } else {
-              for (int j = 0; j < kTileM / a_atom; ++j)
-                tma_load_2d_pair(sa + j * (p.k_per_stage * kStageRowBytes), &tmap_a, bar, m0 + j * a_atom, k0);
-            }
-            if (!p.b_mn) {
-              tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
-            } else {
-              for (int j = 0; j < bn_local / a_atom; ++j)
-                tma_load_2d_pair(sb + j * (p.k_per_stage * kStageRowBytes), &tmap_b, bar, n0 + j * a_atom, k0);
+              const uint32_t bar = mapa_cluster(smem_u32(&full_bar[s]), 0);
+              if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], skip_b ? 2u * kATileBytes : expect);
+              if (!p.a_mn) {
+                tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
+              } else {
+                for (int j = 0; j < kTileM / a_atom; ++j)
+                  tma_load_2d_pair(sa + j * mn_box_bytes, &tmap_a, bar, m0 + j * a_atom, k0);
+              }
+              if (skip_b) {
+              } else if (!p.b_mn) {
+                tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
+              } else {
+                for (int j = 0; j < bn_local / a_atom; ++j)
+                  tma_load_2d_pair(sb + j * mn_box_bytes, &tmap_b, bar, n0 + j * a_atom, k0);
+              }
             }
           }
+          __syncwarp();
           if (++s == stages) {
             s = 0;
             ph ^= 1;
           }
         }
       }
+      if (prof && p.debug_out != nullptr && lane == 0) {
+        p.debug_out[blockIdx.x * 16 + 0] = prof_wait;
+        p.debug_out[blockIdx.x * 16 + 1] = clock64() - prof_t0;
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && cta_rank == 0) {
+    // Warp-uniform loop; one elected lane issues the MMAs and commits. In a pair only the even CTA issues.
+    if (cta_rank == 0) {
       WorkIter wi(p, pid, nprog);
       int s = 0;
       uint32_t ph = 0;
@@ -317,43 +334,66 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t mn_atom_stride = static_cast<uint32_t>(p.k_per_stage) * kStageRowBytes;
       const uint32_t a_lead = p.a_mn ? mn_atom_stride : 16u, b_lead = p.b_mn ? mn_atom_stride : 16u;
       // K advance per MMA (32 bytes of K): 32 bytes inside the swizzle row, or (32/esize) rows of 128 bytes.
-      const uint32_t a_kstep = p.a_mn ? (32u / p.esize) * kStageRowBytes : 32u;
-      const uint32_t b_kstep = p.b_mn ? (32u / p.esize) * kStageRowBytes : 32u;
+      const uint32_t a_kstep = (p.a_mn ? (32u / p.esize) * kStageRowBytes : 32u) >> 4;
+      const uint32_t b_kstep = (p.b_mn ? (32u / p.esize) * kStageRowBytes : 32u) >> 4;
+      // MN-major 32-bit operands use the 32-byte-chunk swizzle, whose pattern repeats every 4 rows (512 bytes).
+      const uint32_t a_type = (p.a_mn && p.esize == 4) ? 1u : 2u, b_type = (p.b_mn && p.esize == 4) ? 1u : 2u;
+      const uint32_t a_sbo = a_type == 1u ? 512u : 1024u, b_sbo = b_type == 1u ? 512u : 1024u;
+      const uint32_t ring_addr = smem_u32(ring);
+      // Descriptors of stage 0; a stage adds stage_bytes >> 4 to the start-address field.
+      const uint64_t adesc0 = make_smem_desc(ring_addr, a_lead, a_sbo, a_type);
+      const uint64_t bdesc0 = make_smem_desc(ring_addr + kATileBytes, b_lead, b_sbo, b_type);
+      const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
+      const uint32_t idesc = p.idesc;
       bool ok = true;
+      long long prof_full = 0, prof_tmem = 0, prof_issue = 0, prof_t0 = clock64();
       for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
-        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, wctx, TB_DEV_TIMEOUT_TMEM_EMPTY)) break;
+        const long long pt0 = prof ? clock64() : 0;
+        ok = mbar_wait_warp(&tmem_empty[acc], acc_ph ^ 1, wctx, TB_DEV_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        if (prof) prof_tmem += clock64() - pt0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * acc_stride);
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (!mbar_wait(&full_bar[s], ph, wctx, TB_DEV_TIMEOUT_SMEM_FULL)) {
-            ok = false;
-            break;
+          const long long pf0 = prof ? clock64() : 0;
+          ok = mbar_wait_warp(&full_bar[s], ph, wctx, TB_DEV_TIMEOUT_SMEM_FULL);
+          if (!ok) break;
+          const long long pf1 = prof ? clock64() : 0;
+          prof_full += pf1 - pf0;
+          const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * stage_step);
+          const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * stage_step);
+          const uint32_t first = (kb > w.kb0) ? 1u : 0u;
+          if (elect_one()) {
+            umma<KIND, CTAS>(d_tmem, adesc, bdesc, idesc, first);
+            umma<KIND, CTAS>(d_tmem, adesc + a_kstep, bdesc + b_kstep, idesc, 1u);
+            umma<KIND, CTAS>(d_tmem, adesc + 2 * a_kstep, bdesc + 2 * b_kstep, idesc, 1u);
+            umma<KIND, CTAS>(d_tmem, adesc + 3 * a_kstep, bdesc + 3 * b_kstep, idesc, 1u);
+            // Free the stage once these MMAs have read it.
+            if constexpr (CTAS == 1) umma_commit(&empty_bar[s]);
+            else umma_commit_pair(&empty_bar[s], 3);
+            if (kb + 1 == w.kb1) {
+              if constexpr (CTAS == 1) umma_commit(&tmem_full[acc]);
+              else umma_commit_pair(&tmem_full[acc], 3);
+            }
           }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(ring + static_cast<size_t>(s) * stage_bytes);
-          const uint32_t sb = sa + kATileBytes;
-          const uint64_t adesc = make_smem_desc(sa, a_lead, 1024);
-          const uint64_t bdesc = make_smem_desc(sb, b_lead, 1024);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            umma<KIND, CTAS>(d_tmem, adesc + ((k * a_kstep) >> 4), bdesc + ((k * b_kstep) >> 4), p.idesc,
-                             (kb > w.kb0 || k > 0) ? 1u : 0u);
-          }
-          // Free the stage once these MMAs have read it.
-          if constexpr (CTAS == 1) umma_commit(&empty_bar[s]);
-          else umma_commit_pair(&empty_bar[s], 3);
+          __syncwarp();
+          if (prof) prof_issue += clock64() - pf1;
           if (++s == stages) {
             s = 0;
             ph ^= 1;
           }
         }
         if (!ok) break;
-        if constexpr (CTAS == 1) umma_commit(&tmem_full[acc]);
-        else umma_commit_pair(&tmem_full[acc], 3);
         if (++acc == 2) {
           acc = 0;
           acc_ph ^= 1;
         }
+      }
+      if (prof && p.debug_out != nullptr && lane == 0) {
+        p.debug_out[blockIdx.x * 16 + 2] = prof_full;
+        p.debug_out[blockIdx.x * 16 + 3] = prof_tmem;
+        p.debug_out[blockIdx.x * 16 + 4] = prof_issue;
+        p.debug_out[blockIdx.x * 16 + 5] = clock64() - prof_t0;
       }
     }
   } else {
@@ -367,17 +407,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const size_t slot_elems = static_cast<size_t>(p.block_n) * kTileM;
     const uint32_t tmem_empty_remote = (CTAS == 2) ? mapa_cluster(smem_u32(&tmem_empty[0]), 0) : 0u;
     bool ok = true;
+    long long prof_wait = 0, prof_t0 = clock64();
     for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
       int tm, tn;
       tile_coords(p, w.tile, tm, tn);
       const int m0 = tm * (kTileM * CTAS) + static_cast<int>(cta_rank) * kTileM;
       const int n0 = tn * p.block_n;
+      const long long pe0 = prof ? clock64() : 0;
       const int row = m0 + row_in_tile;
       const bool owner = (w.kb0 == 0);
       const bool complete = owner && (w.kb1 == p.num_k_blocks);
       // Every decision to unwind is made warp-uniform: the TMEM loads below need the whole warp.
       ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_ph, wctx, TB_DEV_TIMEOUT_TMEM_FULL));
       if (!ok) break;
+      if (prof) prof_wait += clock64() - pe0;
       tc_fence_after();
 
       // Peers that hold the rest of this tile's K range: programs after this one whose slice starts inside the tile.
@@ -457,6 +500,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         acc = 0;
         acc_ph ^= 1;
       }
+    }
+    if ((p.debug_flags & 2) && p.debug_out != nullptr && threadIdx.x == 64) {
+      p.debug_out[blockIdx.x * 16 + 6] = prof_wait;
+      p.debug_out[blockIdx.x * 16 + 7] = clock64() - prof_t0;
     }
   }
 

@@ -103,6 +103,32 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   }
 }
 
+// One lane of a converged warp (all 32 lanes must call this together).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// Warp-collective bounded wait: every lane of a converged warp calls it and every lane gets the same answer, so the
+// caller's control flow stays warp-uniform (which lets the compiler keep descriptors in uniform registers).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const WaitCtx& w, int code) {
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, w, code);
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  // The phase cannot advance again before this warp acts, so each lane's own acquiring test succeeds at once.
+  if (ok) {
+    for (int i = 0; i < 1024 && !mbar_try_wait(bar, parity); ++i) {
+    }
+  }
+  return ok;
+}
+
 // Bounded wait until *flag == want (acquire at gpu scope). Used for stream-K partial-tile hand-off.
 __device__ __forceinline__ bool flag_wait(const unsigned* flag, unsigned want, const WaitCtx& w, int code) {
   unsigned v;
@@ -280,13 +306,16 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // Shared-memory matrix descriptor for a 128-byte-swizzled operand tile whose base is 1024-byte aligned.
 //   K-major : rows of 128 bytes (one row per M/N index), 8-row groups 1024 bytes apart (stride_bytes = 1024).
 //   MN-major: 64x8-element-class atoms; lead_bytes = distance between atoms along M/N, stride_bytes = between 8-row K groups.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lead_bytes, uint32_t stride_bytes) {
+//   layout_type: 2 = 128-byte swizzle of 16-byte chunks (8-row pattern); 1 = 128-byte swizzle of 32-byte chunks
+//   (4-row pattern), the only swizzled form the tensor core accepts for MN-major 32-bit operands.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lead_bytes, uint32_t stride_bytes,
+                                                   uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
   d |= static_cast<uint64_t>((lead_bytes >> 4) & 0x3FFF) << 16;
   d |= static_cast<uint64_t>((stride_bytes >> 4) & 0x3FFF) << 32;
   d |= 1ull << 46;  // descriptor version for this architecture
-  d |= 2ull << 61;  // 128-byte swizzle
+  d |= static_cast<uint64_t>(layout_type) << 61;
   return d;
 }
 // Descriptor for unswizzled 8x16-byte core matrices (used for scale-factor copies into TMEM).

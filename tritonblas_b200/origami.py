@@ -119,6 +119,15 @@ class OrigamiMatmulSelector:
                     raise AttributeError(name)
                 setattr(cfg, name, int(value))
             cfg.block_m = 128 * (2 if cfg.cta_pair == 2 else 1)
+            if "cta_pair" in fields or "block_n" in fields:
+                # grids follow the tile shape unless they are forced as well
+                pair = 2 if cfg.cta_pair == 2 else 1
+                programs = max(cfg.num_sms // pair, 1)
+                tiles = -(-self._m // cfg.block_m) * -(-self._n // cfg.block_n)
+                if "grid" not in fields:
+                    cfg.grid = min(programs, tiles)
+                if "sk_grid" not in fields:
+                    cfg.sk_grid = min(programs, tiles * -(-self._k // cfg.block_k))
         return self
 
     def hierarchical_split(self, num_xcds):
