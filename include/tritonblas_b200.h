@@ -104,6 +104,14 @@ int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override);
 /* Enqueue one GEMM. `cfg` may be NULL (the library selects). */
 int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);
 
+/* MXFP4 block quantiser: x (rows, k) in f16/bf16/f32 with `x_row_stride` elements between rows, k % 32 == 0, to packed
+ * e2m1 codes (rows, k/2) and e8m0 scale bytes (rows, k/32), both row-major with the given row strides in bytes.
+ * hadamard = 0 replaces dynamic_mxfp4_quant / _dynamic_mxfp4_quant_kernel (include/tritonblas/utils.py:646-789) bit for
+ * bit. hadamard = 1 first rotates every 32-element block by the Sylvester Hadamard matrix / sqrt(32) (fp32 butterflies,
+ * strides 1,2,4,8,16, then one multiply); the reference has no such kernel. */
+int tb_mxfp4_quant(const void* x, int32_t x_dtype, int64_t rows, int64_t k, int64_t x_row_stride, void* codes,
+                   int64_t codes_row_stride, void* scales, int64_t scales_row_stride, int32_t hadamard, void* stream);
+
 /* Reads (synchronously: waits for the device) and clears the per-device status word that kernels set when a bounded
  * wait gives up. 0 = no failure since the last call. No reference counterpart (its waits are unbounded,
  * kernels/streamk_gemm.py:295-300). */

@@ -15,8 +15,8 @@ def pytest_configure(config):
 @pytest.fixture(scope="session", autouse=True)
 def _library_built():
     """The C-ABI library must exist before any test imports the package (there is no fallback to test instead)."""
-    from tritonblas_b200.csrc import build
-    build.build()
+    import __graft_entry__
+    __graft_entry__.build()
 
 
 @pytest.fixture()

@@ -55,7 +55,7 @@ class GemmArgs(ctypes.Structure):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
-            f"{LIB_PATH} is missing: build it with `python -m tritonblas_b200.csrc.build` "
+            f"{LIB_PATH} is missing: build it with `python tritonblas_b200/csrc/build.py` "
             "(nvcc, sm_100a). tritonblas_b200 has no CPU or PyTorch fallback path.")
     lib = ctypes.CDLL(LIB_PATH)
     lib.tb_select.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(Config)]
@@ -64,6 +64,10 @@ def _load():
     lib.tb_gemm_workspace_bytes.restype = ctypes.c_int64
     lib.tb_gemm.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p]
     lib.tb_gemm.restype = ctypes.c_int
+    lib.tb_mxfp4_quant.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                   ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
+                                   ctypes.c_void_p]
+    lib.tb_mxfp4_quant.restype = ctypes.c_int
     lib.tb_device_status.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)]
     lib.tb_device_status.restype = ctypes.c_int
     lib.tb_device_info.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]

@@ -1,6 +1,7 @@
 """Builds libtritonblas_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-Usage: python -m tritonblas_b200.csrc.build [--force] [--verbose]
+Usage: python tritonblas_b200/csrc/build.py [--force] [--verbose]   (run as a script: importing it through the
+package would first try to load the library it builds)
 """
 import os
 import subprocess
@@ -9,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB = os.path.join(PKG, "libtritonblas_b200.so")
-SOURCES = ["api.cu", "simt_gemm.cu", "selector.cpp"]
+SOURCES = ["api.cu", "simt_gemm.cu", "quant_mxfp4.cu", "selector.cpp"]
 HEADERS_DIRS = [HERE, os.path.join(os.path.dirname(PKG), "include")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

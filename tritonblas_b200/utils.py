@@ -1,0 +1,208 @@
+"""Input generation, quantisers and decoders with the names the reference exposes in include/tritonblas/utils.py.
+
+The MXFP4 quantisers run hand-written CUDA kernels through the C ABI; the per-channel FP8/INT8 quantiser and the
+decoders are torch-op fixtures, as they are in the reference.
+"""
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Tuple, Union
+
+import torch
+
+from . import _lib
+
+_STR2DTYPE = {"fp16": torch.float16, "float16": torch.float16, "bf16": torch.bfloat16, "bfloat16": torch.bfloat16,
+              "fp32": torch.float32, "float32": torch.float32, "fp8": torch.float8_e4m3fn,
+              "fp8e4m3": torch.float8_e4m3fn, "float8_e4m3fn": torch.float8_e4m3fn, "fp8e5m2": torch.float8_e5m2,
+              "float8_e5m2": torch.float8_e5m2, "int8": torch.int8, "uint8": torch.uint8}
+
+
+def _ensure_dtype(dt):
+    if isinstance(dt, torch.dtype):
+        return dt
+    key = str(dt).lower().replace("torch.", "")
+    if key not in _STR2DTYPE:
+        raise ValueError(f"Unsupported dtype: {dt}")
+    return _STR2DTYPE[key]
+
+
+def _is_float8_like(dt):
+    return dt in (torch.float8_e4m3fn, torch.float8_e5m2)
+
+
+def _is_int8(dt):
+    return dt == torch.int8
+
+
+@dataclass
+class MatmulInputs:
+    """What generate_matmul_inputs returns (reference: utils.py:200-262)."""
+    A: torch.Tensor
+    B: torch.Tensor
+    C: torch.Tensor
+    bias: torch.Tensor
+    scaleA: Optional[torch.Tensor] = None
+    scaleB: Optional[torch.Tensor] = None
+
+    @property
+    def is_quantized(self):
+        return self.scaleA is not None and self.scaleB is not None
+
+    @property
+    def is_fp4(self):
+        return self.is_quantized and self.scaleA.ndim == 2 and self.scaleB.ndim == 2
+
+
+def matmul_input_gen(size, dtype, init_type, *, quantize=None, min_scale=1e-8, device="cuda"):
+    """A tensor of `size` initialised by `init_type` ("randn", "hpl", "trig_float", "zeros"); with `quantize` it is
+    scaled per row to FP8/INT8 and (q, scale[(M, 1)]) is returned (reference: utils.py:264-337)."""
+    dtype = _ensure_dtype(dtype)
+    M, N = size
+    if init_type == "hpl":
+        base = torch.empty(size, device=device, dtype=torch.float32).uniform_(-0.5, 0.5)
+    elif init_type == "trig_float":
+        base = torch.arange(0, M * N, device=device, dtype=torch.float32).reshape(M, N).sin()
+    elif init_type == "zeros":
+        base = torch.zeros(size, dtype=torch.float32, device=device)
+    elif init_type == "randn":
+        base = torch.randn(size, dtype=torch.float32, device=device)
+    else:
+        raise ValueError(f"Unsupported init_type: {init_type}")
+    mode = quantize
+    if mode == "auto":
+        mode = "fp8" if _is_float8_like(dtype) else "int8" if _is_int8(dtype) else None
+    if mode is None:
+        return base.to(dtype)
+    amax = base.abs().amax(dim=1, keepdim=True).clamp(min=min_scale)
+    if mode == "fp8":
+        scale = amax / torch.finfo(dtype).max
+        return (base / scale).to(dtype), scale.to(torch.float32)
+    if mode == "int8":
+        scale = amax / 127.0
+        return torch.round(base / scale).clamp_(-127.0, 127.0).to(torch.int8), scale.to(torch.float32)
+    raise ValueError(f"Unsupported quantize mode: {mode}")
+
+
+def quantize_tensor_per_channel(tensor, target_dtype, axis, *, min_scale=1e-8):
+    """Symmetric per-channel quantisation along `axis`: scale = clamp(amax, min_scale) / dtype_max,
+    q = (x * (1/scale)).to(dtype); returns (q, scale squeezed to 1-D fp32) (reference: utils.py:340-377)."""
+    dtype = _ensure_dtype(target_dtype)
+    if not (_is_float8_like(dtype) or _is_int8(dtype)):
+        raise ValueError(f"Unsupported quantized dtype: {dtype}")
+    base = tensor.to(torch.float32)
+    amax = base.abs().amax(dim=axis, keepdim=True).clamp(min=min_scale)
+    qmax = torch.finfo(dtype).max if _is_float8_like(dtype) else 127.0
+    scale = amax / qmax
+    q = base * (1.0 / scale)
+    if _is_int8(dtype):
+        q = torch.round(q).clamp_(-qmax, qmax)
+    return q.to(dtype), scale.squeeze(axis).to(torch.float32)
+
+
+def _mxfp4_quant(x, hadamard):
+    assert x.ndim == 2, "Input must be 2D tensor"
+    M, N = x.shape
+    assert N % 32 == 0, f"N ({N}) must be divisible by 32"
+    if not x.is_cuda:
+        raise RuntimeError("the MXFP4 quantiser runs on CUDA tensors only (no CPU path)")
+    if x.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise ValueError(f"Unsupported input dtype: {x.dtype}")
+    es = x.element_size()
+    if x.stride(1) != 1 or (x.stride(0) * es) % 16 != 0 or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    codes = torch.empty((M, N // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((M, N // 32), dtype=torch.uint8, device=x.device)
+    if M == 0 or N == 0:
+        return codes, scales
+    with torch.cuda.device(x.device):
+        rc = _lib.lib.tb_mxfp4_quant(ctypes.c_void_p(x.data_ptr()), _lib.DTYPE_CODE[x.dtype], M, N, x.stride(0),
+                                     ctypes.c_void_p(codes.data_ptr()), codes.stride(0),
+                                     ctypes.c_void_p(scales.data_ptr()), scales.stride(0), int(hadamard),
+                                     _lib.current_stream_ptr(x.device))
+    _lib.check(rc, "tb_mxfp4_quant")
+    return codes, scales
+
+
+def dynamic_mxfp4_quant(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """x (M, N) -> packed e2m1 codes (M, N/2) uint8 and e8m0 scales (M, N/32) uint8, one scale per 32 contiguous
+    elements; bit-identical to the reference quantiser (utils.py:742-789)."""
+    return _mxfp4_quant(x, False)
+
+
+def hadamard_mxfp4_quant(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Fused activation transform: rotate every 32-element block by H32/sqrt(32), then quantise to MXFP4.
+    Apply it to both operands' K blocks: (A H)(B H)^T = A B^T because H is orthonormal and symmetric."""
+    return _mxfp4_quant(x, True)
+
+
+_E2M1_TABLE = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
+
+
+def mxfp4_to_f32(x: torch.Tensor) -> torch.Tensor:
+    """Unpack e2m1 pairs (low nibble first) to fp32 (reference: utils.py:547-607)."""
+    if hasattr(torch, "float4_e2m1fn_x2") and x.dtype == torch.float4_e2m1fn_x2:
+        x = x.view(torch.uint8)
+    lut = torch.tensor(_E2M1_TABLE, dtype=torch.float32, device=x.device)
+    lo = lut[(x & 0xF).long()]
+    hi = lut[(x >> 4).long()]
+    return torch.stack((lo, hi), dim=-1).reshape(*x.shape[:-1], x.shape[-1] * 2)
+
+
+def e8m0_to_f32(scale_e8m0: torch.Tensor) -> torch.Tensor:
+    """Exponent bytes to fp32 2^(s-127); 0 decodes to the bit pattern 0x00400000, 255 to NaN
+    (reference: utils.py:610-643)."""
+    s = scale_e8m0.view(torch.uint8)
+    bits = s.to(torch.int32) << 23
+    bits = torch.where(s == 0, torch.full_like(bits, 0x00400000), bits)
+    bits = torch.where(s == 0xFF, torch.full_like(bits, 0x7F800001), bits)
+    return bits.view(torch.float32)
+
+
+def generate_matmul_inputs(m, n, k, in_dtype=None, out_dtype=torch.float16, transA="T", transB="T", init_type="randn",
+                           *, device="cuda", quantize_mode="auto", dtype_a=None, dtype_b=None, seed=None) -> MatmulInputs:
+    """A (m, k), B (k, n), C (m, n), bias (m,) and, for fp8/int8/"fp4" inputs, their scales (reference:
+    utils.py:390-538). "T" keeps the matrix as generated; "N" generates the transposed shape and passes a .T view.
+    A is seeded with `seed`, B with `seed + 10000`."""
+    dtype_a = in_dtype if dtype_a is None else dtype_a
+    dtype_b = in_dtype if dtype_b is None else dtype_b
+    if dtype_a is None or dtype_b is None:
+        raise ValueError("Either in_dtype or dtype_a/dtype_b must be provided")
+    fp4_a = isinstance(dtype_a, str) and dtype_a.lower() == "fp4"
+    fp4_b = isinstance(dtype_b, str) and dtype_b.lower() == "fp4"
+    dtype_a = torch.uint8 if fp4_a else _ensure_dtype(dtype_a)
+    dtype_b = torch.uint8 if fp4_b else _ensure_dtype(dtype_b)
+    out_dtype = _ensure_dtype(out_dtype)
+    if transA not in ("T", "N") or transB not in ("T", "N"):
+        raise ValueError("transA/transB must be 'T' or 'N'")
+
+    def init(shape, s):
+        if s is not None:
+            torch.manual_seed(s)
+            if str(device).startswith("cuda"):
+                torch.cuda.manual_seed(s)
+        return matmul_input_gen(shape, torch.float32, init_type, device=device)
+
+    A = init((m, k), seed) if transA == "T" else init((k, m), seed).T
+    b_seed = seed + 10000 if seed is not None else None
+    B = init((k, n), b_seed) if transB == "T" else init((n, k), b_seed).T
+    scaleA = scaleB = None
+    if fp4_a or fp4_b:
+        if k % 32 != 0:
+            raise ValueError(f"For FP4 quantization, K must be divisible by 32, got K={k}")
+        A, scaleA = dynamic_mxfp4_quant(A.contiguous())            # (m, k/2), (m, k/32)
+        Bq, scaleB = dynamic_mxfp4_quant(B.T.contiguous())          # (n, k/2), (n, k/32)
+        B = Bq.T                                                     # (k/2, n) view, K contiguous
+    else:
+        quant_a = quantize_mode in ("fp8", "int8") or (quantize_mode == "auto" and (_is_float8_like(dtype_a) or _is_int8(dtype_a)))
+        quant_b = quantize_mode in ("fp8", "int8") or (quantize_mode == "auto" and (_is_float8_like(dtype_b) or _is_int8(dtype_b)))
+        if quant_a:
+            A, scaleA = quantize_tensor_per_channel(A, dtype_a, axis=1)
+        else:
+            A = A.to(dtype_a)
+        if quant_b:
+            B, scaleB = quantize_tensor_per_channel(B, dtype_b, axis=0)
+        else:
+            B = B.to(dtype_b)
+    C = torch.zeros((m, n), device=device, dtype=out_dtype)
+    bias = torch.zeros((m,), device=device, dtype=out_dtype)
+    return MatmulInputs(A=A, B=B, C=C, bias=bias, scaleA=scaleA, scaleB=scaleB)
