@@ -104,6 +104,24 @@ int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override);
 /* Enqueue one GEMM. `cfg` may be NULL (the library selects). */
 int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);
 
+/* MXFP4 GEMM: C (m, n) = sum over 32-element K blocks of (A_e2m1 * 2^(sa-127)) . (B_e2m1 * 2^(sb-127)), fp32
+ * accumulate, one cast. A is (m, k/2) bytes and B is (n, k/2) bytes, two e2m1 codes per byte (even element in the low
+ * nibble), K contiguous, row strides in bytes (multiples of 16). Scales are e8m0 bytes, row-major (m, k/32) and
+ * (n, k/32). Runs on the block-scaled tensor-core instruction. Replaces matmul_fp4 + the fp4_matmul kernel
+ * (include/tritonblas/matmul.py:519-625, kernels/fp4_matmul.py:8-130). */
+typedef struct tb_mxfp4_args {
+  int32_t m, n, k;           /* k = number of 4-bit elements, a multiple of 32 */
+  const void* a; int64_t a_row_stride;
+  const void* b; int64_t b_row_stride;
+  void* c; int64_t c_stride_m, c_stride_n; int32_t c_dtype;
+  const void* a_scales; int64_t a_scales_row_stride;
+  const void* b_scales; int64_t b_scales_row_stride;
+  int32_t block_n;           /* 0 = library's choice; else a multiple of 32, at most 224 */
+  int32_t cta_pair;          /* 0 = library's choice; 1 or 2 */
+  int32_t group_m;           /* 0 = library's choice */
+} tb_mxfp4_args;
+int tb_gemm_mxfp4(const tb_mxfp4_args* args, void* stream);
+
 /* MXFP4 block quantiser: x (rows, k) in f16/bf16/f32 with `x_row_stride` elements between rows, k % 32 == 0, to packed
  * e2m1 codes (rows, k/2) and e8m0 scale bytes (rows, k/32), both row-major with the given row strides in bytes.
  * hadamard = 0 replaces dynamic_mxfp4_quant / _dynamic_mxfp4_quant_kernel (include/tritonblas/utils.py:646-789) bit for

@@ -52,6 +52,18 @@ class GemmArgs(ctypes.Structure):
     ]
 
 
+class Mxfp4Args(ctypes.Structure):
+    _fields_ = [
+        ("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32),
+        ("a", ctypes.c_void_p), ("a_row_stride", ctypes.c_int64),
+        ("b", ctypes.c_void_p), ("b_row_stride", ctypes.c_int64),
+        ("c", ctypes.c_void_p), ("c_stride_m", ctypes.c_int64), ("c_stride_n", ctypes.c_int64), ("c_dtype", ctypes.c_int32),
+        ("a_scales", ctypes.c_void_p), ("a_scales_row_stride", ctypes.c_int64),
+        ("b_scales", ctypes.c_void_p), ("b_scales_row_stride", ctypes.c_int64),
+        ("block_n", ctypes.c_int32), ("cta_pair", ctypes.c_int32), ("group_m", ctypes.c_int32),
+    ]
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
@@ -64,6 +76,8 @@ def _load():
     lib.tb_gemm_workspace_bytes.restype = ctypes.c_int64
     lib.tb_gemm.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p]
     lib.tb_gemm.restype = ctypes.c_int
+    lib.tb_gemm_mxfp4.argtypes = [ctypes.POINTER(Mxfp4Args), ctypes.c_void_p]
+    lib.tb_gemm_mxfp4.restype = ctypes.c_int
     lib.tb_mxfp4_quant.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                    ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
                                    ctypes.c_void_p]

@@ -144,7 +144,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const Gemm
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(static_cast<unsigned>(programs * CTAS), 1, 1);
-  lc.blockDim = dim3(kGemmThreads, 1, 1);
+  lc.blockDim = dim3(gemm_threads<KIND>(), 1, 1);
   lc.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   lc.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -314,6 +314,77 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
 #undef TB_LAUNCH
 }
 
+// ---------------------------------------------------------------- MXFP4 (block-scaled e2m1 x e2m1)
+static int gemm_mxfp4_impl(const tb_mxfp4_args& a, cudaStream_t stream) {
+  if (a.m < 0 || a.n < 0 || a.k < 0 || (a.k % 32) != 0) return TB_ERR_INVALID;
+  if (a.m == 0 || a.n == 0) return TB_OK;
+  if (a.k == 0) return TB_ERR_UNSUPPORTED;
+  if (a.a == nullptr || a.b == nullptr || a.c == nullptr || a.a_scales == nullptr || a.b_scales == nullptr) return TB_ERR_INVALID;
+  if (a.c_dtype != TB_DTYPE_F16 && a.c_dtype != TB_DTYPE_BF16 && a.c_dtype != TB_DTYPE_F32) return TB_ERR_UNSUPPORTED;
+  DeviceState* dev = nullptr;
+  int device = 0;
+  int rc = current_device_state(&dev, &device);
+  if (rc != TB_OK) return rc;
+
+  tb_config cfg;
+  tb_problem pr = {};
+  pr.m = a.m; pr.n = a.n; pr.k = a.k;
+  pr.a_dtype = pr.b_dtype = TB_DTYPE_F4; pr.c_dtype = a.c_dtype;
+  pr.mx_block_size = 32;
+  pr.device = device;
+  rc = select_config(pr, machine_for(dev), &cfg);
+  if (rc != TB_OK) return rc;
+  if (a.block_n > 0) cfg.block_n = a.block_n;
+  if (a.cta_pair > 0) cfg.cta_pair = a.cta_pair;
+  if (a.group_m > 0) cfg.group_m = a.group_m;
+  const int pair = cfg.cta_pair == 2 ? 2 : 1;
+  const int bn = cfg.block_n;
+  const int groups = (bn + 127) / 128;
+  if (bn < 32 || (bn % 32) != 0 || ((bn / pair) % 16) != 0 || 2 * bn + 8 + 8 * groups > 512) return TB_ERR_INVALID;
+  const int kbytes = a.k / 2;
+  const int stage_bytes = (128 * 128 + (bn / pair) * 128 + (2 + 2 * groups) * 512 + 1023) & ~1023;
+  int stages = (dev->smem_optin - 2048) / stage_bytes;
+  if (stages > 8) stages = 8;
+  if (stages < 2) return TB_ERR_INVALID;
+  const int smem_bytes = stages * stage_bytes + (2 * stages + 8) * 8 + 64 + 1024;
+
+  GemmParams p = {};
+  p.M = a.m; p.N = a.n; p.K = a.k;
+  p.block_n = bn;
+  p.k_per_stage = 128;  // bytes of packed K per stage (256 elements)
+  p.num_k_blocks = (kbytes + 127) / 128;
+  p.tiles_m = (a.m + 128 * pair - 1) / (128 * pair);
+  p.tiles_n = (a.n + bn - 1) / bn;
+  p.group_m = cfg.group_m > 0 ? cfg.group_m : 8;
+  p.stages = stages;
+  p.esize = 1;
+  p.a_mn = 0; p.b_mn = 0;
+  int tc = 32;
+  while (tc < 2 * bn + 8 + 8 * groups) tc <<= 1;
+  p.tmem_cols = static_cast<uint32_t>(tc);
+  p.C = a.c; p.ldc_m = a.c_stride_m; p.ldc_n = a.c_stride_n; p.c_dtype = a.c_dtype;
+  p.sfa = static_cast<const unsigned char*>(a.a_scales); p.sfa_stride = a.a_scales_row_stride;
+  p.sfb = static_cast<const unsigned char*>(a.b_scales); p.sfb_stride = a.b_scales_row_stride;
+  p.status = dev->status;
+  p.timeout_ns = 2000000000ull;
+  // e2m1 operands (format 1), ue8m0 scales (bit 23), K-major, N >> 3, M >> 4; scale-factor ids are set per MMA
+  p.idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) | (1u << 23) |
+            (static_cast<uint32_t>((128 * pair) >> 4) << 24);
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  int programs = dev->num_sms / pair;
+  if (programs > tiles) programs = static_cast<int>(tiles);
+  if (programs < 1) programs = 1;
+  p.dp_tiles = static_cast<int>(tiles);
+  p.sk_tiles = 0;
+
+  CUtensorMap ta, tbm;
+  rc = encode_2d(&ta, TB_DTYPE_U8, a.a, kbytes, a.m, static_cast<uint64_t>(a.a_row_stride), 128, 128, 1);
+  if (rc == TB_OK) rc = encode_2d(&tbm, TB_DTYPE_U8, a.b, kbytes, a.n, static_cast<uint64_t>(a.b_row_stride), 128, bn / pair, 1);
+  if (rc != TB_OK) return rc;
+  if (pair == 1) return launch_gemm<3, 1>(ta, tbm, p, programs, smem_bytes, stream);
+  return launch_gemm<3, 2>(ta, tbm, p, programs, smem_bytes, stream);
+}
+
 }  // namespace tb
 
 // ====================================================================== exported C ABI
@@ -338,6 +409,11 @@ int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override) 
 int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream) {
   if (args == nullptr) return TB_ERR_INVALID;
   return tb::gemm_impl(*args, cfg, static_cast<cudaStream_t>(stream));
+}
+
+int tb_gemm_mxfp4(const tb_mxfp4_args* args, void* stream) {
+  if (args == nullptr) return TB_ERR_INVALID;
+  return tb::gemm_mxfp4_impl(*args, static_cast<cudaStream_t>(stream));
 }
 
 int tb_device_status(int32_t device, int32_t* status_out) {

@@ -24,7 +24,11 @@ namespace tb {
 
 constexpr int kTileM = 128;          // accumulator rows per CTA (TMEM lanes)
 constexpr int kStageRowBytes = 128;  // one swizzle row: K extent of a stage in bytes for K-major operands
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 192;      // producer + MMA + 4 epilogue warps
+constexpr int kGemmThreadsMx = 224;    // block-scaled kinds add one warp that stages the scale factors
+constexpr int kSfAtomBytes = 512;      // scale factors of 128 rows x 4 K blocks, laid out [32 rows][4 row quads][4 blocks]
+template <int KIND>
+constexpr int gemm_threads() { return KIND == 3 ? kGemmThreadsMx : kGemmThreads; }
 constexpr int kATileBytes = kTileM * kStageRowBytes;  // 16 KB
 
 enum : int { TB_F16 = 0, TB_BF16 = 1, TB_F32 = 2, TB_E4M3 = 3, TB_E5M2 = 4, TB_U8 = 5 };
@@ -58,6 +62,11 @@ struct GemmParams {
   // failure reporting
   int* status;
   unsigned long long timeout_ns;
+  // block-scaled (MXFP4) operands: e8m0 scale bytes, row-major (rows, K/32) with a row stride in bytes
+  const unsigned char* sfa;
+  long long sfa_stride;
+  const unsigned char* sfb;
+  long long sfb_stride;
   long long* debug_out;  // bit 1 of debug_flags: per-CTA cycle counters of each role are written here
   int debug_flags;  // measurement-only knobs (results are wrong when set): bit 0 = do not reload B on odd K blocks
 };
@@ -187,8 +196,23 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, in
   }
 }
 
+// Eight consecutive scale bytes of one row (K blocks kb8*8 .. kb8*8+7); 127 (= 1.0) where the row or block is outside.
+__device__ __forceinline__ uint2 load_scales8(const unsigned char* base, long long stride, int row, int rows, int kb8,
+                                              int kblocks, bool vec_ok) {
+  if (row >= rows) return make_uint2(0x7F7F7F7Fu, 0x7F7F7F7Fu);
+  const unsigned char* p = base + row * stride + static_cast<long long>(kb8) * 8;
+  if (vec_ok && kb8 * 8 + 8 <= kblocks) return __ldg(reinterpret_cast<const uint2*>(p));
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t b = (kb8 * 8 + j < kblocks) ? static_cast<uint32_t>(__ldg(p + j)) : 0x7Fu;
+    w[j >> 2] |= b << ((j & 3) * 8);
+  }
+  return make_uint2(w[0], w[1]);
+}
+
 template <int KIND, int CTAS>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads<KIND>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is what the 128-byte swizzle pattern and the matrix descriptors assume.
@@ -202,7 +226,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int bn_local = p.block_n / CTAS;  // B rows this CTA stages
   const int b_tile_bytes = bn_local * kStageRowBytes;
-  const int stage_bytes = kATileBytes + b_tile_bytes;
+  // Block-scaled kinds append the stage's scale factors: A rows of this CTA (2 atoms), then all B rows of the tile
+  // (2 atoms per group of 128 rows).
+  const int sf_groups_b = (p.block_n + 127) / 128;
+  const int sf_bytes = (KIND == 3) ? (2 + 2 * sf_groups_b) * kSfAtomBytes : 0;
+  const int stage_bytes = (kATileBytes + b_tile_bytes + sf_bytes + 1023) & ~1023;
   const int stages = p.stages;
 
   uint8_t* ring = smem;
@@ -221,7 +249,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], KIND == 3 ? 1 + CTAS : 1);  // + one arrival per scale-staging warp
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -257,7 +285,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t ph = 0;
       const int a_atom = kStageRowBytes / p.esize;  // elements per 128-byte row
       // In a pair, transaction bytes of both CTAs land on the even CTA's barrier, which expects the sum.
-      const uint32_t expect = static_cast<uint32_t>(stage_bytes) * CTAS;
+      const uint32_t expect = static_cast<uint32_t>(kATileBytes + b_tile_bytes) * CTAS;
       const int mn_box_bytes = p.k_per_stage * kStageRowBytes;
       bool ok = true;
       long long prof_wait = 0, prof_t0 = clock64();
@@ -364,10 +392,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * stage_step);
           const uint32_t first = (kb > w.kb0) ? 1u : 0u;
           if (elect_one()) {
-            umma<KIND, CTAS>(d_tmem, adesc, bdesc, idesc, first);
-            umma<KIND, CTAS>(d_tmem, adesc + a_kstep, bdesc + b_kstep, idesc, 1u);
-            umma<KIND, CTAS>(d_tmem, adesc + 2 * a_kstep, bdesc + 2 * b_kstep, idesc, 1u);
-            umma<KIND, CTAS>(d_tmem, adesc + 3 * a_kstep, bdesc + 3 * b_kstep, idesc, 1u);
+            if constexpr (KIND == 3) {
+              // Scale factors of this stage: shared memory -> TMEM (one buffer, rewritten every stage; the copies and
+              // the MMAs that follow execute in issue order). Columns: [A atom0 | A atom1 | B atom0 groups | B atom1 groups].
+              const uint32_t sf_smem = ring_addr + static_cast<uint32_t>(s) * stage_bytes + kATileBytes + b_tile_bytes;
+              const uint32_t sfa_t = tmem_base + 2u * acc_stride;
+              const uint32_t sfb_t = sfa_t + 8u;
+#pragma unroll
+              for (int t = 0; t < 2; ++t)
+                tmem_cp_32x128b_warpx4<CTAS>(sfa_t + 4u * t, make_smem_desc_noswizzle(sf_smem + t * kSfAtomBytes, 16, 128));
+              for (int t = 0; t < 2; ++t)
+                for (int g = 0; g < sf_groups_b; ++g)
+                  tmem_cp_32x128b_warpx4<CTAS>(
+                      sfb_t + 4u * (t * sf_groups_b + g),
+                      make_smem_desc_noswizzle(sf_smem + (2 + g * 2 + t) * kSfAtomBytes, 16, 128));
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                // an MMA covers 64 K elements = two scale bytes: bytes {0,1} or {2,3} of the atom's columns
+                const uint32_t sf_id = (k & 1) * 2u;
+                const uint32_t id = idesc | (sf_id << 4) | (sf_id << 29);
+                umma_mxf4<CTAS>(d_tmem, adesc + k * a_kstep, bdesc + k * b_kstep, id,
+                                (sfa_t + 4u * (k >> 1)) | (sf_id << 30),
+                                (sfb_t + 4u * (k >> 1) * sf_groups_b) | (sf_id << 30), k == 0 ? first : 1u);
+              }
+            } else {
+              umma<KIND, CTAS>(d_tmem, adesc, bdesc, idesc, first);
+              umma<KIND, CTAS>(d_tmem, adesc + a_kstep, bdesc + b_kstep, idesc, 1u);
+              umma<KIND, CTAS>(d_tmem, adesc + 2 * a_kstep, bdesc + 2 * b_kstep, idesc, 1u);
+              umma<KIND, CTAS>(d_tmem, adesc + 3 * a_kstep, bdesc + 3 * b_kstep, idesc, 1u);
+            }
             // Free the stage once these MMAs have read it.
             if constexpr (CTAS == 1) umma_commit(&empty_bar[s]);
             else umma_commit_pair(&empty_bar[s], 3);
@@ -394,6 +447,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         p.debug_out[blockIdx.x * 16 + 3] = prof_tmem;
         p.debug_out[blockIdx.x * 16 + 4] = prof_issue;
         p.debug_out[blockIdx.x * 16 + 5] = clock64() - prof_t0;
+      }
+    }
+  } else if (KIND == 3 && warp == 6) {
+    // ------------------------------------------------------------------ scale-factor stager (block-scaled kinds)
+    // Reads row-major e8m0 bytes (8 per row and stage) and writes them into shared memory in the order the
+    // shared-memory -> TMEM copy expects: row r, K block j of an atom at (r % 32) * 16 + (r / 32) * 4 + j.
+    WorkIter wi(p, pid, nprog);
+    int s = 0;
+    uint32_t ph = 0;
+    const int kblocks = (p.K + 31) / 32;
+    const bool vec_a = ((reinterpret_cast<uintptr_t>(p.sfa) | static_cast<uintptr_t>(p.sfa_stride)) & 7) == 0;
+    const bool vec_b = ((reinterpret_cast<uintptr_t>(p.sfb) | static_cast<uintptr_t>(p.sfb_stride)) & 7) == 0;
+    const uint32_t full_remote = mapa_cluster(smem_u32(&full_bar[0]), 0);
+    bool ok = true;
+    for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
+      int tm, tn;
+      tile_coords(p, w.tile, tm, tn);
+      const int m0 = tm * (kTileM * CTAS) + static_cast<int>(cta_rank) * kTileM;
+      const int n0 = tn * p.block_n;
+      for (int kb = w.kb0; kb < w.kb1; ++kb) {
+        ok = mbar_wait_warp(&empty_bar[s], ph ^ 1, wctx, TB_DEV_TIMEOUT_SCALE);
+        if (!ok) break;
+        uint8_t* sf = ring + static_cast<size_t>(s) * stage_bytes + kATileBytes + b_tile_bytes;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint2 v = load_scales8(p.sfa, p.sfa_stride, m0 + q * 32 + lane, p.M, kb, kblocks, vec_a);
+          *reinterpret_cast<uint32_t*>(sf + lane * 16 + q * 4) = v.x;
+          *reinterpret_cast<uint32_t*>(sf + kSfAtomBytes + lane * 16 + q * 4) = v.y;
+        }
+        for (int g = 0; g < sf_groups_b; ++g) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int r = g * 128 + q * 32 + lane;
+            const uint2 v = (r < p.block_n) ? load_scales8(p.sfb, p.sfb_stride, n0 + r, p.N, kb, kblocks, vec_b)
+                                            : make_uint2(0x7F7F7F7Fu, 0x7F7F7F7Fu);
+            uint8_t* dst = sf + (2 + g * 2) * kSfAtomBytes + lane * 16 + q * 4;
+            *reinterpret_cast<uint32_t*>(dst) = v.x;
+            *reinterpret_cast<uint32_t*>(dst + kSfAtomBytes) = v.y;
+          }
+        }
+        fence_proxy_async_smem();  // generic-proxy writes above are read by the tensor-core copy engine
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CTAS == 1) mbar_arrive(&full_bar[s]);
+          else mbar_arrive_remote(full_remote + s * 8);
+        }
+        if (++s == stages) {
+          s = 0;
+          ph ^= 1;
+        }
       }
     }
   } else {

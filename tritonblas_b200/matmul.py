@@ -228,6 +228,55 @@ def matmul_a8w8(a, b, a_scale, b_scale, c, enable_streamk=False, work_stealing=F
     return persistent_matmul_lt(a, b, c, selector, None, a_scale=a_scale, b_scale=b_scale, quantized=True)
 
 
+def matmul_fp4(a, b, c, a_scales, b_scales, block_m=None, block_n=None, block_k=None, group_size_m=8, num_warps=8,
+               num_stages=2):
+    """MXFP4 product C = A @ B^T of packed e2m1 operands with e8m0 block-32 scales (reference: matmul.py:519-625).
+
+    a: (M, K/2) uint8, b: (N, K/2) uint8 (two codes per byte, even element in the low nibble), c: (M, N) bf16/fp16/fp32,
+    a_scales: (M, K/32) uint8, b_scales: (N, K/32) uint8. ``block_n`` (a multiple of 32, at most 224) and
+    ``group_size_m`` override the library's choice; block_m, block_k, num_warps and num_stages are accepted for
+    signature compatibility (tile height, stage depth and warp roles are fixed by the kernel).
+    """
+    M, K = a.shape[0], a.shape[1] * 2
+    N = b.shape[0]
+    assert b.shape[1] * 2 == K, f"Incompatible Dimensions: A has K={K}, B has K={b.shape[1] * 2}"
+    assert K % 32 == 0, "K must be a multiple of the MX block size (32)"
+    if block_k is not None:
+        assert block_k % 64 == 0, "BLOCK_K must be multiple of 64 for FP4"
+    if not (a.is_cuda and b.is_cuda and c.is_cuda):
+        raise RuntimeError("tritonblas_b200 runs on CUDA tensors only (no CPU path)")
+    if hasattr(torch, "float4_e2m1fn_x2"):
+        a = a.view(torch.uint8) if a.dtype == torch.float4_e2m1fn_x2 else a
+        b = b.view(torch.uint8) if b.dtype == torch.float4_e2m1fn_x2 else b
+
+    def rows_ok(t):
+        return t.stride(1) == 1 and t.stride(0) % 16 == 0 and t.data_ptr() % 16 == 0
+
+    a = a if rows_ok(a) else a.contiguous()
+    b = b if rows_ok(b) else b.contiguous()
+    a_scales = a_scales.view(torch.uint8)
+    b_scales = b_scales.view(torch.uint8)
+    a_scales = a_scales if a_scales.stride(1) == 1 else a_scales.contiguous()
+    b_scales = b_scales if b_scales.stride(1) == 1 else b_scales.contiguous()
+    assert tuple(a_scales.shape) == (M, K // 32) and tuple(b_scales.shape) == (N, K // 32), "scale shapes"
+    if M == 0 or N == 0:
+        return c
+    args = _lib.Mxfp4Args()
+    args.m, args.n, args.k = M, N, K
+    args.a, args.a_row_stride = _ptr(a), a.stride(0)
+    args.b, args.b_row_stride = _ptr(b), b.stride(0)
+    args.c, (args.c_stride_m, args.c_stride_n), args.c_dtype = _ptr(c), _strides(c), _lib.DTYPE_CODE[c.dtype]
+    args.a_scales, args.a_scales_row_stride = _ptr(a_scales), a_scales.stride(0)
+    args.b_scales, args.b_scales_row_stride = _ptr(b_scales), b_scales.stride(0)
+    args.block_n = int(block_n) if block_n else 0
+    args.cta_pair = {None: 0, 128: 1, 256: 2}.get(block_m, 0)  # tile height 128 = one CTA, 256 = a CTA pair
+    args.group_m = int(group_size_m) if (block_m is not None or block_n is not None) else 0
+    with torch.cuda.device(a.device):
+        rc = _lib.lib.tb_gemm_mxfp4(ctypes.byref(args), _lib.current_stream_ptr(a.device))
+    _lib.check(rc, "tb_gemm_mxfp4")
+    return c
+
+
 @torch.library.custom_op("tritonblas::_addmm", mutates_args=())
 def _addmm(bias: torch.Tensor, a: torch.Tensor, b: torch.Tensor, enable_streamk: Optional[bool] = False,
            sk_grid: Optional[int] = None, work_stealing: Optional[bool] = False) -> torch.Tensor:
