@@ -106,21 +106,31 @@ int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);
 
 /* MXFP4 GEMM: C (m, n) = sum over 32-element K blocks of (A_e2m1 * 2^(sa-127)) . (B_e2m1 * 2^(sb-127)), fp32
  * accumulate, one cast. A is (m, k/2) bytes and B is (n, k/2) bytes, two e2m1 codes per byte (even element in the low
- * nibble), K contiguous, row strides in bytes (multiples of 16). Scales are e8m0 bytes, row-major (m, k/32) and
- * (n, k/32). Runs on the block-scaled tensor-core instruction. Replaces matmul_fp4 + the fp4_matmul kernel
- * (include/tritonblas/matmul.py:519-625, kernels/fp4_matmul.py:8-130). */
+ * nibble), K contiguous, row strides in bytes (multiples of 16). Scales are e8m0 bytes in the "atom" arrangement the
+ * tensor core's scale copy consumes (see tb_mxfp4_scales_to_atoms): set scales_in_atoms = 1. Runs on the block-scaled
+ * tensor-core instruction. Replaces matmul_fp4 + the fp4_matmul kernel (include/tritonblas/matmul.py:519-625,
+ * kernels/fp4_matmul.py:8-130). */
 typedef struct tb_mxfp4_args {
   int32_t m, n, k;           /* k = number of 4-bit elements, a multiple of 32 */
   const void* a; int64_t a_row_stride;
   const void* b; int64_t b_row_stride;
   void* c; int64_t c_stride_m, c_stride_n; int32_t c_dtype;
-  const void* a_scales; int64_t a_scales_row_stride;
-  const void* b_scales; int64_t b_scales_row_stride;
-  int32_t block_n;           /* 0 = library's choice; else a multiple of 32, at most 224 */
+  const void* a_scales;      /* tb_mxfp4_atoms_bytes(m, k) bytes */
+  const void* b_scales;      /* tb_mxfp4_atoms_bytes(n, k) bytes */
+  int32_t scales_in_atoms;   /* must be 1 */
+  int32_t block_n;           /* 0 = library's choice; else 64, 128 or 192 */
   int32_t cta_pair;          /* 0 = library's choice; 1 or 2 */
   int32_t group_m;           /* 0 = library's choice */
 } tb_mxfp4_args;
 int tb_gemm_mxfp4(const tb_mxfp4_args* args, void* stream);
+
+/* Scale bytes in "atom" order: [ceil(rows/128)][ceil(k/128)][512], the byte of (row r, K block j) inside its atom at
+ * (r % 32) * 16 + ((r % 128) / 32) * 4 + (j % 4). Padding rows and blocks hold 127 (scale 1.0).
+ * tb_mxfp4_atoms_bytes gives the buffer size; tb_mxfp4_scales_to_atoms re-arranges row-major (rows, k/32) scale bytes
+ * (what the reference API passes, include/tritonblas/matmul.py:539-540) into it. */
+int64_t tb_mxfp4_atoms_bytes(int64_t rows, int64_t k);
+int tb_mxfp4_scales_to_atoms(const void* scales, int64_t scales_row_stride, int64_t rows, int64_t k, void* atoms,
+                             void* stream);
 
 /* MXFP4 block quantiser: x (rows, k) in f16/bf16/f32 with `x_row_stride` elements between rows, k % 32 == 0, to packed
  * e2m1 codes (rows, k/2) and e8m0 scale bytes (rows, k/32), both row-major with the given row strides in bytes.
@@ -129,6 +139,11 @@ int tb_gemm_mxfp4(const tb_mxfp4_args* args, void* stream);
  * strides 1,2,4,8,16, then one multiply); the reference has no such kernel. */
 int tb_mxfp4_quant(const void* x, int32_t x_dtype, int64_t rows, int64_t k, int64_t x_row_stride, void* codes,
                    int64_t codes_row_stride, void* scales, int64_t scales_row_stride, int32_t hadamard, void* stream);
+/* Same, and additionally (when atoms != NULL) writes the scale bytes in atom order for tb_gemm_mxfp4; `scales` may then
+ * be NULL. The atoms buffer must have been filled with 127 once (padding rows keep that value). */
+int tb_mxfp4_quant_atoms(const void* x, int32_t x_dtype, int64_t rows, int64_t k, int64_t x_row_stride, void* codes,
+                         int64_t codes_row_stride, void* scales, int64_t scales_row_stride, void* atoms, int32_t hadamard,
+                         void* stream);
 
 /* Reads (synchronously: waits for the device) and clears the per-device status word that kernels set when a bounded
  * wait gives up. 0 = no failure since the last call. No reference counterpart (its waits are unbounded,

@@ -42,7 +42,7 @@ def _no_device_failure():
     assert tb.device_status() == 0
 
 
-@pytest.mark.parametrize("block_m,block_n", [(128, 128), (128, 224), (256, 128), (256, 192), (256, 224), (None, None)])
+@pytest.mark.parametrize("block_m,block_n", [(128, 64), (128, 128), (128, 192), (256, 64), (256, 128), (256, 192), (None, None)])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 256), (256, 256, 512), (512, 448, 1024), (384, 640, 2048)])
 def test_fp4_tile_shapes(m, n, k, block_m, block_n):
     _, _, (qa, sa), (qb, sb) = _quantised(m, n, k, seed=m + n)
@@ -96,3 +96,29 @@ def test_fp4_config4_full_size_with_hadamard_activations():
     got = c[torch.as_tensor(rows).cuda()][:, torch.as_tensor(cols).cuda()].float()
     rel = (got - src).norm() / src.norm()
     assert rel < 0.2, rel   # 4-bit operands: ~10 % relative Frobenius error is expected, 100 % would mean a layout bug
+
+
+@pytest.mark.parametrize("rows,k", [(1, 32), (130, 96), (256, 1024), (333, 1120)])
+def test_scale_atoms_round_trip_and_fused_emit(rows, k):
+    """Atom-ordered scales: the re-arrangement kernel, the quantiser's direct emit and the row-major bytes all agree."""
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, k, generator=g).to(torch.bfloat16).cuda()
+    codes, scales = utils.dynamic_mxfp4_quant(x)
+    codes2, atoms = utils.dynamic_mxfp4_quant(x, scale_atoms=True)
+    assert torch.equal(codes, codes2)
+    assert torch.equal(atoms.to_row_major(), scales)
+    conv = utils.mxfp4_scales_to_atoms(scales, k)
+    assert torch.equal(conv.to_row_major(), scales)
+    assert torch.equal(conv.data, atoms.data)            # padding bytes included (127)
+
+
+def test_fp4_accepts_prearranged_scales():
+    m, n, k = 384, 448, 1024
+    g = torch.Generator().manual_seed(21)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(n, k, generator=g).to(torch.bfloat16).cuda()
+    qa, sa = utils.hadamard_mxfp4_quant(a, scale_atoms=True)
+    qb, sb = utils.hadamard_mxfp4_quant(b, scale_atoms=True)
+    c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    tb.matmul_fp4(qa, qb, c, sa, sb)
+    _check(c, qa, sa.to_row_major(), qb, sb.to_row_major(), "fp4 atoms in")

@@ -58,8 +58,7 @@ class Mxfp4Args(ctypes.Structure):
         ("a", ctypes.c_void_p), ("a_row_stride", ctypes.c_int64),
         ("b", ctypes.c_void_p), ("b_row_stride", ctypes.c_int64),
         ("c", ctypes.c_void_p), ("c_stride_m", ctypes.c_int64), ("c_stride_n", ctypes.c_int64), ("c_dtype", ctypes.c_int32),
-        ("a_scales", ctypes.c_void_p), ("a_scales_row_stride", ctypes.c_int64),
-        ("b_scales", ctypes.c_void_p), ("b_scales_row_stride", ctypes.c_int64),
+        ("a_scales", ctypes.c_void_p), ("b_scales", ctypes.c_void_p), ("scales_in_atoms", ctypes.c_int32),
         ("block_n", ctypes.c_int32), ("cta_pair", ctypes.c_int32), ("group_m", ctypes.c_int32),
     ]
 
@@ -82,6 +81,15 @@ def _load():
                                    ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
                                    ctypes.c_void_p]
     lib.tb_mxfp4_quant.restype = ctypes.c_int
+    lib.tb_mxfp4_quant_atoms.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                         ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p,
+                                         ctypes.c_int32, ctypes.c_void_p]
+    lib.tb_mxfp4_quant_atoms.restype = ctypes.c_int
+    lib.tb_mxfp4_atoms_bytes.argtypes = [ctypes.c_int64, ctypes.c_int64]
+    lib.tb_mxfp4_atoms_bytes.restype = ctypes.c_int64
+    lib.tb_mxfp4_scales_to_atoms.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                             ctypes.c_void_p, ctypes.c_void_p]
+    lib.tb_mxfp4_scales_to_atoms.restype = ctypes.c_int
     lib.tb_device_status.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)]
     lib.tb_device_status.restype = ctypes.c_int
     lib.tb_device_info.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]

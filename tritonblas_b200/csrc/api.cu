@@ -113,6 +113,20 @@ int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uin
   return TB_OK;
 }
 
+// Scale-factor atoms as a 3-D tensor of 32-bit words: [row groups][K atoms][128 words]; box = one group x two atoms.
+int encode_sf_atoms(CUtensorMap* map, const void* base, uint64_t k_atoms, uint64_t groups) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return TB_ERR_ALIGNMENT;
+  cuuint64_t dims[3] = {128, k_atoms, groups};
+  cuuint64_t strides[2] = {512, 512 * k_atoms};
+  cuuint32_t box[3] = {128, 2, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cu_fail(static_cast<int>(r), "cuTensorMapEncodeTiled(scale atoms)");
+  return TB_OK;
+}
+
 static int esize_of(int dtype) {
   switch (dtype) {
     case TB_DTYPE_F16:
@@ -138,7 +152,7 @@ MachineModel machine_for(const DeviceState* d) {
 
 template <int KIND, int CTAS>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const GemmParams& p, int programs, int smem_bytes,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const CUtensorMap* tsfa = nullptr, const CUtensorMap* tsfb = nullptr) {
   auto kernel = gemm_kernel<KIND, CTAS>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
@@ -154,7 +168,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const Gemm
   attr[0].val.clusterDim.z = 1;
   lc.attrs = attr;
   lc.numAttrs = 1;
-  e = cudaLaunchKernelEx(&lc, kernel, ta, tb_, p);
+  // Kinds without block scales never touch the scale maps; they get copies of the operand maps as placeholders.
+  e = cudaLaunchKernelEx(&lc, kernel, ta, tb_, tsfa != nullptr ? *tsfa : ta, tsfb != nullptr ? *tsfb : tb_, p);
   if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemm)");
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return TB_OK;
@@ -320,6 +335,7 @@ static int gemm_mxfp4_impl(const tb_mxfp4_args& a, cudaStream_t stream) {
   if (a.m == 0 || a.n == 0) return TB_OK;
   if (a.k == 0) return TB_ERR_UNSUPPORTED;
   if (a.a == nullptr || a.b == nullptr || a.c == nullptr || a.a_scales == nullptr || a.b_scales == nullptr) return TB_ERR_INVALID;
+  if (a.scales_in_atoms != 1) return TB_ERR_UNSUPPORTED;  // row-major scales are re-arranged by tb_mxfp4_scales_to_atoms first
   if (a.c_dtype != TB_DTYPE_F16 && a.c_dtype != TB_DTYPE_BF16 && a.c_dtype != TB_DTYPE_F32) return TB_ERR_UNSUPPORTED;
   DeviceState* dev = nullptr;
   int device = 0;
@@ -339,8 +355,9 @@ static int gemm_mxfp4_impl(const tb_mxfp4_args& a, cudaStream_t stream) {
   if (a.group_m > 0) cfg.group_m = a.group_m;
   const int pair = cfg.cta_pair == 2 ? 2 : 1;
   const int bn = cfg.block_n;
-  const int groups = (bn + 127) / 128;
-  if (bn < 32 || (bn % 32) != 0 || ((bn / pair) % 16) != 0 || 2 * bn + 8 + 8 * groups > 512) return TB_ERR_INVALID;
+  const int groups = kSfGroupsB;  // 128-row scale groups staged per tile
+  // Widths are multiples of 64: the MMA reads B's scale factors starting at an even TMEM column (64 rows apart).
+  if (bn < 64 || bn > 192 || (bn % 64) != 0) return TB_ERR_INVALID;
   const int kbytes = a.k / 2;
   const int stage_bytes = (128 * 128 + (bn / pair) * 128 + (2 + 2 * groups) * 512 + 1023) & ~1023;
   int stages = (dev->smem_optin - 2048) / stage_bytes;
@@ -363,8 +380,6 @@ static int gemm_mxfp4_impl(const tb_mxfp4_args& a, cudaStream_t stream) {
   while (tc < 2 * bn + 8 + 8 * groups) tc <<= 1;
   p.tmem_cols = static_cast<uint32_t>(tc);
   p.C = a.c; p.ldc_m = a.c_stride_m; p.ldc_n = a.c_stride_n; p.c_dtype = a.c_dtype;
-  p.sfa = static_cast<const unsigned char*>(a.a_scales); p.sfa_stride = a.a_scales_row_stride;
-  p.sfb = static_cast<const unsigned char*>(a.b_scales); p.sfb_stride = a.b_scales_row_stride;
   p.status = dev->status;
   p.timeout_ns = 2000000000ull;
   // e2m1 operands (format 1), ue8m0 scales (bit 23), K-major, N >> 3, M >> 4; scale-factor ids are set per MMA
@@ -380,9 +395,13 @@ static int gemm_mxfp4_impl(const tb_mxfp4_args& a, cudaStream_t stream) {
   CUtensorMap ta, tbm;
   rc = encode_2d(&ta, TB_DTYPE_U8, a.a, kbytes, a.m, static_cast<uint64_t>(a.a_row_stride), 128, 128, 1);
   if (rc == TB_OK) rc = encode_2d(&tbm, TB_DTYPE_U8, a.b, kbytes, a.n, static_cast<uint64_t>(a.b_row_stride), 128, bn / pair, 1);
+  CUtensorMap tsfa, tsfb;
+  const uint64_t k_atoms = (static_cast<uint64_t>(a.k) + 127) / 128;
+  if (rc == TB_OK) rc = encode_sf_atoms(&tsfa, a.a_scales, k_atoms, (static_cast<uint64_t>(a.m) + 127) / 128);
+  if (rc == TB_OK) rc = encode_sf_atoms(&tsfb, a.b_scales, k_atoms, (static_cast<uint64_t>(a.n) + 127) / 128);
   if (rc != TB_OK) return rc;
-  if (pair == 1) return launch_gemm<3, 1>(ta, tbm, p, programs, smem_bytes, stream);
-  return launch_gemm<3, 2>(ta, tbm, p, programs, smem_bytes, stream);
+  if (pair == 1) return launch_gemm<3, 1>(ta, tbm, p, programs, smem_bytes, stream, &tsfa, &tsfb);
+  return launch_gemm<3, 2>(ta, tbm, p, programs, smem_bytes, stream, &tsfa, &tsfb);
 }
 
 }  // namespace tb

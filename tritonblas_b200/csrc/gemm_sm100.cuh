@@ -25,10 +25,12 @@ namespace tb {
 constexpr int kTileM = 128;          // accumulator rows per CTA (TMEM lanes)
 constexpr int kStageRowBytes = 128;  // one swizzle row: K extent of a stage in bytes for K-major operands
 constexpr int kGemmThreads = 192;      // producer + MMA + 4 epilogue warps
-constexpr int kGemmThreadsMx = 224;    // block-scaled kinds add one warp that stages the scale factors
 constexpr int kSfAtomBytes = 512;      // scale factors of 128 rows x 4 K blocks, laid out [32 rows][4 row quads][4 blocks]
+constexpr int kSfGroupsB = 2;          // 128-row scale groups staged for B: tiles are 64, 128 or 192 columns wide and start
+                                       // at a multiple of 64 (the MMA takes its scale columns from an even TMEM column),
+                                       // so a tile touches at most two groups
 template <int KIND>
-constexpr int gemm_threads() { return KIND == 3 ? kGemmThreadsMx : kGemmThreads; }
+constexpr int gemm_threads() { return kGemmThreads; }
 constexpr int kATileBytes = kTileM * kStageRowBytes;  // 16 KB
 
 enum : int { TB_F16 = 0, TB_BF16 = 1, TB_F32 = 2, TB_E4M3 = 3, TB_E5M2 = 4, TB_U8 = 5 };
@@ -62,11 +64,8 @@ struct GemmParams {
   // failure reporting
   int* status;
   unsigned long long timeout_ns;
-  // block-scaled (MXFP4) operands: e8m0 scale bytes, row-major (rows, K/32) with a row stride in bytes
-  const unsigned char* sfa;
-  long long sfa_stride;
-  const unsigned char* sfb;
-  long long sfb_stride;
+  // block-scaled (MXFP4) operands: scale factors arrive through two extra tensor maps over the pre-arranged
+  // ("atom") layout [128-row group][K atom of 128 elements][512 bytes]
   long long* debug_out;  // bit 1 of debug_flags: per-CTA cycle counters of each role are written here
   int debug_flags;  // measurement-only knobs (results are wrong when set): bit 0 = do not reload B on odd K blocks
 };
@@ -196,24 +195,10 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, in
   }
 }
 
-// Eight consecutive scale bytes of one row (K blocks kb8*8 .. kb8*8+7); 127 (= 1.0) where the row or block is outside.
-__device__ __forceinline__ uint2 load_scales8(const unsigned char* base, long long stride, int row, int rows, int kb8,
-                                              int kblocks, bool vec_ok) {
-  if (row >= rows) return make_uint2(0x7F7F7F7Fu, 0x7F7F7F7Fu);
-  const unsigned char* p = base + row * stride + static_cast<long long>(kb8) * 8;
-  if (vec_ok && kb8 * 8 + 8 <= kblocks) return __ldg(reinterpret_cast<const uint2*>(p));
-  uint32_t w[2] = {0u, 0u};
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const uint32_t b = (kb8 * 8 + j < kblocks) ? static_cast<uint32_t>(__ldg(p + j)) : 0x7Fu;
-    w[j >> 2] |= b << ((j & 3) * 8);
-  }
-  return make_uint2(w[0], w[1]);
-}
-
 template <int KIND, int CTAS>
 __global__ void __launch_bounds__(gemm_threads<KIND>(), 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is what the 128-byte swizzle pattern and the matrix descriptors assume.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -226,10 +211,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int bn_local = p.block_n / CTAS;  // B rows this CTA stages
   const int b_tile_bytes = bn_local * kStageRowBytes;
-  // Block-scaled kinds append the stage's scale factors: A rows of this CTA (2 atoms), then all B rows of the tile
-  // (2 atoms per group of 128 rows).
-  const int sf_groups_b = (p.block_n + 127) / 128;
-  const int sf_bytes = (KIND == 3) ? (2 + 2 * sf_groups_b) * kSfAtomBytes : 0;
+  // Block-scaled kinds append the stage's scale factors: two K atoms for this CTA's A rows, then two K atoms for each
+  // of the two 128-row groups of B that can overlap the tile.
+  const int sf_bytes = (KIND == 3) ? (2 + 2 * kSfGroupsB) * kSfAtomBytes : 0;
   const int stage_bytes = (kATileBytes + b_tile_bytes + sf_bytes + 1023) & ~1023;
   const int stages = p.stages;
 
@@ -249,7 +233,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], KIND == 3 ? 1 + CTAS : 1);  // + one arrival per scale-staging warp
+      mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -285,7 +269,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t ph = 0;
       const int a_atom = kStageRowBytes / p.esize;  // elements per 128-byte row
       // In a pair, transaction bytes of both CTAs land on the even CTA's barrier, which expects the sum.
-      const uint32_t expect = static_cast<uint32_t>(kATileBytes + b_tile_bytes) * CTAS;
+      const uint32_t expect = static_cast<uint32_t>(kATileBytes + b_tile_bytes + sf_bytes) * CTAS;
       const int mn_box_bytes = p.k_per_stage * kStageRowBytes;
       bool ok = true;
       long long prof_wait = 0, prof_t0 = clock64();
@@ -319,6 +303,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 for (int j = 0; j < bn_local / a_atom; ++j)
                   tma_load_2d(sb + j * mn_box_bytes, &tmap_b, &full_bar[s], n0 + j * a_atom, k0);
               }
+              if constexpr (KIND == 3) {
+                uint8_t* sf = sb + b_tile_bytes;
+                // scale tensor maps are [row group][K atom][128 words]; a box holds the stage's two K atoms
+                tma_load_3d(sf, &tmap_sfa, &full_bar[s], 0, 2 * kb, m0 >> 7);
+                for (int g = 0; g < kSfGroupsB; ++g)
+                  tma_load_3d(sf + (2 + 2 * g) * kSfAtomBytes, &tmap_sfb, &full_bar[s], 0, 2 * kb,
+                              ((tn * p.block_n) >> 7) + g);
+              }
             } else {
               const uint32_t bar = mapa_cluster(smem_u32(&full_bar[s]), 0);
               if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], skip_b ? 2u * kATileBytes : expect);
@@ -334,6 +326,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               } else {
                 for (int j = 0; j < bn_local / a_atom; ++j)
                   tma_load_2d_pair(sb + j * mn_box_bytes, &tmap_b, bar, n0 + j * a_atom, k0);
+              }
+              if constexpr (KIND == 3) {
+                // Each CTA of the pair needs the scales of its own A rows and of every B row of the tile.
+                uint8_t* sf = sb + b_tile_bytes;
+                tma_load_3d_pair(sf, &tmap_sfa, bar, 0, 2 * kb, m0 >> 7);
+                for (int g = 0; g < kSfGroupsB; ++g)
+                  tma_load_3d_pair(sf + (2 + 2 * g) * kSfAtomBytes, &tmap_sfb, bar, 0, 2 * kb,
+                                   ((tn * p.block_n) >> 7) + g);
               }
             }
           }
@@ -382,6 +382,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (prof) prof_tmem += clock64() - pt0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * acc_stride);
+        // Block-scaled kinds: where the tile's first column sits inside its first 128-row scale group.
+        int mtm, mtn;
+        tile_coords(p, w.tile, mtm, mtn);
+        const uint32_t sfb_col0 = static_cast<uint32_t>((mtn * p.block_n) & 127) >> 5;
+        const int sf_groups_used = (((mtn * p.block_n) & 127) + p.block_n + 127) >> 7;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           const long long pf0 = prof ? clock64() : 0;
           ok = mbar_wait_warp(&full_bar[s], ph, wctx, TB_DEV_TIMEOUT_SMEM_FULL);
@@ -394,18 +399,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (elect_one()) {
             if constexpr (KIND == 3) {
               // Scale factors of this stage: shared memory -> TMEM (one buffer, rewritten every stage; the copies and
-              // the MMAs that follow execute in issue order). Columns: [A atom0 | A atom1 | B atom0 groups | B atom1 groups].
+              // the MMAs that follow execute in issue order). TMEM columns, one per 32 rows:
+              //   [A atom0 (4) | A atom1 (4) | B atom0: 2 groups (8) | B atom1: 2 groups (8)].
               const uint32_t sf_smem = ring_addr + static_cast<uint32_t>(s) * stage_bytes + kATileBytes + b_tile_bytes;
               const uint32_t sfa_t = tmem_base + 2u * acc_stride;
               const uint32_t sfb_t = sfa_t + 8u;
 #pragma unroll
               for (int t = 0; t < 2; ++t)
                 tmem_cp_32x128b_warpx4<CTAS>(sfa_t + 4u * t, make_smem_desc_noswizzle(sf_smem + t * kSfAtomBytes, 16, 128));
+#pragma unroll
               for (int t = 0; t < 2; ++t)
-                for (int g = 0; g < sf_groups_b; ++g)
-                  tmem_cp_32x128b_warpx4<CTAS>(
-                      sfb_t + 4u * (t * sf_groups_b + g),
-                      make_smem_desc_noswizzle(sf_smem + (2 + g * 2 + t) * kSfAtomBytes, 16, 128));
+#pragma unroll
+                for (int g = 0; g < kSfGroupsB; ++g)
+                  if (g < sf_groups_used)
+                    tmem_cp_32x128b_warpx4<CTAS>(
+                        sfb_t + 4u * (t * kSfGroupsB + g),
+                        make_smem_desc_noswizzle(sf_smem + (2 + g * 2 + t) * kSfAtomBytes, 16, 128));
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
                 // an MMA covers 64 K elements = two scale bytes: bytes {0,1} or {2,3} of the atom's columns
@@ -413,7 +422,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 const uint32_t id = idesc | (sf_id << 4) | (sf_id << 29);
                 umma_mxf4<CTAS>(d_tmem, adesc + k * a_kstep, bdesc + k * b_kstep, id,
                                 (sfa_t + 4u * (k >> 1)) | (sf_id << 30),
-                                (sfb_t + 4u * (k >> 1) * sf_groups_b) | (sf_id << 30), k == 0 ? first : 1u);
+                                (sfb_t + 4u * (k >> 1) * kSfGroupsB + sfb_col0) | (sf_id << 30), k == 0 ? first : 1u);
               }
             } else {
               umma<KIND, CTAS>(d_tmem, adesc, bdesc, idesc, first);
@@ -447,56 +456,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         p.debug_out[blockIdx.x * 16 + 3] = prof_tmem;
         p.debug_out[blockIdx.x * 16 + 4] = prof_issue;
         p.debug_out[blockIdx.x * 16 + 5] = clock64() - prof_t0;
-      }
-    }
-  } else if (KIND == 3 && warp == 6) {
-    // ------------------------------------------------------------------ scale-factor stager (block-scaled kinds)
-    // Reads row-major e8m0 bytes (8 per row and stage) and writes them into shared memory in the order the
-    // shared-memory -> TMEM copy expects: row r, K block j of an atom at (r % 32) * 16 + (r / 32) * 4 + j.
-    WorkIter wi(p, pid, nprog);
-    int s = 0;
-    uint32_t ph = 0;
-    const int kblocks = (p.K + 31) / 32;
-    const bool vec_a = ((reinterpret_cast<uintptr_t>(p.sfa) | static_cast<uintptr_t>(p.sfa_stride)) & 7) == 0;
-    const bool vec_b = ((reinterpret_cast<uintptr_t>(p.sfb) | static_cast<uintptr_t>(p.sfb_stride)) & 7) == 0;
-    const uint32_t full_remote = mapa_cluster(smem_u32(&full_bar[0]), 0);
-    bool ok = true;
-    for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
-      int tm, tn;
-      tile_coords(p, w.tile, tm, tn);
-      const int m0 = tm * (kTileM * CTAS) + static_cast<int>(cta_rank) * kTileM;
-      const int n0 = tn * p.block_n;
-      for (int kb = w.kb0; kb < w.kb1; ++kb) {
-        ok = mbar_wait_warp(&empty_bar[s], ph ^ 1, wctx, TB_DEV_TIMEOUT_SCALE);
-        if (!ok) break;
-        uint8_t* sf = ring + static_cast<size_t>(s) * stage_bytes + kATileBytes + b_tile_bytes;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint2 v = load_scales8(p.sfa, p.sfa_stride, m0 + q * 32 + lane, p.M, kb, kblocks, vec_a);
-          *reinterpret_cast<uint32_t*>(sf + lane * 16 + q * 4) = v.x;
-          *reinterpret_cast<uint32_t*>(sf + kSfAtomBytes + lane * 16 + q * 4) = v.y;
-        }
-        for (int g = 0; g < sf_groups_b; ++g) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int r = g * 128 + q * 32 + lane;
-            const uint2 v = (r < p.block_n) ? load_scales8(p.sfb, p.sfb_stride, n0 + r, p.N, kb, kblocks, vec_b)
-                                            : make_uint2(0x7F7F7F7Fu, 0x7F7F7F7Fu);
-            uint8_t* dst = sf + (2 + g * 2) * kSfAtomBytes + lane * 16 + q * 4;
-            *reinterpret_cast<uint32_t*>(dst) = v.x;
-            *reinterpret_cast<uint32_t*>(dst + kSfAtomBytes) = v.y;
-          }
-        }
-        fence_proxy_async_smem();  // generic-proxy writes above are read by the tensor-core copy engine
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (CTAS == 1) mbar_arrive(&full_bar[s]);
-          else mbar_arrive_remote(full_remote + s * 8);
-        }
-        if (++s == stages) {
-          s = 0;
-          ph ^= 1;
-        }
       }
     }
   } else {

@@ -98,11 +98,40 @@ __device__ __forceinline__ uint32_t encode_e2m1(float q) {
   return sign | code;
 }
 
+// Byte offset of the scale of (row, K block) in atom order [row / 128][block / 4][512].
+__device__ __forceinline__ long long atom_offset(int row, int blk, int k_atoms) {
+  return (static_cast<long long>(row >> 7) * k_atoms + (blk >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (blk & 3);
+}
+
+__global__ void __launch_bounds__(256) scales_to_atoms_kernel(const unsigned char* __restrict__ scales, long long row_stride,
+                                                                 unsigned char* __restrict__ atoms, int rows, int kblocks,
+                                                                 int k_atoms, int row_groups) {
+  // One thread per 32-bit word of the output: row r, K blocks 4a .. 4a+3 (padding gets 127 = scale 1.0).
+  const long long total = static_cast<long long>(row_groups) * k_atoms * 128;
+  for (long long w = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; w < total;
+       w += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int word = static_cast<int>(w & 127);
+    const long long atom = w >> 7;
+    const int a = static_cast<int>(atom % k_atoms);
+    const int g = static_cast<int>(atom / k_atoms);
+    const int row = g * 128 + (word & 3) * 32 + (word >> 2);
+    uint32_t v = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int blk = a * 4 + j;
+      const uint32_t b = (row < rows && blk < kblocks) ? scales[row * row_stride + blk] : 0x7Fu;
+      v |= b << (8 * j);
+    }
+    reinterpret_cast<uint32_t*>(atoms)[w] = v;
+  }
+}
+
 template <typename T, bool HADAMARD>
 __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const T* __restrict__ x, long long x_row_stride,
                                                             unsigned char* __restrict__ codes, long long codes_row_stride,
                                                             unsigned char* __restrict__ scales, long long scales_row_stride,
-                                                            int rows, int blocks_per_row) {
+                                                            unsigned char* __restrict__ atoms, int k_atoms, int rows,
+                                                            int blocks_per_row) {
   const long long total = static_cast<long long>(rows) * blocks_per_row;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -128,13 +157,17 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const T* __restrict__ 
       packed[i >> 3] |= code << ((i & 7) * 4);
     }
     *reinterpret_cast<uint4*>(codes + row * codes_row_stride + blk * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    scales[row * scales_row_stride + blk] = static_cast<unsigned char>((e + 127) & 0xFF);
+    const unsigned char sbyte = static_cast<unsigned char>((e + 127) & 0xFF);
+    if (scales != nullptr) scales[row * scales_row_stride + blk] = sbyte;
+    if (atoms != nullptr)  // the arrangement the block-scaled MMA's scale copy consumes (see atom_offset)
+      atoms[atom_offset(row, blk, k_atoms)] = sbyte;
   }
 }
 
 template <typename T>
-int launch(const void* x, long long xs, void* codes, long long cs, void* scales, long long ss, int rows, int k, int hadamard,
-           int num_sms, cudaStream_t stream) {
+int launch(const void* x, long long xs, void* codes, long long cs, void* scales, long long ss, void* atoms, int rows, int k,
+           int hadamard, int num_sms, cudaStream_t stream) {
+  const int k_atoms = (k + 127) / 128;
   const int bpr = k / 32;
   const long long total = static_cast<long long>(rows) * bpr;
   long long blocks = (total + 255) / 256;
@@ -143,10 +176,12 @@ int launch(const void* x, long long xs, void* codes, long long cs, void* scales,
   if (blocks < 1) blocks = 1;
   if (hadamard)
     quant_mxfp4_kernel<T, true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-        static_cast<const T*>(x), xs, static_cast<unsigned char*>(codes), cs, static_cast<unsigned char*>(scales), ss, rows, bpr);
+        static_cast<const T*>(x), xs, static_cast<unsigned char*>(codes), cs, static_cast<unsigned char*>(scales), ss,
+        static_cast<unsigned char*>(atoms), k_atoms, rows, bpr);
   else
     quant_mxfp4_kernel<T, false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-        static_cast<const T*>(x), xs, static_cast<unsigned char*>(codes), cs, static_cast<unsigned char*>(scales), ss, rows, bpr);
+        static_cast<const T*>(x), xs, static_cast<unsigned char*>(codes), cs, static_cast<unsigned char*>(scales), ss,
+        static_cast<unsigned char*>(atoms), k_atoms, rows, bpr);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "quant_mxfp4_kernel launch");
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -156,10 +191,10 @@ int launch(const void* x, long long xs, void* codes, long long cs, void* scales,
 }  // namespace
 }  // namespace tb
 
-extern "C" int tb_mxfp4_quant(const void* x, int32_t x_dtype, int64_t rows, int64_t k, int64_t x_row_stride, void* codes,
-                              int64_t codes_row_stride, void* scales, int64_t scales_row_stride, int32_t hadamard,
-                              void* stream) {
-  if (x == nullptr || codes == nullptr || scales == nullptr) return TB_ERR_INVALID;
+extern "C" int tb_mxfp4_quant_atoms(const void* x, int32_t x_dtype, int64_t rows, int64_t k, int64_t x_row_stride, void* codes,
+                                    int64_t codes_row_stride, void* scales, int64_t scales_row_stride, void* atoms,
+                                    int32_t hadamard, void* stream) {
+  if (x == nullptr || codes == nullptr || (scales == nullptr && atoms == nullptr)) return TB_ERR_INVALID;
   if (rows < 0 || k < 0 || (k % 32) != 0) return TB_ERR_INVALID;
   if (rows == 0 || k == 0) return TB_OK;
   if (rows > 0x7FFFFFFF || k > 0x7FFFFFFF) return TB_ERR_INVALID;
@@ -174,11 +209,42 @@ extern "C" int tb_mxfp4_quant(const void* x, int32_t x_dtype, int64_t rows, int6
   const int r = static_cast<int>(rows), kk = static_cast<int>(k);
   switch (x_dtype) {
     case TB_DTYPE_BF16:
-      return tb::launch<__nv_bfloat16>(x, x_row_stride, codes, codes_row_stride, scales, scales_row_stride, r, kk, hadamard, sms, st);
+      return tb::launch<__nv_bfloat16>(x, x_row_stride, codes, codes_row_stride, scales, scales_row_stride, atoms, r, kk, hadamard, sms, st);
     case TB_DTYPE_F16:
-      return tb::launch<__half>(x, x_row_stride, codes, codes_row_stride, scales, scales_row_stride, r, kk, hadamard, sms, st);
+      return tb::launch<__half>(x, x_row_stride, codes, codes_row_stride, scales, scales_row_stride, atoms, r, kk, hadamard, sms, st);
     case TB_DTYPE_F32:
-      return tb::launch<float>(x, x_row_stride, codes, codes_row_stride, scales, scales_row_stride, r, kk, hadamard, sms, st);
+      return tb::launch<float>(x, x_row_stride, codes, codes_row_stride, scales, scales_row_stride, atoms, r, kk, hadamard, sms, st);
     default: return TB_ERR_UNSUPPORTED;
   }
+}
+
+extern "C" int tb_mxfp4_quant(const void* x, int32_t x_dtype, int64_t rows, int64_t k, int64_t x_row_stride, void* codes,
+                              int64_t codes_row_stride, void* scales, int64_t scales_row_stride, int32_t hadamard,
+                              void* stream) {
+  if (scales == nullptr) return TB_ERR_INVALID;
+  return tb_mxfp4_quant_atoms(x, x_dtype, rows, k, x_row_stride, codes, codes_row_stride, scales, scales_row_stride, nullptr,
+                              hadamard, stream);
+}
+
+extern "C" int64_t tb_mxfp4_atoms_bytes(int64_t rows, int64_t k) {
+  if (rows <= 0 || k <= 0) return 0;
+  return ((rows + 127) / 128) * ((k + 127) / 128) * 512;
+}
+
+extern "C" int tb_mxfp4_scales_to_atoms(const void* scales, int64_t scales_row_stride, int64_t rows, int64_t k, void* atoms,
+                                        void* stream) {
+  if (scales == nullptr || atoms == nullptr || rows < 0 || k < 0 || (k % 32) != 0) return TB_ERR_INVALID;
+  if (rows == 0 || k == 0) return TB_OK;
+  if (rows > 0x7FFFFFFF || k > 0x7FFFFFFF) return TB_ERR_INVALID;
+  const int groups = static_cast<int>((rows + 127) / 128), k_atoms = static_cast<int>((k + 127) / 128);
+  const long long words = static_cast<long long>(groups) * k_atoms * 128;
+  long long blocks = (words + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  tb::scales_to_atoms_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned char*>(scales), scales_row_stride, static_cast<unsigned char*>(atoms), static_cast<int>(rows),
+      static_cast<int>(k / 32), k_atoms, groups);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return tb::cuda_fail(e, "scales_to_atoms_kernel launch");
+  tb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return TB_OK;
 }

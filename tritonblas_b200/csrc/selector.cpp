@@ -66,9 +66,10 @@ int select_config(const tb_problem& p, const MachineModel& hw, tb_config* out) {
 
   Candidate best{};
   double best_cost = 1e30;
-  // Block-scaled kinds keep their scale factors in TMEM beside two accumulator stages, which caps the width at 224.
+  // Block-scaled kinds keep their scale factors in TMEM beside two accumulator stages and need tile starts that are
+  // multiples of 64 columns, which leaves 192, 128 and 64.
   static const int kBNDense[] = {256, 128, 64, 32, 0};
-  static const int kBNMx[] = {224, 192, 128, 0};
+  static const int kBNMx[] = {192, 128, 64, 0};
   const int* widths = mx ? kBNMx : kBNDense;
   for (int pair = 2; pair >= 1; --pair) {
     if (pair == 2 && (sms < 2 || !hw.allow_pair)) continue;
@@ -81,7 +82,7 @@ int select_config(const tb_problem& p, const MachineModel& hw, tb_config* out) {
       const long long tiles_m = (p.m + tile_m - 1) / tile_m, tiles_n = (p.n + bn - 1) / bn;
       const long long tiles = tiles_m * tiles_n;
       const int programs = std::max(1, sms / pair);
-      const int sf_bytes = mx ? (2 + 2 * ((bn + 127) / 128)) * 512 : 0;
+      const int sf_bytes = mx ? (2 + 2 * 2) * 512 : 0;
       int stages = (hw.smem_optin - 2048) / ((128 * 128 + bn_local * 128 + sf_bytes + 1023) & ~1023);
       stages = std::min(stages, 8);
       if (stages < 2) continue;
@@ -129,8 +130,8 @@ int select_config(const tb_problem& p, const MachineModel& hw, tb_config* out) {
   out->sk_grid = best.sk_grid;
   out->num_sms = sms;
   out->smem_bytes = smem_bytes_for(best.bn, best.pair, best.stages) +
-                    (mx ? best.stages * (2 + 2 * ((best.bn + 127) / 128)) * 512 : 0);
-  out->tmem_cols = next_pow2(2 * best.bn + (mx ? 8 + 8 * ((best.bn + 127) / 128) : 0));
+                    (mx ? best.stages * (2 + 2 * 2) * 512 : 0);
+  out->tmem_cols = next_pow2(2 * best.bn + (mx ? 8 + 8 * 2 : 0));
   out->predicted_us = static_cast<float>(best.dp_us);
   out->predicted_sk_us = static_cast<float>(best.sk_us);
   return TB_OK;

@@ -233,7 +233,7 @@ def matmul_fp4(a, b, c, a_scales, b_scales, block_m=None, block_n=None, block_k=
     """MXFP4 product C = A @ B^T of packed e2m1 operands with e8m0 block-32 scales (reference: matmul.py:519-625).
 
     a: (M, K/2) uint8, b: (N, K/2) uint8 (two codes per byte, even element in the low nibble), c: (M, N) bf16/fp16/fp32,
-    a_scales: (M, K/32) uint8, b_scales: (N, K/32) uint8. ``block_n`` (a multiple of 32, at most 224) and
+    a_scales: (M, K/32) uint8, b_scales: (N, K/32) uint8. ``block_n`` (64, 128 or 192) and
     ``group_size_m`` override the library's choice; block_m, block_k, num_warps and num_stages are accepted for
     signature compatibility (tile height, stage depth and warp roles are fixed by the kernel).
     """
@@ -254,20 +254,20 @@ def matmul_fp4(a, b, c, a_scales, b_scales, block_m=None, block_n=None, block_k=
 
     a = a if rows_ok(a) else a.contiguous()
     b = b if rows_ok(b) else b.contiguous()
-    a_scales = a_scales.view(torch.uint8)
-    b_scales = b_scales.view(torch.uint8)
-    a_scales = a_scales if a_scales.stride(1) == 1 else a_scales.contiguous()
-    b_scales = b_scales if b_scales.stride(1) == 1 else b_scales.contiguous()
     assert tuple(a_scales.shape) == (M, K // 32) and tuple(b_scales.shape) == (N, K // 32), "scale shapes"
     if M == 0 or N == 0:
         return c
+    # The tensor core consumes scales in 128-row x 4-block atoms; row-major scales (the reference layout) are re-arranged
+    # by one small kernel each, pre-arranged ones (utils.Mxfp4ScaleAtoms) are used as they are.
+    from .utils import mxfp4_scales_to_atoms
+    a_atoms = mxfp4_scales_to_atoms(a_scales, K)
+    b_atoms = mxfp4_scales_to_atoms(b_scales, K)
     args = _lib.Mxfp4Args()
     args.m, args.n, args.k = M, N, K
     args.a, args.a_row_stride = _ptr(a), a.stride(0)
     args.b, args.b_row_stride = _ptr(b), b.stride(0)
     args.c, (args.c_stride_m, args.c_stride_n), args.c_dtype = _ptr(c), _strides(c), _lib.DTYPE_CODE[c.dtype]
-    args.a_scales, args.a_scales_row_stride = _ptr(a_scales), a_scales.stride(0)
-    args.b_scales, args.b_scales_row_stride = _ptr(b_scales), b_scales.stride(0)
+    args.a_scales, args.b_scales, args.scales_in_atoms = _ptr(a_atoms.data), _ptr(b_atoms.data), 1
     args.block_n = int(block_n) if block_n else 0
     args.cta_pair = {None: 0, 128: 1, 256: 2}.get(block_m, 0)  # tile height 128 = one CTA, 256 = a CTA pair
     args.group_m = int(group_size_m) if (block_m is not None or block_n is not None) else 0

@@ -99,7 +99,48 @@ def quantize_tensor_per_channel(tensor, target_dtype, axis, *, min_scale=1e-8):
     return q.to(dtype), scale.squeeze(axis).to(torch.float32)
 
 
-def _mxfp4_quant(x, hadamard):
+class Mxfp4ScaleAtoms:
+    """e8m0 scales of a (rows, k) operand in the arrangement the block-scaled tensor-core copy consumes:
+    [ceil(rows/128)][ceil(k/128)][512 bytes], byte of (row r, K block j) at (r % 32) * 16 + ((r % 128) / 32) * 4 + j % 4
+    inside its atom, padding = 127. matmul_fp4 accepts this in place of the row-major (rows, k/32) tensor and then skips
+    its own re-arrangement pass."""
+
+    def __init__(self, data, rows, k):
+        self.data, self.rows, self.k = data, int(rows), int(k)
+
+    @property
+    def shape(self):
+        return (self.rows, self.k // 32)
+
+    def to_row_major(self):
+        """Back to the (rows, k/32) layout of the reference API (a torch gather; for tests and debugging)."""
+        k_atoms = -(-self.k // 128)
+        r = torch.arange(self.rows, device=self.data.device).view(-1, 1)
+        j = torch.arange(self.k // 32, device=self.data.device).view(1, -1)
+        off = ((r // 128) * k_atoms + j // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + j % 4
+        return self.data[off]
+
+
+def mxfp4_scales_to_atoms(scales, k=None):
+    """Re-arrange row-major e8m0 scales (rows, k/32) into :class:`Mxfp4ScaleAtoms` (one small CUDA kernel)."""
+    if isinstance(scales, Mxfp4ScaleAtoms):
+        return scales
+    scales = scales.view(torch.uint8)
+    if scales.stride(1) != 1:
+        scales = scales.contiguous()
+    rows, kblocks = scales.shape
+    k = kblocks * 32 if k is None else k
+    nbytes = int(_lib.lib.tb_mxfp4_atoms_bytes(rows, k))
+    atoms = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=scales.device)
+    if rows and kblocks:
+        with torch.cuda.device(scales.device):
+            rc = _lib.lib.tb_mxfp4_scales_to_atoms(ctypes.c_void_p(scales.data_ptr()), scales.stride(0), rows, k,
+                                                   ctypes.c_void_p(atoms.data_ptr()), _lib.current_stream_ptr(scales.device))
+        _lib.check(rc, "tb_mxfp4_scales_to_atoms")
+    return Mxfp4ScaleAtoms(atoms, rows, k)
+
+
+def _mxfp4_quant(x, hadamard, scale_atoms=False):
     assert x.ndim == 2, "Input must be 2D tensor"
     M, N = x.shape
     assert N % 32 == 0, f"N ({N}) must be divisible by 32"
@@ -112,27 +153,34 @@ def _mxfp4_quant(x, hadamard):
         x = x.contiguous()
     codes = torch.empty((M, N // 2), dtype=torch.uint8, device=x.device)
     scales = torch.empty((M, N // 32), dtype=torch.uint8, device=x.device)
+    atoms = None
+    if scale_atoms:
+        atoms = torch.full((max(int(_lib.lib.tb_mxfp4_atoms_bytes(M, N)), 16),), 127, dtype=torch.uint8, device=x.device)
     if M == 0 or N == 0:
-        return codes, scales
+        return (codes, Mxfp4ScaleAtoms(atoms, M, N)) if scale_atoms else (codes, scales)
     with torch.cuda.device(x.device):
-        rc = _lib.lib.tb_mxfp4_quant(ctypes.c_void_p(x.data_ptr()), _lib.DTYPE_CODE[x.dtype], M, N, x.stride(0),
-                                     ctypes.c_void_p(codes.data_ptr()), codes.stride(0),
-                                     ctypes.c_void_p(scales.data_ptr()), scales.stride(0), int(hadamard),
-                                     _lib.current_stream_ptr(x.device))
+        rc = _lib.lib.tb_mxfp4_quant_atoms(ctypes.c_void_p(x.data_ptr()), _lib.DTYPE_CODE[x.dtype], M, N, x.stride(0),
+                                           ctypes.c_void_p(codes.data_ptr()), codes.stride(0),
+                                           ctypes.c_void_p(scales.data_ptr()), scales.stride(0),
+                                           ctypes.c_void_p(atoms.data_ptr()) if scale_atoms else ctypes.c_void_p(0),
+                                           int(hadamard), _lib.current_stream_ptr(x.device))
     _lib.check(rc, "tb_mxfp4_quant")
+    if scale_atoms:
+        return codes, Mxfp4ScaleAtoms(atoms, M, N)
     return codes, scales
 
 
-def dynamic_mxfp4_quant(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def dynamic_mxfp4_quant(x: torch.Tensor, scale_atoms: bool = False):
     """x (M, N) -> packed e2m1 codes (M, N/2) uint8 and e8m0 scales (M, N/32) uint8, one scale per 32 contiguous
-    elements; bit-identical to the reference quantiser (utils.py:742-789)."""
-    return _mxfp4_quant(x, False)
+    elements; bit-identical to the reference quantiser (utils.py:742-789). With ``scale_atoms`` the scales come back as
+    :class:`Mxfp4ScaleAtoms`, ready for matmul_fp4 without a re-arrangement pass."""
+    return _mxfp4_quant(x, False, scale_atoms)
 
 
-def hadamard_mxfp4_quant(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def hadamard_mxfp4_quant(x: torch.Tensor, scale_atoms: bool = False):
     """Fused activation transform: rotate every 32-element block by H32/sqrt(32), then quantise to MXFP4.
     Apply it to both operands' K blocks: (A H)(B H)^T = A B^T because H is orthonormal and symmetric."""
-    return _mxfp4_quant(x, True)
+    return _mxfp4_quant(x, True, scale_atoms)
 
 
 _E2M1_TABLE = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
