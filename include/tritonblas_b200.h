@@ -91,6 +91,11 @@ typedef struct tb_gemm_args {
   int64_t workspace_bytes;
   uint32_t epoch;        /* stream-K: a value never used before on this workspace (start at 1, add 1 per launch;
                             the workspace must be zero-filled once when it is created) */
+  /* Grouped (MoE) GEMM, tb_grouped_gemm only: group g multiplies rows [group_offsets[g], group_offsets[g+1]) of A
+   * (m = total rows) by its own B_g, stored as rows [g*n, (g+1)*n) of a (num_groups*n, k) K-contiguous matrix, into the
+   * same rows of C. group_offsets is a DEVICE array of num_groups + 1 ascending int32. */
+  const int32_t* group_offsets;
+  int32_t num_groups;
 } tb_gemm_args;
 
 /* Fill `cfg` for `p`. Stands in for origami.select_config + OrigamiMatmulSelector._compute_sk_grid
@@ -103,6 +108,10 @@ int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override);
 
 /* Enqueue one GEMM. `cfg` may be NULL (the library selects). */
 int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);
+
+/* Grouped GEMM over row groups of A (expert-parallel MoE projections). No reference counterpart: its semantics are the
+ * dense contract of tb_gemm applied per group. A and every B_g must be K-contiguous; data-parallel schedule only. */
+int tb_grouped_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);
 
 /* MXFP4 GEMM: C (m, n) = sum over 32-element K blocks of (A_e2m1 * 2^(sa-127)) . (B_e2m1 * 2^(sb-127)), fp32
  * accumulate, one cast. A is (m, k/2) bytes and B is (n, k/2) bytes, two e2m1 codes per byte (even element in the low

@@ -49,6 +49,7 @@ class GemmArgs(ctypes.Structure):
         ("bias", ctypes.c_void_p), ("bias_stride", ctypes.c_int64), ("bias_dtype", ctypes.c_int32),
         ("allow_tf32", ctypes.c_int32), ("streamk", ctypes.c_int32), ("sk_grid", ctypes.c_int32),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("epoch", ctypes.c_uint32),
+        ("group_offsets", ctypes.c_void_p), ("num_groups", ctypes.c_int32),
     ]
 
 
@@ -75,6 +76,8 @@ def _load():
     lib.tb_gemm_workspace_bytes.restype = ctypes.c_int64
     lib.tb_gemm.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p]
     lib.tb_gemm.restype = ctypes.c_int
+    lib.tb_grouped_gemm.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p]
+    lib.tb_grouped_gemm.restype = ctypes.c_int
     lib.tb_gemm_mxfp4.argtypes = [ctypes.POINTER(Mxfp4Args), ctypes.c_void_p]
     lib.tb_gemm_mxfp4.restype = ctypes.c_int
     lib.tb_mxfp4_quant.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,

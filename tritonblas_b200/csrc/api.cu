@@ -178,8 +178,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const Gemm
 int gemm_fp32_exact(const tb_gemm_args& a, cudaStream_t stream);                 // simt_gemm.cu
 int gemm_generic_loader(const tb_gemm_args& a, const tb_config& cfg, cudaStream_t stream, int* status);  // unaligned operands
 
-static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStream_t stream) {
+static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStream_t stream, bool grouped = false) {
   if (a.m < 0 || a.n < 0 || a.k < 0) return TB_ERR_INVALID;
+  if (grouped && (a.group_offsets == nullptr || a.num_groups <= 0 || a.num_groups > 4096 || a.streamk)) return TB_ERR_INVALID;
   if (a.m == 0 || a.n == 0) return TB_OK;
   if (a.a == nullptr || a.b == nullptr || a.c == nullptr) return TB_ERR_INVALID;
   if (a.a_dtype != a.b_dtype) return TB_ERR_UNSUPPORTED;
@@ -194,7 +195,7 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
   int rc = current_device_state(&dev, &device);
   if (rc != TB_OK) return rc;
 
-  if (a.a_dtype == TB_DTYPE_F32 && !a.allow_tf32) return gemm_fp32_exact(a, stream);
+  if (a.a_dtype == TB_DTYPE_F32 && !a.allow_tf32) return grouped ? TB_ERR_UNSUPPORTED : gemm_fp32_exact(a, stream);
 
   // operand majors from strides
   int a_mn, b_mn;
@@ -205,13 +206,15 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
   else if (a.b_stride_n == 1 || a.n == 1) b_mn = 1;
   else return TB_ERR_UNSUPPORTED;
   if (a.a_stride_k == 1 && a.a_stride_m == 1 && a.m > 1 && a.k > 1) return TB_ERR_INVALID;
+  if (grouped && (a_mn || b_mn)) return TB_ERR_UNSUPPORTED;
 
   tb_config cfg;
   if (user_cfg != nullptr) {
     cfg = *user_cfg;
   } else {
     tb_problem pr = {};
-    pr.m = a.m; pr.n = a.n; pr.k = a.k;
+    pr.m = grouped ? (a.m + a.num_groups - 1) / a.num_groups : a.m;  // grouped: model the average group
+    pr.n = a.n; pr.k = a.k;
     pr.a_dtype = a.a_dtype; pr.b_dtype = a.b_dtype; pr.c_dtype = a.c_dtype;
     pr.a_mn_major = a_mn; pr.b_mn_major = b_mn;
     pr.streamk = a.streamk;
@@ -228,8 +231,9 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
   const int bk = 128 / es;
   int stages = cfg.stages;
   if (stages < 2) stages = 2;
-  while (stages > 2 && smem_bytes_for(bn, pair, stages) > dev->smem_optin) --stages;
-  const int smem_bytes = smem_bytes_for(bn, pair, stages);
+  const int extra_smem = grouped ? 4 * (a.num_groups + 2) : 0;  // per-group tile prefix
+  while (stages > 2 && smem_bytes_for(bn, pair, stages) + extra_smem > dev->smem_optin) --stages;
+  const int smem_bytes = smem_bytes_for(bn, pair, stages) + extra_smem;
   if (smem_bytes > dev->smem_optin) return TB_ERR_INVALID;
 
   GemmParams p = {};
@@ -251,6 +255,10 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
   p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
   p.status = dev->status;
   p.timeout_ns = 2000000000ull;
+  if (grouped) {
+    p.group_offsets = a.group_offsets;
+    p.num_groups = a.num_groups;
+  }
   {
     const char* dbg = getenv("TB_DEBUG_FLAGS");
     p.debug_flags = dbg != nullptr ? atoi(dbg) : 0;
@@ -292,6 +300,10 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
       p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(a.workspace) + 4096);
       p.epoch = a.epoch;
     }
+  } else if (grouped) {
+    programs = max_programs;  // the tile count depends on the device-side group sizes
+    p.dp_tiles = 0;
+    p.sk_tiles = 0;
   } else {
     programs = cfg.grid > 0 ? cfg.grid : max_programs;
     if (programs > max_programs) programs = max_programs;
@@ -310,10 +322,11 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
   if (!a_mn) rc = encode_2d(&ta, a.a_dtype, A, a.k, a.m, static_cast<uint64_t>(a.a_stride_m) * es, bk, 128, 1);
   else rc = encode_2d(&ta, a.a_dtype, A, a.m, a.k, static_cast<uint64_t>(a.a_stride_k) * es, mn_atom, bk, mn_swz);
   if (rc == TB_OK) {
-    if (!b_mn) rc = encode_2d(&tbm, a.b_dtype, B, a.k, a.n, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, 1);
+    const uint64_t b_rows = grouped ? static_cast<uint64_t>(a.n) * a.num_groups : static_cast<uint64_t>(a.n);
+    if (!b_mn) rc = encode_2d(&tbm, a.b_dtype, B, a.k, b_rows, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, 1);
     else rc = encode_2d(&tbm, a.b_dtype, B, a.n, a.k, static_cast<uint64_t>(a.b_stride_k) * es, mn_atom, bk, mn_swz);
   }
-  if (rc == TB_ERR_ALIGNMENT) return gemm_generic_loader(a, cfg, stream, dev->status);
+  if (rc == TB_ERR_ALIGNMENT && !grouped) return gemm_generic_loader(a, cfg, stream, dev->status);
   if (rc != TB_OK) return rc;
 
 #define TB_LAUNCH(K, C) return launch_gemm<K, C>(ta, tbm, p, programs, smem_bytes, stream)
@@ -428,6 +441,11 @@ int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override) 
 int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream) {
   if (args == nullptr) return TB_ERR_INVALID;
   return tb::gemm_impl(*args, cfg, static_cast<cudaStream_t>(stream));
+}
+
+int tb_grouped_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream) {
+  if (args == nullptr) return TB_ERR_INVALID;
+  return tb::gemm_impl(*args, cfg, static_cast<cudaStream_t>(stream), true);
 }
 
 int tb_gemm_mxfp4(const tb_mxfp4_args* args, void* stream) {

@@ -61,6 +61,10 @@ struct GemmParams {
   float* partials;   // [programs * CTAS][block_n][128] fp32
   unsigned* flags;   // [programs * CTAS]
   unsigned epoch;    // value that marks a partial as published for this launch
+  // grouped (MoE) mode: group g owns rows [group_offsets[g], group_offsets[g+1]) of A and C and rows
+  // [g * N, (g + 1) * N) of B; null for a plain GEMM
+  const int* group_offsets;
+  int num_groups;
   // failure reporting
   int* status;
   unsigned long long timeout_ns;
@@ -80,8 +84,9 @@ struct WorkIter {
   int pid, nprog, nkb, dp_tiles, sk_tiles;
   int dp_next;
   long long it, it_end;
-  __device__ WorkIter(const GemmParams& p, int pid_, int nprog_)
-      : pid(pid_), nprog(nprog_), nkb(p.num_k_blocks), dp_tiles(p.dp_tiles), sk_tiles(p.sk_tiles) {
+  __device__ WorkIter(const GemmParams& p, int pid_, int nprog_, int grouped_tiles = -1)
+      : pid(pid_), nprog(nprog_), nkb(p.num_k_blocks), dp_tiles(grouped_tiles >= 0 ? grouped_tiles : p.dp_tiles),
+        sk_tiles(grouped_tiles >= 0 ? 0 : p.sk_tiles) {
     dp_next = pid;
     range(pid, it, it_end);
   }
@@ -118,14 +123,49 @@ struct WorkIter {
   }
 };
 
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
-  const int width = p.group_m * p.tiles_n;
+__device__ __forceinline__ void tile_coords_dims(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int width = group_m * tiles_n;
   const int group = tile / width;
-  const int first_m = group * p.group_m;
-  const int gsz = min(p.tiles_m - first_m, p.group_m);
+  const int first_m = group * group_m;
+  const int gsz = min(tiles_m - first_m, group_m);
   const int r = tile - group * width;
   tm = first_m + r % gsz;
   tn = r / gsz;
+}
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+  tile_coords_dims(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+}
+
+// Where a tile sits: first row of the tile in A / C, one past the last valid row, first column, first row of B.
+struct TileGeom {
+  int m0, row_end, n0, b_row0;
+};
+// tile_prefix (shared memory, grouped mode only): tiles before group g, for g in [0, num_groups].
+__device__ __forceinline__ TileGeom tile_geometry(const GemmParams& p, int tile, int tile_m, const int* tile_prefix) {
+  TileGeom g;
+  int tm, tn;
+  if (p.group_offsets == nullptr) {
+    tile_coords(p, tile, tm, tn);
+    g.m0 = tm * tile_m;
+    g.row_end = p.M;
+    g.n0 = tn * p.block_n;
+    g.b_row0 = g.n0;
+    return g;
+  }
+  int lo = 0, hi = p.num_groups;  // last group whose prefix is <= tile
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_prefix[mid] <= tile) lo = mid;
+    else hi = mid;
+  }
+  const int row0 = p.group_offsets[lo], row1 = p.group_offsets[lo + 1];
+  const int tiles_m = (row1 - row0 + tile_m - 1) / tile_m;
+  tile_coords_dims(tile - tile_prefix[lo], tiles_m, p.tiles_n, p.group_m, tm, tn);
+  g.m0 = row0 + tm * tile_m;
+  g.row_end = row1;
+  g.n0 = tn * p.block_n;
+  g.b_row0 = lo * p.N + g.n0;
+  return g;
 }
 
 __device__ __forceinline__ float load_as_float(const void* p, long long idx, int dtype) {
@@ -226,6 +266,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint64_t* publish_bar = tmem_empty + 2;  // the four epilogue warps have all written their part of a partial tile
   uint32_t* tmem_ptr_slot = reinterpret_cast<uint32_t*>(publish_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_slot + 1);
+  int* tile_prefix = reinterpret_cast<int*>(tmem_ptr_slot + 2);  // grouped mode: [num_groups + 1]
 
   WaitCtx wctx{abort_flag, p.status, p.timeout_ns};
   const bool prof = (p.debug_flags & 2) != 0;  // measurement builds: per-role cycle counters
@@ -242,6 +283,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     mbar_init(publish_bar, 4);
     mbar_fence_init();
+    if (p.group_offsets != nullptr) {
+      int acc_tiles = 0;
+      tile_prefix[0] = 0;
+      for (int g = 0; g < p.num_groups; ++g) {
+        const int rows = p.group_offsets[g + 1] - p.group_offsets[g];
+        acc_tiles += ((rows + kTileM * CTAS - 1) / (kTileM * CTAS)) * p.tiles_n;
+        tile_prefix[g + 1] = acc_tiles;
+      }
+    }
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
   }
@@ -257,6 +307,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
+  const int grouped_tiles = p.group_offsets != nullptr ? tile_prefix[p.num_groups] : -1;
+  constexpr int kPairTileM = kTileM * CTAS;
 
   const int acc_stride = p.block_n;  // TMEM columns per accumulator stage
 
@@ -264,7 +316,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the schedule (warp-uniform control flow); one elected lane issues the copies.
     {
-      WorkIter wi(p, pid, nprog);
+      WorkIter wi(p, pid, nprog, grouped_tiles);
       int s = 0;
       uint32_t ph = 0;
       const int a_atom = kStageRowBytes / p.esize;  // elements per 128-byte row
@@ -274,10 +326,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       bool ok = true;
       long long prof_wait = 0, prof_t0 = clock64();
       for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
-        int tm, tn;
-        tile_coords(p, w.tile, tm, tn);
-        const int m0 = tm * (kTileM * CTAS) + static_cast<int>(cta_rank) * kTileM;
-        const int n0 = tn * p.block_n + static_cast<int>(cta_rank) * bn_local;
+        const TileGeom tg = tile_geometry(p, w.tile, kPairTileM, tile_prefix);
+        const int m0 = tg.m0 + static_cast<int>(cta_rank) * kTileM;
+        const int n0 = tg.b_row0 + static_cast<int>(cta_rank) * bn_local;  // row of the B map
+        const int sf_n0 = tg.n0;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           const long long pw0 = prof ? clock64() : 0;
           ok = mbar_wait_warp(&empty_bar[s], ph ^ 1, wctx, TB_DEV_TIMEOUT_SMEM_EMPTY);
@@ -309,7 +361,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 tma_load_3d(sf, &tmap_sfa, &full_bar[s], 0, 2 * kb, m0 >> 7);
                 for (int g = 0; g < kSfGroupsB; ++g)
                   tma_load_3d(sf + (2 + 2 * g) * kSfAtomBytes, &tmap_sfb, &full_bar[s], 0, 2 * kb,
-                              ((tn * p.block_n) >> 7) + g);
+                              (sf_n0 >> 7) + g);
               }
             } else {
               const uint32_t bar = mapa_cluster(smem_u32(&full_bar[s]), 0);
@@ -333,7 +385,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 tma_load_3d_pair(sf, &tmap_sfa, bar, 0, 2 * kb, m0 >> 7);
                 for (int g = 0; g < kSfGroupsB; ++g)
                   tma_load_3d_pair(sf + (2 + 2 * g) * kSfAtomBytes, &tmap_sfb, bar, 0, 2 * kb,
-                                   ((tn * p.block_n) >> 7) + g);
+                                   (sf_n0 >> 7) + g);
               }
             }
           }
@@ -353,7 +405,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ------------------------------------------------------------------ MMA issuer
     // Warp-uniform loop; one elected lane issues the MMAs and commits. In a pair only the even CTA issues.
     if (cta_rank == 0) {
-      WorkIter wi(p, pid, nprog);
+      WorkIter wi(p, pid, nprog, grouped_tiles);
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -383,10 +435,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * acc_stride);
         // Block-scaled kinds: where the tile's first column sits inside its first 128-row scale group.
-        int mtm, mtn;
-        tile_coords(p, w.tile, mtm, mtn);
-        const uint32_t sfb_col0 = static_cast<uint32_t>((mtn * p.block_n) & 127) >> 5;
-        const int sf_groups_used = (((mtn * p.block_n) & 127) + p.block_n + 127) >> 7;
+        const int mma_n0 = (KIND == 3) ? tile_geometry(p, w.tile, kPairTileM, tile_prefix).n0 : 0;
+        const uint32_t sfb_col0 = static_cast<uint32_t>(mma_n0 & 127) >> 5;
+        const int sf_groups_used = ((mma_n0 & 127) + p.block_n + 127) >> 7;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           const long long pf0 = prof ? clock64() : 0;
           ok = mbar_wait_warp(&full_bar[s], ph, wctx, TB_DEV_TIMEOUT_SMEM_FULL);
@@ -462,7 +513,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ------------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const int row_in_tile = q * 32 + lane;
-    WorkIter wi(p, pid, nprog);
+    WorkIter wi(p, pid, nprog, grouped_tiles);
     int acc = 0;
     uint32_t acc_ph = 0;
     const int slot = pid * CTAS + static_cast<int>(cta_rank);
@@ -471,10 +522,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     bool ok = true;
     long long prof_wait = 0, prof_t0 = clock64();
     for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
-      int tm, tn;
-      tile_coords(p, w.tile, tm, tn);
-      const int m0 = tm * (kTileM * CTAS) + static_cast<int>(cta_rank) * kTileM;
-      const int n0 = tn * p.block_n;
+      const TileGeom tg = tile_geometry(p, w.tile, kPairTileM, tile_prefix);
+      const int m0 = tg.m0 + static_cast<int>(cta_rank) * kTileM;
+      const int n0 = tg.n0;
+      const int row_end = tg.row_end;
       const long long pe0 = prof ? clock64() : 0;
       const int row = m0 + row_in_tile;
       const bool owner = (w.kb0 == 0);
@@ -501,7 +552,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (!ok) break;
       }
 
-      const float a_s = (p.a_scale != nullptr && row < p.M) ? p.a_scale[row] : 1.0f;
+      const float a_s = (p.a_scale != nullptr && row < row_end) ? p.a_scale[row] : 1.0f;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * acc_stride);
       for (int c = 0; c < p.block_n / 32; ++c) {
         uint32_t r[32];
@@ -524,7 +575,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * kTileM);
         }
         const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
+        if (row < row_end && col0 < p.N) {
           if (p.a_scale != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= a_s;

@@ -228,6 +228,48 @@ def matmul_a8w8(a, b, a_scale, b_scale, c, enable_streamk=False, work_stealing=F
     return persistent_matmul_lt(a, b, c, selector, None, a_scale=a_scale, b_scale=b_scale, quantized=True)
 
 
+def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None):
+    """Grouped (MoE) GEMM: out[r] = x[r] @ w[g].T for every row r of group g, rows of group g being
+    [group_offsets[g], group_offsets[g+1]).
+
+    x: (rows, K) K-contiguous; w: (G, N, K) contiguous (each expert's weight stored N x K, the K-contiguous fast layout);
+    group_offsets: int32 CUDA tensor of G + 1 ascending offsets (it stays on the device: no host synchronisation);
+    out: (rows, N), allocated in x.dtype when omitted. The reference has no grouped kernel; per group this is its dense
+    contract (fp32 accumulate, one cast).
+    """
+    assert x.ndim == 2 and w.ndim == 3 and x.shape[1] == w.shape[2], "Incompatible Dimensions"
+    if not (x.is_cuda and w.is_cuda and group_offsets.is_cuda):
+        raise RuntimeError("tritonblas_b200 runs on CUDA tensors only (no CPU path)")
+    rows, K = x.shape
+    G, N, _ = w.shape
+    assert group_offsets.dtype == torch.int32 and group_offsets.numel() == G + 1, "group_offsets must be int32[G + 1]"
+    if out is None:
+        out = x.new_empty(rows, N)
+    if rows == 0 or N == 0:
+        return out
+    x = x if x.stride(1) == 1 else x.contiguous()
+    w = w if w.is_contiguous() else w.contiguous()
+    group_offsets = group_offsets.contiguous()
+    selector = _make_matmul_selector(max(rows // G, 1), N, K, x.dtype, w.dtype, out.dtype, x.device)
+    cfg = selector.config_for(False, False)
+    args = _lib.GemmArgs()
+    args.m, args.n, args.k = rows, N, K
+    args.a_dtype, args.b_dtype, args.c_dtype = (_lib.DTYPE_CODE[x.dtype], _lib.DTYPE_CODE[w.dtype], _lib.DTYPE_CODE[out.dtype])
+    args.a, (args.a_stride_m, args.a_stride_k) = _ptr(x), _strides(x)
+    args.b, args.b_stride_k, args.b_stride_n = _ptr(w), 1, K
+    args.c, (args.c_stride_m, args.c_stride_n) = _ptr(out), _strides(out)
+    if a_scale is not None:
+        a_scale = a_scale.to(torch.float32).contiguous().view(-1)
+        b_scale = b_scale.to(torch.float32).contiguous().view(-1)
+        args.a_scale, args.b_scale = _ptr(a_scale), _ptr(b_scale)
+    args.allow_tf32 = 1
+    args.group_offsets, args.num_groups = _ptr(group_offsets), G
+    with torch.cuda.device(x.device):
+        rc = _lib.lib.tb_grouped_gemm(ctypes.byref(args), ctypes.byref(cfg), _lib.current_stream_ptr(x.device))
+    _lib.check(rc, "tb_grouped_gemm")
+    return out
+
+
 def matmul_fp4(a, b, c, a_scales, b_scales, block_m=None, block_n=None, block_k=None, group_size_m=8, num_warps=8,
                num_stages=2):
     """MXFP4 product C = A @ B^T of packed e2m1 operands with e8m0 block-32 scales (reference: matmul.py:519-625).
