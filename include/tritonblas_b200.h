@@ -69,6 +69,8 @@ typedef struct tb_config {
   int32_t tmem_cols;
   float predicted_us;     /* model estimate for the data-parallel schedule */
   float predicted_sk_us;  /* model estimate for the stream-K schedule */
+  int32_t swap_ab;   /* 1: the kernel computes C^T = B^T A^T (few rows of A: the weight matrix takes the 128-row side of
+                        the tile); block_m/block_n then describe the swapped problem */
 } tb_config;
 
 /* One dense GEMM: C = cast( (A . B) [* a_scale[:,None]] [* b_scale[None,:]] [+ bias[None,:]] ).

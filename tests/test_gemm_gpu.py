@@ -198,3 +198,35 @@ def test_torch_compile_fullgraph():
     a, b = make_operands(256, 256, 256, torch.bfloat16, "T", "N")
     fn = torch.compile(lambda x, y: tb.matmul(x, y), fullgraph=True)
     assert_close_to_oracle(fn(a, b), a, b, what="compiled")
+
+
+@pytest.mark.parametrize("streamk", [False, True])
+@pytest.mark.parametrize("ta,tb_", LAYOUTS)
+@pytest.mark.parametrize("m", [1, 5, 16, 33, 64])
+def test_decode_shapes_take_the_transposed_path(m, ta, tb_, streamk):
+    """Few rows of A against a wide B: the library computes C^T = B^T A^T internally; results, bias axis and output
+    layout must be unaffected."""
+    n, k = 1280, 512
+    a, b = make_operands(m, n, k, torch.bfloat16, ta, tb_, seed=m)
+    sel = tb.OrigamiMatmulSelector(m, n, k, torch.bfloat16, torch.bfloat16, torch.bfloat16, torch.device("cuda", 0),
+                                   streamk=streamk)
+    assert sel._cfg.swap_ab == 1
+    c = tb.matmul(a, b, enable_streamk=streamk)
+    assert_close_to_oracle(c, a, b, what=f"decode m={m} {ta}{tb_} sk={streamk}")
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    c2 = tb.addmm(bias, a, b, enable_streamk=streamk)
+    assert_close_to_oracle(c2, a, b, bias=bias, what=f"decode addmm m={m}")
+
+
+def test_decode_shape_a8w8_scales_swap_with_operands():
+    from tritonblas_b200 import utils
+    m, n, k = 16, 2048, 1024
+    g = torch.Generator().manual_seed(0)
+    a16 = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    b16 = (torch.randn(k, n, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    a8, a_s = utils.quantize_tensor_per_channel(a16, torch.float8_e4m3fn, axis=1)
+    b8, b_s = utils.quantize_tensor_per_channel(b16, torch.float8_e4m3fn, axis=0)
+    b8 = b8.T.contiguous().T
+    c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    tb.matmul_a8w8(a8, b8, a_s, b_s, c)
+    assert_close_to_oracle(c, a8, b8, a_scale=a_s, b_scale=b_s, what="decode a8w8")

@@ -178,7 +178,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const Gemm
 int gemm_fp32_exact(const tb_gemm_args& a, cudaStream_t stream);                 // simt_gemm.cu
 int gemm_generic_loader(const tb_gemm_args& a, const tb_config& cfg, cudaStream_t stream, int* status);  // unaligned operands
 
-static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStream_t stream, bool grouped = false) {
+static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaStream_t stream, bool grouped = false,
+                     bool swapped = false) {
+  const tb_gemm_args& a = a_in;
   if (a.m < 0 || a.n < 0 || a.k < 0) return TB_ERR_INVALID;
   if (grouped && (a.group_offsets == nullptr || a.num_groups <= 0 || a.num_groups > 4096 || a.streamk)) return TB_ERR_INVALID;
   if (a.m == 0 || a.n == 0) return TB_OK;
@@ -222,6 +224,22 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
     rc = select_config(pr, machine_for(dev), &cfg);
     if (rc != TB_OK) return rc;
   }
+  if (cfg.swap_ab && !swapped && !grouped) {
+    // C^T = B^T A^T: exchange the operands' roles and transpose the output view; the per-row and per-column epilogue
+    // vectors trade places and the bias becomes a per-row vector.
+    tb_gemm_args t = a;
+    t.m = a.n; t.n = a.m;
+    t.a = a.b; t.a_stride_m = a.b_stride_n; t.a_stride_k = a.b_stride_k;
+    t.b = a.a; t.b_stride_k = a.a_stride_k; t.b_stride_n = a.a_stride_m;
+    t.c_stride_m = a.c_stride_n; t.c_stride_n = a.c_stride_m;
+    t.a_scale = a.b_scale; t.b_scale = a.a_scale;
+    tb_config c2 = cfg;
+    c2.swap_ab = 0;
+    rc = gemm_impl(t, &c2, stream, false, true);
+    // Operands TMA cannot address go to the CUDA-core kernel in their original orientation (its bias is per column).
+    if (rc == TB_ERR_ALIGNMENT) return gemm_generic_loader(a, cfg, stream, dev->status);
+    return rc;
+  }
   const int pair = cfg.cta_pair == 2 ? 2 : 1;
   const int bn = cfg.block_n;
   const int mn_atom = 128 / es;
@@ -253,6 +271,7 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
   p.C = a.c; p.ldc_m = a.c_stride_m; p.ldc_n = a.c_stride_n; p.c_dtype = a.c_dtype;
   p.a_scale = a.a_scale; p.b_scale = a.b_scale;
   p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
+  p.bias_along_m = swapped ? 1 : 0;
   p.status = dev->status;
   p.timeout_ns = 2000000000ull;
   if (grouped) {
@@ -326,7 +345,7 @@ static int gemm_impl(const tb_gemm_args& a, const tb_config* user_cfg, cudaStrea
     if (!b_mn) rc = encode_2d(&tbm, a.b_dtype, B, a.k, b_rows, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, 1);
     else rc = encode_2d(&tbm, a.b_dtype, B, a.n, a.k, static_cast<uint64_t>(a.b_stride_k) * es, mn_atom, bk, mn_swz);
   }
-  if (rc == TB_ERR_ALIGNMENT && !grouped) return gemm_generic_loader(a, cfg, stream, dev->status);
+  if (rc == TB_ERR_ALIGNMENT && !grouped && !swapped) return gemm_generic_loader(a, cfg, stream, dev->status);
   if (rc != TB_OK) return rc;
 
 #define TB_LAUNCH(K, C) return launch_gemm<K, C>(ta, tbm, p, programs, smem_bytes, stream)

@@ -55,6 +55,7 @@ struct GemmParams {
   const void* bias;      // (N,) or null
   long long bias_stride;
   int bias_dtype;
+  int bias_along_m;      // 1: bias indexed by row (set when the problem was transposed to C^T = B^T A^T)
   // schedule
   int dp_tiles;  // tiles [0, dp_tiles) are data-parallel: tile = program + i * programs
   int sk_tiles;  // tiles [dp_tiles, dp_tiles + sk_tiles) have their K iterations split evenly over all programs
@@ -585,9 +586,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             for (int j = 0; j < 32; ++j) v[j] *= (col0 + j < p.N) ? p.b_scale[col0 + j] : 1.0f;
           }
           if (p.bias != nullptr) {
+            if (p.bias_along_m) {
+              const float bv = load_as_float(p.bias, row * p.bias_stride, p.bias_dtype);
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] += load_as_float(p.bias, (col0 + j) * p.bias_stride, p.bias_dtype);
+              for (int j = 0; j < 32; ++j) v[j] += bv;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] += load_as_float(p.bias, (col0 + j) * p.bias_stride, p.bias_dtype);
+            }
           }
           store_row_chunk(p, row, col0, v);
         }

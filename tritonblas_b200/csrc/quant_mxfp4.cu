@@ -4,7 +4,8 @@
 //   amax of the block -> (bits + 0x200000) & 0xFF800000 (round up to a power of two when the mantissa is >= 1.75)
 //   -> e = clamp(floor(log2(.)) - 2, -127, 127) -> q = x * 2^-e -> e2m1 by integer operations (denormal shift below
 //   1.0, re-bias, round to nearest with ties away from zero, saturate at 6.0) -> two codes per byte, even element in
-//   the low nibble; scale byte = e + 127.
+//   the low nibble; scale byte = e + 127. The code itself comes from the hardware fp32 -> e2m1 conversion, arranged to
+//   reproduce that rounding exactly (see encode_e2m1x8).
 // The rotation has no reference counterpart; its operation order is fixed so results are reproducible bit for bit:
 //   fp32 butterflies with strides 1, 2, 4, 8, 16, each (a, b) -> (a + b, a - b), no fused multiply-add, then one fp32
 //   multiply by 0.17677669529663687 (1/sqrt(32)).
@@ -82,20 +83,25 @@ __device__ __forceinline__ void hadamard32(float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(v[i], 0.17677669529663687f);
 }
 
-// fp32 (already divided by the block scale) -> 4-bit e2m1 code, by the reference's integer recipe.
-__device__ __forceinline__ uint32_t encode_e2m1(float q) {
-  const uint32_t bits = __float_as_uint(q);
-  const uint32_t sign = (bits >> 28) & 0x8u;
-  uint32_t ex = (bits >> 23) & 0xFFu;
-  uint32_t man = bits & 0x7FFFFFu;
-  if (ex < 127u) {
-    const uint32_t shift = 126u - ex;  // 127 - (ex + 1)
-    man = shift < 32u ? ((0x400000u | (man >> 1)) >> shift) : 0u;
-  }
-  ex = (ex > 126u ? ex : 126u) - 126u;
-  uint32_t code = (((ex << 2) | (man >> 21)) + 1u) >> 1;
-  code = code < 7u ? code : 7u;
-  return sign | code;
+// Eight fp32 values (already divided by the block scale) -> eight e2m1 codes, v[0] in the lowest nibble.
+// The reference's integer recipe is round-to-nearest with ties away from zero and saturation at 6.0. The hardware
+// conversion rounds ties to even, so the lowest mantissa bit of every input is set first: an exact tie (whose low bits
+// are zero) moves one ulp up and rounds away from zero, while no other value can reach or cross a tie by gaining one
+// ulp (a tie has that bit clear). Signs, -0.0 and saturation behave as in the recipe.
+__device__ __forceinline__ uint32_t encode_e2m1x8(const float (&v)[8]) {
+  float a[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a[i] = __uint_as_float(__float_as_uint(v[i]) | 1u);
+  uint32_t r;
+  asm("{\n\t.reg .b8 t0, t1, t2, t3;\n\t.reg .b16 h0, h1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n\t"
+      "mov.b16 h0, {t0, t1};\n\tmov.b16 h1, {t2, t3};\n\tmov.b32 %0, {h0, h1};\n\t}"
+      : "=r"(r)
+      : "f"(a[0]), "f"(a[1]), "f"(a[2]), "f"(a[3]), "f"(a[4]), "f"(a[5]), "f"(a[6]), "f"(a[7]));
+  return r;
 }
 
 // Byte offset of the scale of (row, K block) in atom order [row / 128][block / 4][512].
@@ -150,11 +156,13 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const T* __restrict__ 
     e = e < -127 ? -127 : (e > 127 ? 127 : e);
     // 2^-e as bits (2^-127 is the denormal 0x00400000)
     const float inv_scale = __uint_as_float(e == 127 ? 0x00400000u : static_cast<uint32_t>(127 - e) << 23);
-    uint32_t packed[4] = {0u, 0u, 0u, 0u};
+    uint32_t packed[4];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const uint32_t code = encode_e2m1(__fmul_rn(v[i], inv_scale));
-      packed[i >> 3] |= code << ((i & 7) * 4);
+    for (int w = 0; w < 4; ++w) {
+      float q[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = __fmul_rn(v[w * 8 + i], inv_scale);
+      packed[w] = encode_e2m1x8(q);
     }
     *reinterpret_cast<uint4*>(codes + row * codes_row_stride + blk * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     const unsigned char sbyte = static_cast<unsigned char>((e + 127) & 0xFF);

@@ -48,9 +48,19 @@ struct Candidate {
   int grid, sk_grid, stages, group_m;
 };
 
-int select_config(const tb_problem& p, const MachineModel& hw, tb_config* out) {
-  if (p.m <= 0 || p.n <= 0 || p.k <= 0) return TB_ERR_INVALID;
-  const bool mx = p.mx_block_size == 32 || p.a_dtype == TB_DTYPE_F4;
+int select_config(const tb_problem& p_in, const MachineModel& hw, tb_config* out) {
+  if (p_in.m <= 0 || p_in.n <= 0 || p_in.k <= 0) return TB_ERR_INVALID;
+  const bool mx = p_in.mx_block_size == 32 || p_in.a_dtype == TB_DTYPE_F4;
+  // Few rows of A against a wide B (decode shapes): compute C^T = B^T A^T so the streamed matrix fills the 128-row side
+  // of the tile and the few rows become a narrow tile width; shared memory then holds almost only streamed data.
+  tb_problem p = p_in;
+  const bool swap = !mx && p_in.m <= 64 && p_in.n >= 256 && p_in.n >= 4 * p_in.m;
+  if (swap) {
+    p.m = p_in.n;
+    p.n = p_in.m;
+    p.a_mn_major = p_in.b_mn_major;
+    p.b_mn_major = p_in.a_mn_major;
+  }
   const int es = mx ? 1 : esize_of(p.a_dtype);
   if (es == 0) return TB_ERR_UNSUPPORTED;
   const int sms = (p.num_sms > 0 && p.num_sms <= hw.num_sms) ? p.num_sms : hw.num_sms;
@@ -73,10 +83,14 @@ int select_config(const tb_problem& p, const MachineModel& hw, tb_config* out) {
   const int* widths = mx ? kBNMx : kBNDense;
   for (int pair = 2; pair >= 1; --pair) {
     if (pair == 2 && (sms < 2 || !hw.allow_pair)) continue;
+    // A pair halves each CTA's share of B; with at most 128 rows of A the second CTA of a pair would only multiply
+    // padding, and partial tiles of a stream-K launch would double in size.
+    if (pair == 2 && (p.m <= 128 || p.n <= 64)) continue;
     for (int wi = 0; widths[wi] != 0; ++wi) {
       const int bn = widths[wi];
       const int bn_local = bn / pair;
       if (p.b_mn_major && (bn_local % mn_atom) != 0) continue;
+      if (bn >= 2 * p.n && bn > 32 && !(p.b_mn_major && bn <= mn_atom)) continue;  // more than half the tile would be padding
       if (bn_local < 16) continue;
       const int tile_m = 128 * pair;
       const long long tiles_m = (p.m + tile_m - 1) / tile_m, tiles_n = (p.n + bn - 1) / bn;
@@ -84,24 +98,29 @@ int select_config(const tb_problem& p, const MachineModel& hw, tb_config* out) {
       const int programs = std::max(1, sms / pair);
       const int sf_bytes = mx ? (2 + 2 * 2) * 512 : 0;
       int stages = (hw.smem_optin - 2048) / ((128 * 128 + bn_local * 128 + sf_bytes + 1023) & ~1023);
-      stages = std::min(stages, 8);
+      stages = std::min(stages, 12);
       if (stages < 2) continue;
       const double mma_clk = mma_clk_per_stage_per_bn * bn;
       const double fill_clk = (128.0 + bn_local) * 128.0 / hw.fabric_bytes_per_clk;
       const double stage_clk = std::max(mma_clk, fill_clk);
       const double ramp_clk = hw.tile_ramp_clk;  // first-stage latency + epilogue drain not hidden by the next tile
       const double clk_to_us = 1.0 / (hw.sm_mhz);
+      // HBM floor: one SM cannot pull its share of the full bandwidth alone, so idle SMs cost bandwidth
+      auto hbm_floor = [&](long long active_ctas) {
+        const double share = std::min(1.0, 1.15 * static_cast<double>(active_ctas) / hw.num_sms);
+        return hbm_us / share;
+      };
       // data-parallel
       const long long waves = (tiles + programs - 1) / programs;
       double dp = (waves * nkb * stage_clk + ramp_clk + bn * 8.0) * clk_to_us;
-      dp = std::max(dp, hbm_us) + hw.launch_us;
+      dp = std::max(dp, hbm_floor(std::min<long long>(tiles, programs) * pair)) + hw.launch_us;
       // stream-K: stages per program, plus one partial tile written and read back through L2, plus the flag hop
       const int sk_grid = static_cast<int>(std::min<long long>(programs, tiles * nkb));
       const double per_prog = std::ceil(static_cast<double>(tiles) * nkb / sk_grid);
       const bool needs_fix = (tiles % sk_grid) != 0;
       double sk = (per_prog * stage_clk + ramp_clk + bn * 8.0) * clk_to_us;
       if (needs_fix) sk += 2.0 * 128.0 * bn * 4.0 / (hw.fabric_bytes_per_clk * hw.sm_mhz) + hw.flag_us;
-      sk = std::max(sk, hbm_us) + hw.launch_us;
+      sk = std::max(sk, hbm_floor(static_cast<long long>(sk_grid) * pair)) + hw.launch_us;
       const double cost = p.streamk ? sk : dp;
       // Prefer, on ties, the wider tile and the pair (fewer fabric bytes per flop).
       if (cost < best_cost * 0.995) {
@@ -134,6 +153,7 @@ int select_config(const tb_problem& p, const MachineModel& hw, tb_config* out) {
   out->tmem_cols = next_pow2(2 * best.bn + (mx ? 8 + 8 * 2 : 0));
   out->predicted_us = static_cast<float>(best.dp_us);
   out->predicted_sk_us = static_cast<float>(best.sk_us);
+  out->swap_ab = swap ? 1 : 0;
   return TB_OK;
 }
 

@@ -1,0 +1,155 @@
+"""The two multi-GPU paths of the GEMM family, one process per GPU over torch.distributed (NCCL on GPUs):
+
+  * column-sharded weight GEMM: every rank holds A and a contiguous block of B's columns, computes its block of C and the
+    ranks all-gather C (tensor-parallel column split);
+  * expert-parallel MoE projections: tokens start data-parallel, an all-to-all sends every (token, expert) row to the
+    rank that owns the expert, grouped GEMMs run locally, a second all-to-all returns the rows.
+
+The reference is a single-GPU library (its only collectives are background traffic in benchmarks/overlap.py:221-253), so
+the semantics here are those of the dense / grouped contracts applied per shard. `matmul_fn` / `grouped_fn` default to
+this package's CUDA kernels; the CPU tests of the partition and routing logic pass stand-ins for them.
+"""
+from dataclasses import dataclass
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n: int, world: int, rank: int):
+    """Contiguous [start, stop) of an axis of length n owned by `rank`; earlier ranks take the remainder."""
+    base, rem = divmod(n, world)
+    start = rank * base + min(rank, rem)
+    return start, start + base + (1 if rank < rem else 0)
+
+
+class ColumnShardedGemm:
+    """C = A @ B with B split by columns over the ranks of `group`.
+
+    `b_shard_t` is this rank's block of B stored (n_local, K), K-contiguous. forward(a) returns C as a
+    (world, M, n_local) tensor (rank r's columns in slice r) when all shards have equal width, which is the gathered
+    layout NCCL produces without any extra copy; `as_matrix` materialises the (M, N) matrix when a caller needs it.
+    """
+
+    def __init__(self, b_shard_t: torch.Tensor, group=None, matmul_fn: Optional[Callable] = None):
+        self.b_shard_t = b_shard_t
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if matmul_fn is None:
+            from .matmul import matmul as matmul_fn
+        self.matmul_fn = matmul_fn
+
+    def forward(self, a: torch.Tensor, out_local: Optional[torch.Tensor] = None, gathered: Optional[torch.Tensor] = None):
+        c_local = self.matmul_fn(a, self.b_shard_t.T) if out_local is None else (self.matmul_fn(a, self.b_shard_t.T, out_local) or out_local)
+        if self.world == 1:
+            return c_local.unsqueeze(0)
+        if gathered is None:
+            gathered = c_local.new_empty(self.world, *c_local.shape)
+        # the collective sees the ranks' blocks concatenated along the first axis
+        dist.all_gather_into_tensor(gathered.view(self.world * c_local.shape[0], c_local.shape[1]), c_local.contiguous(),
+                                    group=self.group)
+        return gathered
+
+    @staticmethod
+    def as_matrix(gathered: torch.Tensor) -> torch.Tensor:
+        world, m, n_local = gathered.shape
+        return gathered.permute(1, 0, 2).reshape(m, world * n_local)
+
+
+@dataclass
+class DispatchPlan:
+    """Everything the combine step needs to undo a dispatch."""
+    sort_idx: torch.Tensor          # (T*topk,) positions of the flattened (token, k) pairs in expert order
+    send_counts: torch.Tensor       # (world, experts_per_rank) rows this rank sends, per destination expert
+    recv_counts: torch.Tensor       # (world, experts_per_rank) rows this rank receives, per source rank and local expert
+    send_splits: List[int]
+    recv_splits: List[int]
+    regroup_idx: Optional[torch.Tensor]   # received rows (source-major) -> expert-major order
+    group_offsets: torch.Tensor     # int32 (experts_per_rank + 1,) row offsets of the expert-major buffer
+
+
+def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None) -> DispatchPlan:
+    """Sort the (token, k) pairs of this rank by expert and exchange per-expert row counts with the other ranks."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    assert num_experts % world == 0, "experts must divide evenly over the ranks"
+    epr = num_experts // world
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    sort_idx = torch.argsort(flat, stable=True)
+    send_counts = torch.bincount(flat, minlength=num_experts).reshape(world, epr)
+    if world > 1:
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=group)
+    else:
+        recv_counts = send_counts.clone()
+    send_splits = send_counts.sum(1).tolist()
+    recv_splits = recv_counts.sum(1).tolist()
+    # received rows arrive source-major, each source's rows expert-sorted; regroup them expert-major
+    per_expert = recv_counts.sum(0)
+    group_offsets = torch.zeros(epr + 1, dtype=torch.int32, device=topk_ids.device)
+    group_offsets[1:] = per_expert.cumsum(0).to(torch.int32)
+    regroup_idx = None
+    if world > 1:
+        total = int(sum(recv_splits))
+        seg_start_src = (recv_counts.reshape(-1).cumsum(0) - recv_counts.reshape(-1)).reshape(world, epr)   # source-major
+        counts_em = recv_counts.T.contiguous()                                                           # (epr, world)
+        seg_start_dst = (counts_em.reshape(-1).cumsum(0) - counts_em.reshape(-1)).reshape(epr, world)     # expert-major
+        seg_len = counts_em.reshape(-1)
+        seg_src = seg_start_src.T.contiguous().reshape(-1)
+        seg_id = torch.repeat_interleave(torch.arange(seg_len.numel(), device=seg_len.device), seg_len, output_size=total)
+        within = torch.arange(total, device=seg_len.device) - seg_start_dst.reshape(-1)[seg_id]
+        regroup_idx = seg_src[seg_id] + within
+    return DispatchPlan(sort_idx, send_counts, recv_counts, send_splits, recv_splits, regroup_idx, group_offsets)
+
+
+def dispatch(x: torch.Tensor, topk: int, plan: DispatchPlan, group=None) -> torch.Tensor:
+    """Rows of x (T, H), replicated topk times and ordered by expert, sent to the experts' owners. Returns the rows this
+    rank's experts must process, expert-major (aligned with plan.group_offsets)."""
+    rows = x[plan.sort_idx // topk]
+    if plan.regroup_idx is None:
+        return rows
+    recv = rows.new_empty(int(sum(plan.recv_splits)), x.shape[1])
+    dist.all_to_all_single(recv, rows, plan.recv_splits, plan.send_splits, group=group)
+    return recv[plan.regroup_idx]
+
+
+def combine(y: torch.Tensor, topk_weights: torch.Tensor, plan: DispatchPlan, group=None) -> torch.Tensor:
+    """Inverse of dispatch for the experts' outputs y (expert-major), followed by the top-k weighted sum per token."""
+    tokens, topk = topk_weights.shape
+    if plan.regroup_idx is not None:
+        src_major = torch.empty_like(y)
+        src_major[plan.regroup_idx] = y
+        back = y.new_empty(int(sum(plan.send_splits)), y.shape[1])
+        dist.all_to_all_single(back, src_major, plan.send_splits, plan.recv_splits, group=group)
+    else:
+        back = y
+    unsorted = torch.empty_like(back)
+    unsorted[plan.sort_idx] = back
+    return (unsorted.reshape(tokens, topk, -1).float() * topk_weights.unsqueeze(-1).float()).sum(1).to(y.dtype)
+
+
+def swiglu(h: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for h = [gate | up]; the activation sits between the two projections and is outside the GEMM
+    contract (elementwise torch ops)."""
+    gate, up = h.chunk(2, dim=-1)
+    return torch.nn.functional.silu(gate.float()).mul_(up.float()).to(h.dtype)
+
+
+class ExpertParallelMoE:
+    """Expert-parallel MoE feed-forward: gate/up projection, SwiGLU, down projection, with all-to-all token dispatch.
+
+    w1: (experts_per_rank, 2*ffn, hidden) and w2: (experts_per_rank, hidden, ffn) hold this rank's experts, K-contiguous.
+    """
+
+    def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, group=None, grouped_fn: Optional[Callable] = None):
+        self.w1, self.w2, self.num_experts, self.group = w1, w2, num_experts, group
+        if grouped_fn is None:
+            from .matmul import grouped_matmul as grouped_fn
+        self.grouped_fn = grouped_fn
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor):
+        plan = plan_dispatch(topk_ids, self.num_experts, self.group)
+        rows = dispatch(x, topk_ids.shape[1], plan, self.group)
+        h = self.grouped_fn(rows, self.w1, plan.group_offsets)
+        y = self.grouped_fn(swiglu(h), self.w2, plan.group_offsets)
+        return combine(y, topk_weights, plan, self.group), plan
