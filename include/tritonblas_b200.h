@@ -111,6 +111,24 @@ int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override);
 /* Enqueue one GEMM. `cfg` may be NULL (the library selects). */
 int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);
 
+/* Stream-K GEMM for callers that cannot allocate device memory: a serving process that handed all of HBM to its own
+ * arena at start-up, or a latency path on which cudaMalloc (which synchronises the whole device) is not allowed, has no
+ * way to size and own the partial-tile workspace tb_gemm asks for. This entry point takes no workspace: flags and fp32
+ * partial tiles live in an array that is part of the library image (4 KB + 10 MB per GPU that loads the library, held
+ * until the process exits), and the failure word its kernels write is built in as well. It calls no allocator (no
+ * cudaMalloc / cudaFree, no torch). It has no counterpart in the reference.
+ *   - Same arguments as tb_gemm with streamk = 1; args->workspace / workspace_bytes / epoch are ignored. Operands must be
+ *     K-contiguous f16, bf16 or e4m3; output f16, bf16 or f32.
+ *   - Limit: programs x 128 x block_n x 4 bytes (x2 for a CTA pair) of partial tiles must fit 10 MB; a launch that needs
+ *     more returns TB_ERR_WORKSPACE and tb_last_cuda_error() says by how much (lower args->sk_grid, or use tb_gemm).
+ *   - The first call on a device looks up the device addresses of the built-in arrays; make that first call before any
+ *     stream capture begins.
+ *   - All calls on a device share the one array, which keeps the previous call's contents (the flags are cleared at the
+ *     start of every call, on `stream`): two calls whose kernels overlap on the GPU (different streams) race.
+ *   - prev_status, when not NULL, receives and clears the failure code recorded by earlier calls on this device; reading
+ *     it waits for `stream`. Pass NULL to stay asynchronous. */
+int tb_gemm_streamk_builtin(const tb_gemm_args* args, const tb_config* cfg, void* stream, int32_t* prev_status);
+
 /* Grouped GEMM over row groups of A (expert-parallel MoE projections). No reference counterpart: its semantics are the
  * dense contract of tb_gemm applied per group. A and every B_g must be K-contiguous; data-parallel schedule only. */
 int tb_grouped_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);

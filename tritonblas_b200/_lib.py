@@ -76,6 +76,9 @@ def _load():
     lib.tb_gemm_workspace_bytes.restype = ctypes.c_int64
     lib.tb_gemm.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p]
     lib.tb_gemm.restype = ctypes.c_int
+    lib.tb_gemm_streamk_builtin.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p,
+                                            ctypes.POINTER(ctypes.c_int32)]
+    lib.tb_gemm_streamk_builtin.restype = ctypes.c_int
     lib.tb_grouped_gemm.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p]
     lib.tb_grouped_gemm.restype = ctypes.c_int
     lib.tb_gemm_mxfp4.argtypes = [ctypes.POINTER(Mxfp4Args), ctypes.c_void_p]

@@ -436,6 +436,168 @@ static int gemm_mxfp4_impl(const tb_mxfp4_args& a, cudaStream_t stream) {
   return launch_gemm<3, 2>(ta, tbm, p, programs, smem_bytes, stream, &tsfa, &tsfb);
 }
 
+// ---------------------------------------------------------------- stream-K GEMM on built-in scratch (allocates nothing)
+// Flags (4 KB) followed by the fp32 partial tiles, in a device array that is part of the library image: every GPU that
+// loads the library holds these bytes until the process exits.
+constexpr size_t kBuiltinFlagBytes = 4096;
+constexpr size_t kBuiltinPartialBytes = 10u * 1024u * 1024u;
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinFlagBytes + kBuiltinPartialBytes];
+static __device__ int g_builtin_status;
+
+struct BuiltinState {
+  bool ready = false;
+  unsigned char* scratch = nullptr;  // device address of g_builtin_scratch on this device
+  int* status = nullptr;             // device address of g_builtin_status on this device
+  int num_sms = 0;
+  int smem_optin = 0;
+};
+static BuiltinState g_builtin[64];
+static std::mutex g_builtin_mu;
+
+// Once per device, with that device current. In host code the array's name only stands for the symbol; the address a
+// kernel can use has to be asked for.
+static int builtin_state(BuiltinState** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return TB_ERR_NO_DEVICE;
+  }
+  if (dev < 0 || dev >= 64) return TB_ERR_INVALID;
+  std::lock_guard<std::mutex> lk(g_builtin_mu);
+  BuiltinState& st = g_builtin[dev];
+  if (!st.ready) {
+    void* p = nullptr;
+    if ((e = cudaGetSymbolAddress(&p, g_builtin_scratch)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(scratch)");
+    st.scratch = static_cast<unsigned char*>(p);
+    if ((e = cudaGetSymbolAddress(&p, g_builtin_status)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status)");
+    st.status = static_cast<int*>(p);
+    cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&st.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+      if (e != cudaSuccess || fn == nullptr) return cuda_fail(e, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    }
+    st.ready = true;
+  }
+  *out = &st;
+  return TB_OK;
+}
+
+static int gemm_streamk_builtin_impl(const tb_gemm_args& in, const tb_config* user_cfg, cudaStream_t stream,
+                                     int32_t* prev_status) {
+  if (in.m <= 0 || in.n <= 0 || in.k <= 0) return TB_ERR_INVALID;
+  if (in.a == nullptr || in.b == nullptr || in.c == nullptr) return TB_ERR_INVALID;
+  if (in.a_dtype != in.b_dtype) return TB_ERR_UNSUPPORTED;
+  if (in.a_dtype != TB_DTYPE_F16 && in.a_dtype != TB_DTYPE_BF16 && in.a_dtype != TB_DTYPE_E4M3) return TB_ERR_UNSUPPORTED;
+  if (in.c_dtype != TB_DTYPE_F16 && in.c_dtype != TB_DTYPE_BF16 && in.c_dtype != TB_DTYPE_F32) return TB_ERR_UNSUPPORTED;
+  // K-contiguous operands only (the layout decode weights are kept in)
+  if ((in.a_stride_k != 1 && in.k != 1) || (in.b_stride_k != 1 && in.k != 1)) return TB_ERR_UNSUPPORTED;
+  BuiltinState* st = nullptr;
+  int rc = builtin_state(&st);
+  if (rc != TB_OK) return rc;
+  if (prev_status != nullptr) {
+    // Outcome of the work enqueued before this call (waits for `stream`), then cleared.
+    int v = 0;
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e == cudaSuccess) e = cudaMemcpy(&v, st->status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && v != 0) e = cudaMemset(st->status, 0, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e, "tb_gemm_streamk_builtin(status read)");
+    *prev_status = v;
+  }
+  const int es = in.a_dtype == TB_DTYPE_E4M3 ? 1 : 2;
+  MachineModel hw;
+  hw.num_sms = st->num_sms;
+  hw.smem_optin = st->smem_optin;
+  tb_config cfg;
+  if (user_cfg != nullptr) {
+    cfg = *user_cfg;
+  } else {
+    tb_problem pr = {};
+    pr.m = in.m; pr.n = in.n; pr.k = in.k;
+    pr.a_dtype = in.a_dtype; pr.b_dtype = in.b_dtype; pr.c_dtype = in.c_dtype;
+    pr.streamk = 1;
+    rc = select_config(pr, hw, &cfg);
+    if (rc != TB_OK) return rc;
+  }
+  tb_gemm_args a = in;
+  const bool swapped = cfg.swap_ab != 0;
+  if (swapped) {  // C^T = B^T A^T, as in the regular entry point
+    a.m = in.n; a.n = in.m;
+    a.a = in.b; a.a_stride_m = in.b_stride_n; a.a_stride_k = in.b_stride_k;
+    a.b = in.a; a.b_stride_k = in.a_stride_k; a.b_stride_n = in.a_stride_m;
+    a.c_stride_m = in.c_stride_n; a.c_stride_n = in.c_stride_m;
+    a.a_scale = in.b_scale; a.b_scale = in.a_scale;
+  }
+  const int pair = cfg.cta_pair == 2 ? 2 : 1;
+  const int bn = cfg.block_n;
+  if (bn < 32 || bn > 256 || (bn % 32) != 0 || ((bn / pair) % 16) != 0 || cfg.block_m != 128 * pair) return TB_ERR_INVALID;
+  const int bk = 128 / es;
+  int stages = cfg.stages < 2 ? 2 : cfg.stages;
+  while (stages > 2 && smem_bytes_for(bn, pair, stages) > st->smem_optin) --stages;
+  const int smem_bytes = smem_bytes_for(bn, pair, stages);
+  if (smem_bytes > st->smem_optin) return TB_ERR_INVALID;
+
+  GemmParams p = {};
+  p.M = a.m; p.N = a.n; p.K = a.k;
+  p.block_n = bn;
+  p.k_per_stage = bk;
+  p.num_k_blocks = (a.k + bk - 1) / bk;
+  p.tiles_m = (a.m + 128 * pair - 1) / (128 * pair);
+  p.tiles_n = (a.n + bn - 1) / bn;
+  p.group_m = cfg.group_m > 0 ? cfg.group_m : 8;
+  p.stages = stages;
+  p.esize = es;
+  int tc = 32;
+  while (tc < 2 * bn) tc <<= 1;
+  p.tmem_cols = static_cast<uint32_t>(tc);
+  p.C = a.c; p.ldc_m = a.c_stride_m; p.ldc_n = a.c_stride_n; p.c_dtype = a.c_dtype;
+  p.a_scale = a.a_scale; p.b_scale = a.b_scale;
+  p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
+  p.bias_along_m = swapped ? 1 : 0;
+  p.status = st->status;
+  p.timeout_ns = 2000000000ull;
+  const uint32_t fmt = in.a_dtype == TB_DTYPE_BF16 ? 1u : 0u;  // f16 = 0, bf16 = 1, e4m3 = 0
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
+            (static_cast<uint32_t>((128 * pair) >> 4) << 24);
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const int max_programs = st->num_sms / pair;
+  int programs = in.sk_grid > 0 ? in.sk_grid : cfg.sk_grid;
+  if (programs <= 0 || programs > max_programs) programs = max_programs;
+  if (programs > tiles * p.num_k_blocks) programs = static_cast<int>(tiles * p.num_k_blocks);
+  if (programs < 1) programs = 1;
+  p.sk_tiles = static_cast<int>(tiles % programs);
+  p.dp_tiles = static_cast<int>(tiles - p.sk_tiles);
+  const size_t need = static_cast<size_t>(programs) * pair * 128 * static_cast<size_t>(bn) * 4;
+  if (need > kBuiltinPartialBytes) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err),
+             "built-in stream-K scratch holds %zu bytes of partial tiles, this launch needs %zu (%d programs x %d x 128 x %d "
+             "fp32); pass a smaller sk_grid or use tb_gemm with a caller workspace",
+             kBuiltinPartialBytes, need, programs, pair, bn);
+    return TB_ERR_WORKSPACE;
+  }
+  p.flags = reinterpret_cast<unsigned*>(st->scratch);
+  p.partials = reinterpret_cast<float*>(st->scratch + kBuiltinFlagBytes);
+  p.epoch = 1;
+  // The array keeps the previous call's contents: the flags must start at zero (the partial tiles are overwritten
+  // before they are read).
+  cudaError_t e = cudaMemsetAsync(st->scratch, 0, kBuiltinFlagBytes, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(flags)");
+
+  CUtensorMap ta, tbm;
+  rc = encode_2d(&ta, a.a_dtype, a.a, a.k, a.m, static_cast<uint64_t>(a.a_stride_m) * es, bk, 128, 1);
+  if (rc == TB_OK) rc = encode_2d(&tbm, a.b_dtype, a.b, a.k, a.n, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, 1);
+  if (rc != TB_OK) return rc;
+  const int kind = in.a_dtype == TB_DTYPE_E4M3 ? 2 : 0;
+  if (pair == 1) return kind == 0 ? launch_gemm<0, 1>(ta, tbm, p, programs, smem_bytes, stream)
+                                  : launch_gemm<2, 1>(ta, tbm, p, programs, smem_bytes, stream);
+  return kind == 0 ? launch_gemm<0, 2>(ta, tbm, p, programs, smem_bytes, stream)
+                   : launch_gemm<2, 2>(ta, tbm, p, programs, smem_bytes, stream);
+}
+
 }  // namespace tb
 
 // ====================================================================== exported C ABI
@@ -460,6 +622,11 @@ int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override) 
 int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream) {
   if (args == nullptr) return TB_ERR_INVALID;
   return tb::gemm_impl(*args, cfg, static_cast<cudaStream_t>(stream));
+}
+
+int tb_gemm_streamk_builtin(const tb_gemm_args* args, const tb_config* cfg, void* stream, int32_t* prev_status) {
+  if (args == nullptr) return TB_ERR_INVALID;
+  return tb::gemm_streamk_builtin_impl(*args, cfg, static_cast<cudaStream_t>(stream), prev_status);
 }
 
 int tb_grouped_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream) {
