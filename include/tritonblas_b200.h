@@ -133,6 +133,16 @@ int tb_gemm_streamk_builtin(const tb_gemm_args* args, const tb_config* cfg, void
  * dense contract of tb_gemm applied per group. A and every B_g must be K-contiguous; data-parallel schedule only. */
 int tb_grouped_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);
 
+/* Memory-bound steps around the grouped MoE GEMMs (the reference has no MoE path, so no counterpart):
+ *   tb_swiglu:      out[r, j] = silu(h[r, j]) * h[r, ffn + j] for h = [gate | up] (rows, 2*ffn); fp32 math, one cast.
+ *   tb_moe_combine: out[t, :] = sum_k weights[t, k] * y[pos[t, k], :]; pos = row of y that holds the k-th expert output
+ *                   of token t (int64, tokens x topk), weights fp32 (tokens x topk); fp32 accumulate in k order.
+ * f16 / bf16 data, 16-byte aligned rows, ffn and hidden multiples of 8. */
+int tb_swiglu(const void* h, int64_t h_row_stride, void* out, int64_t out_row_stride, int64_t rows, int32_t ffn,
+              int32_t dtype, void* stream);
+int tb_moe_combine(const void* y, int64_t y_row_stride, const int64_t* pos, const float* weights, void* out,
+                   int64_t out_row_stride, int32_t tokens, int32_t topk, int32_t hidden, int32_t dtype, void* stream);
+
 /* MXFP4 GEMM: C (m, n) = sum over 32-element K blocks of (A_e2m1 * 2^(sa-127)) . (B_e2m1 * 2^(sb-127)), fp32
  * accumulate, one cast. A is (m, k/2) bytes and B is (n, k/2) bytes, two e2m1 codes per byte (even element in the low
  * nibble), K contiguous, row strides in bytes (multiples of 16). Scales are e8m0 bytes in the "atom" arrangement the

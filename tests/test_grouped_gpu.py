@@ -58,3 +58,23 @@ def test_grouped_moe_projection_shapes():
             rms = ref.pow(2).mean().sqrt()
             assert ((got - ref).abs() <= 1e-2 * ref.abs() + 1e-2 * rms).all(), (n, k, r, e)
     assert tb.device_status() == 0
+
+
+def test_swiglu_and_combine_kernels_match_fp32_formulas():
+    from tritonblas_b200 import distributed as tbd
+    g = torch.Generator().manual_seed(3)
+    h = torch.randn(333, 2 * 256, generator=g).to(torch.bfloat16).cuda()
+    got = tbd.swiglu(h).float().cpu()
+    gate, up = h.float().cpu().chunk(2, dim=-1)
+    ref = torch.nn.functional.silu(gate) * up
+    assert torch.allclose(got, ref, rtol=1e-2, atol=1e-2)
+    tokens, topk, hidden, E = 50, 4, 512, 8
+    ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(tokens)]).cuda()
+    plan = tbd.plan_dispatch(ids, E)
+    x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).cuda()
+    rows = tbd.dispatch(x, topk, plan)                       # expert-major copies of the token rows
+    w = torch.rand(tokens, topk, generator=g).cuda()
+    out = tbd.combine(rows, w, plan).float().cpu()
+    ref = x.float().cpu() * w.sum(1, keepdim=True).cpu()     # every copy is the token itself
+    assert torch.allclose(out, ref, rtol=1e-2, atol=1e-2)
+    assert tb.device_status() == 0

@@ -81,6 +81,13 @@ def _load():
     lib.tb_gemm_streamk_builtin.restype = ctypes.c_int
     lib.tb_grouped_gemm.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p]
     lib.tb_grouped_gemm.restype = ctypes.c_int
+    lib.tb_swiglu.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                              ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+    lib.tb_swiglu.restype = ctypes.c_int
+    lib.tb_moe_combine.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                   ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                   ctypes.c_void_p]
+    lib.tb_moe_combine.restype = ctypes.c_int
     lib.tb_gemm_mxfp4.argtypes = [ctypes.POINTER(Mxfp4Args), ctypes.c_void_p]
     lib.tb_gemm_mxfp4.restype = ctypes.c_int
     lib.tb_mxfp4_quant.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,

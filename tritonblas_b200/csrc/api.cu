@@ -215,7 +215,7 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
     cfg = *user_cfg;
   } else {
     tb_problem pr = {};
-    pr.m = grouped ? (a.m + a.num_groups - 1) / a.num_groups : a.m;  // grouped: model the average group
+    pr.m = a.m;  // grouped: tiles of all groups are pooled over the SMs, so the model sees the total row count
     pr.n = a.n; pr.k = a.k;
     pr.a_dtype = a.a_dtype; pr.b_dtype = a.b_dtype; pr.c_dtype = a.c_dtype;
     pr.a_mn_major = a_mn; pr.b_mn_major = b_mn;
@@ -249,7 +249,7 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   const int bk = 128 / es;
   int stages = cfg.stages;
   if (stages < 2) stages = 2;
-  const int extra_smem = grouped ? 4 * (a.num_groups + 2) : 0;  // per-group tile prefix
+  const int extra_smem = grouped ? 8 * (a.num_groups + 2) : 0;  // per-group tile prefix + copy of the row offsets
   while (stages > 2 && smem_bytes_for(bn, pair, stages) + extra_smem > dev->smem_optin) --stages;
   const int smem_bytes = smem_bytes_for(bn, pair, stages) + extra_smem;
   if (smem_bytes > dev->smem_optin) return TB_ERR_INVALID;

@@ -159,7 +159,8 @@ __device__ __forceinline__ TileGeom tile_geometry(const GemmParams& p, int tile,
     if (tile_prefix[mid] <= tile) lo = mid;
     else hi = mid;
   }
-  const int row0 = p.group_offsets[lo], row1 = p.group_offsets[lo + 1];
+  const int* offs = tile_prefix + p.num_groups + 1;  // shared-memory copy of the row offsets
+  const int row0 = offs[lo], row1 = offs[lo + 1];
   const int tiles_m = (row1 - row0 + tile_m - 1) / tile_m;
   tile_coords_dims(tile - tile_prefix[lo], tiles_m, p.tiles_n, p.group_m, tm, tn);
   g.m0 = row0 + tm * tile_m;
@@ -285,12 +286,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     mbar_init(publish_bar, 4);
     mbar_fence_init();
     if (p.group_offsets != nullptr) {
+      // tile_prefix[0 .. G] = tiles before each group, followed by a copy of the G + 1 row offsets
       int acc_tiles = 0;
+      int* offs = tile_prefix + p.num_groups + 1;
       tile_prefix[0] = 0;
+      int row0 = p.group_offsets[0];
+      offs[0] = row0;
       for (int g = 0; g < p.num_groups; ++g) {
-        const int rows = p.group_offsets[g + 1] - p.group_offsets[g];
-        acc_tiles += ((rows + kTileM * CTAS - 1) / (kTileM * CTAS)) * p.tiles_n;
+        const int row1 = p.group_offsets[g + 1];
+        offs[g + 1] = row1;
+        acc_tiles += ((row1 - row0 + kTileM * CTAS - 1) / (kTileM * CTAS)) * p.tiles_n;
         tile_prefix[g + 1] = acc_tiles;
+        row0 = row1;
       }
     }
     prefetch_tmap(&tmap_a);

@@ -1,0 +1,160 @@
+// Memory-bound helpers on either side of the grouped MoE GEMMs (no reference counterpart; the reference has no MoE path):
+//   swiglu:   out[r, j] = silu(h[r, j]) * h[r, F + j]            (h = [gate | up], fp32 math, one cast)
+//   combine:  out[t, :] = sum_k w[t, k] * y[pos[t, k], :]        (top-k weighted sum of expert outputs, fp32 accumulate
+//                                                                 in k order, one cast)
+// Both stream their inputs once with 16-byte accesses: swiglu moves 6 bytes per output element, combine 2 * (topk + 1).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common_host.h"
+
+namespace tb {
+namespace {
+
+template <typename T>
+struct Vec8;
+template <>
+struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 w = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = __uint_as_float(u[j] << 16);
+      v[2 * j + 1] = __uint_as_float(u[j] & 0xFFFF0000u);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint32_t u[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      u[j] = *reinterpret_cast<uint32_t*>(&t);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(u[0], u[1], u[2], u[3]);
+  }
+};
+template <>
+struct Vec8<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
+    const uint4 w = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[j]));
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__half* p, const float (&v)[8]) {
+    uint32_t u[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __half2 t = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      u[j] = *reinterpret_cast<uint32_t*>(&t);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(u[0], u[1], u[2], u[3]);
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ h, long long h_stride, T* __restrict__ out,
+                                                       long long out_stride, long long rows, int ffn) {
+  const int vec_per_row = ffn / 8;
+  const long long total = rows * vec_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i - r * vec_per_row) * 8;
+    float g[8], u[8], o[8];
+    Vec8<T>::load(h + r * h_stride + c, g);
+    Vec8<T>::load(h + r * h_stride + ffn + c, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
+    Vec8<T>::store(out + r * out_stride + c, o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ y, long long y_stride,
+                                                        const long long* __restrict__ pos, const float* __restrict__ w,
+                                                        T* __restrict__ out, long long out_stride, int tokens, int topk,
+                                                        int hidden) {
+  const int vec_per_row = hidden / 8;
+  const long long total = static_cast<long long>(tokens) * vec_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / vec_per_row);
+    const int c = static_cast<int>(i - static_cast<long long>(t) * vec_per_row) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < topk; ++k) {
+      const long long src = pos[static_cast<long long>(t) * topk + k];
+      const float wk = w[static_cast<long long>(t) * topk + k];
+      float v[8];
+      Vec8<T>::load(y + src * y_stride + c, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(v[j], wk, acc[j]);
+    }
+    Vec8<T>::store(out + static_cast<long long>(t) * out_stride + c, acc);
+  }
+}
+
+int grid_for(long long work_items) {
+  long long blocks = (work_items + 255) / 256;
+  const long long cap = 148LL * 8 * 8;
+  if (blocks > cap) blocks = cap;
+  return static_cast<int>(blocks < 1 ? 1 : blocks);
+}
+
+bool aligned16(const void* p, long long stride_elems) {
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && ((stride_elems * 2) & 15) == 0;
+}
+
+}  // namespace
+}  // namespace tb
+
+extern "C" int tb_swiglu(const void* h, int64_t h_row_stride, void* out, int64_t out_row_stride, int64_t rows, int32_t ffn,
+                         int32_t dtype, void* stream) {
+  if (h == nullptr || out == nullptr || rows < 0 || ffn <= 0 || (ffn % 8) != 0) return TB_ERR_INVALID;
+  if (rows == 0) return TB_OK;
+  if (!tb::aligned16(h, h_row_stride) || !tb::aligned16(out, out_row_stride) || ((ffn * 2) & 15) != 0) return TB_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = tb::grid_for(rows * (ffn / 8));
+  if (dtype == TB_DTYPE_BF16)
+    tb::swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h), h_row_stride,
+                                                          static_cast<__nv_bfloat16*>(out), out_row_stride, rows, ffn);
+  else if (dtype == TB_DTYPE_F16)
+    tb::swiglu_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(h), h_row_stride, static_cast<__half*>(out),
+                                                   out_row_stride, rows, ffn);
+  else
+    return TB_ERR_UNSUPPORTED;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return tb::cuda_fail(e, "swiglu_kernel launch");
+  tb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return TB_OK;
+}
+
+extern "C" int tb_moe_combine(const void* y, int64_t y_row_stride, const int64_t* pos, const float* weights, void* out,
+                              int64_t out_row_stride, int32_t tokens, int32_t topk, int32_t hidden, int32_t dtype,
+                              void* stream) {
+  if (y == nullptr || pos == nullptr || weights == nullptr || out == nullptr) return TB_ERR_INVALID;
+  if (tokens < 0 || topk <= 0 || hidden <= 0 || (hidden % 8) != 0) return TB_ERR_INVALID;
+  if (tokens == 0) return TB_OK;
+  if (!tb::aligned16(y, y_row_stride) || !tb::aligned16(out, out_row_stride)) return TB_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = tb::grid_for(static_cast<long long>(tokens) * (hidden / 8));
+  if (dtype == TB_DTYPE_BF16)
+    tb::combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(y), y_row_stride,
+                                                           reinterpret_cast<const long long*>(pos), weights,
+                                                           static_cast<__nv_bfloat16*>(out), out_row_stride, tokens, topk, hidden);
+  else if (dtype == TB_DTYPE_F16)
+    tb::combine_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(y), y_row_stride,
+                                                    reinterpret_cast<const long long*>(pos), weights,
+                                                    static_cast<__half*>(out), out_row_stride, tokens, topk, hidden);
+  else
+    return TB_ERR_UNSUPPORTED;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return tb::cuda_fail(e, "combine_kernel launch");
+  tb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return TB_OK;
+}

@@ -114,7 +114,8 @@ def dispatch(x: torch.Tensor, topk: int, plan: DispatchPlan, group=None) -> torc
 
 
 def combine(y: torch.Tensor, topk_weights: torch.Tensor, plan: DispatchPlan, group=None) -> torch.Tensor:
-    """Inverse of dispatch for the experts' outputs y (expert-major), followed by the top-k weighted sum per token."""
+    """Inverse of dispatch for the experts' outputs y (expert-major), followed by the top-k weighted sum per token
+    (fp32 accumulate in k order, one cast)."""
     tokens, topk = topk_weights.shape
     if plan.regroup_idx is not None:
         src_major = torch.empty_like(y)
@@ -123,16 +124,45 @@ def combine(y: torch.Tensor, topk_weights: torch.Tensor, plan: DispatchPlan, gro
         dist.all_to_all_single(back, src_major, plan.send_splits, plan.recv_splits, group=group)
     else:
         back = y
-    unsorted = torch.empty_like(back)
-    unsorted[plan.sort_idx] = back
-    return (unsorted.reshape(tokens, topk, -1).float() * topk_weights.unsqueeze(-1).float()).sum(1).to(y.dtype)
+    # position of every (token, k) pair in the expert-sorted order: the inverse of sort_idx
+    pos = torch.empty_like(plan.sort_idx)
+    pos[plan.sort_idx] = torch.arange(plan.sort_idx.numel(), device=plan.sort_idx.device)
+    if back.is_cuda:
+        return _combine_cuda(back, pos, topk_weights, tokens, topk)
+    return (back[pos].reshape(tokens, topk, -1).float() * topk_weights.unsqueeze(-1).float()).sum(1).to(y.dtype)
+
+
+def _combine_cuda(back, pos, topk_weights, tokens, topk):
+    import ctypes
+    from . import _lib
+    back = back if back.stride(1) == 1 else back.contiguous()
+    w = topk_weights.to(torch.float32).contiguous()
+    out = back.new_empty(tokens, back.shape[1])
+    with torch.cuda.device(back.device):
+        rc = _lib.lib.tb_moe_combine(ctypes.c_void_p(back.data_ptr()), back.stride(0), ctypes.c_void_p(pos.data_ptr()),
+                                     ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(out.data_ptr()), out.stride(0),
+                                     tokens, topk, back.shape[1], _lib.DTYPE_CODE[back.dtype],
+                                     _lib.current_stream_ptr(back.device))
+    _lib.check(rc, "tb_moe_combine")
+    return out
 
 
 def swiglu(h: torch.Tensor) -> torch.Tensor:
-    """silu(gate) * up for h = [gate | up]; the activation sits between the two projections and is outside the GEMM
-    contract (elementwise torch ops)."""
-    gate, up = h.chunk(2, dim=-1)
-    return torch.nn.functional.silu(gate.float()).mul_(up.float()).to(h.dtype)
+    """silu(gate) * up for h = [gate | up] (fp32 math, one cast); the activation sits between the two projections and is
+    outside the GEMM contract. One streaming CUDA kernel on the GPU; the CPU form serves the gloo tests."""
+    if not h.is_cuda:
+        gate, up = h.chunk(2, dim=-1)
+        return torch.nn.functional.silu(gate.float()).mul_(up.float()).to(h.dtype)
+    import ctypes
+    from . import _lib
+    h = h if h.stride(1) == 1 else h.contiguous()
+    ffn = h.shape[1] // 2
+    out = h.new_empty(h.shape[0], ffn)
+    with torch.cuda.device(h.device):
+        rc = _lib.lib.tb_swiglu(ctypes.c_void_p(h.data_ptr()), h.stride(0), ctypes.c_void_p(out.data_ptr()), out.stride(0),
+                                h.shape[0], ffn, _lib.DTYPE_CODE[h.dtype], _lib.current_stream_ptr(h.device))
+    _lib.check(rc, "tb_swiglu")
+    return out
 
 
 class ExpertParallelMoE:

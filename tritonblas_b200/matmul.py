@@ -250,7 +250,8 @@ def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None):
     x = x if x.stride(1) == 1 else x.contiguous()
     w = w if w.is_contiguous() else w.contiguous()
     group_offsets = group_offsets.contiguous()
-    selector = _make_matmul_selector(max(rows // G, 1), N, K, x.dtype, w.dtype, out.dtype, x.device)
+    # tiles of all groups are pooled over the SMs, so the tile model sees the total row count
+    selector = _make_matmul_selector(rows, N, K, x.dtype, w.dtype, out.dtype, x.device)
     cfg = selector.config_for(False, False)
     args = _lib.GemmArgs()
     args.m, args.n, args.k = rows, N, K
