@@ -203,6 +203,13 @@ class DenseWorkload:
         self.C = [torch.empty(M, self.n_local, dtype=self.out_dtype, device=dev) for _ in range(min(nsets, 4))]
         self.C_host = torch.empty(M, self.n_local, dtype=self.out_dtype).pin_memory()
         self.Cg = torch.empty(world * M, self.n_local, dtype=self.out_dtype, device=dev) if world > 1 else None
+        self.layers = None
+        if world > 1 and not self.fp8 and not args.nccl_gather:
+            # fused path: the GEMM epilogue pushes every tile into all ranks' gathered buffers (symmetric memory)
+            from tritonblas_b200 import distributed as tbd
+            self.layers = [tbd.ColumnShardedGemm(bt) for bt in self.Bt]
+            for layer in self.layers:
+                layer.enable_fused_gather(M, self.out_dtype)
         self.sel = tb.OrigamiMatmulSelector(M, self.n_local, K, self.in_dtype, self.in_dtype, self.out_dtype, dev,
                                             streamk=self.streamk)
         self.cfg = tb.matmul_preamble(self.sel)
@@ -218,7 +225,17 @@ class DenseWorkload:
                       + (", stream-K" if self.streamk else ""))
         self.extra = {"tile": f"{self.sel.block_m}x{self.sel.block_n}x{self.sel.block_k}", "cta_pair": self.sel.cta_pair,
                       "operand_sets": nsets,
-                      "parallelism": f"N-sharded x{world} + NCCL all-gather of C" if world > 1 else "single GPU"}
+                      "parallelism": (f"N-sharded x{world}, " + ("epilogue pushes C tiles to all ranks over NVLink "
+                                      "(symmetric memory) + barrier" if self.layers else "NCCL all-gather of C"))
+                      if world > 1 else "single GPU"}
+        # end-to-end leg: copies and compute on separate streams, double-buffered device operands
+        self.s_in, self.s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self.a_dev = [torch.empty_like(self.A[0]) for _ in range(2)]
+        self.b_dev = [torch.empty_like(self.Bt[0]) for _ in range(2)]
+        self.c_dev = [torch.empty(M, self.n_local, dtype=self.out_dtype, device=dev) for _ in range(2)]
+        self.ev_in = [None, None]
+        self.ev_c = [None, None]
+        self.ev_out = [None, None]
 
     def gemm(self, i, a=None, b_t=None, c=None):
         s = i % self.nsets
@@ -232,22 +249,45 @@ class DenseWorkload:
         return c
 
     def step(self, i, dist):
+        if self.layers is not None:
+            self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets])
+            return
         c = self.gemm(i)
         if self.world > 1:
             dist.all_gather_into_tensor(self.Cg, c)
 
     def e2e_step(self, i, dist):
-        s = i % self.nsets
-        a = self.A_host[s].to(self.dev, non_blocking=True)
-        b = self.B_host[s].to(self.dev, non_blocking=True)
+        """Host operands in, host result out, through the public API. H2D of step i+1 and D2H of step i-1 run on their own
+        streams beside the GEMM of step i; every step still copies its own inputs and its own result."""
+        s, j = i % self.nsets, i % 2
+        main = torch.cuda.current_stream()
+        with torch.cuda.stream(self.s_in):
+            if self.ev_c[j] is not None:
+                self.s_in.wait_event(self.ev_c[j])          # the GEMM that last read these device operands is done
+            self.a_dev[j].copy_(self.A_host[s], non_blocking=True)
+            self.b_dev[j].copy_(self.B_host[s], non_blocking=True)
+            self.ev_in[j] = self.s_in.record_event()
+        main.wait_event(self.ev_in[j])
+        if self.ev_out[j] is not None:
+            main.wait_event(self.ev_out[j])                 # the previous result in this buffer has left for the host
+        c = self.c_dev[j]
         if self.fp8:
-            c = torch.empty(self.M, self.n_local, dtype=self.out_dtype, device=self.dev)
-            self.tb.matmul_a8w8(a, b.T, self.a_s[s], self.b_s[s], c, enable_streamk=self.streamk)
+            self.tb.matmul_a8w8(self.a_dev[j], self.b_dev[j].T, self.a_s[s], self.b_s[s], c, enable_streamk=self.streamk)
         else:
-            c = self.tb.matmul(a, b.T, enable_streamk=self.streamk)
+            self.tb.matmul(self.a_dev[j], self.b_dev[j].T, out=c, enable_streamk=self.streamk)
         if self.world > 1:
             dist.all_gather_into_tensor(self.Cg, c)
-        self.C_host.copy_(c, non_blocking=True)
+        self.ev_c[j] = main.record_event()
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.ev_c[j])
+            self.C_host.copy_(c, non_blocking=True)
+            self.ev_out[j] = self.s_out.record_event()
+
+    def e2e_finish(self):
+        main = torch.cuda.current_stream()
+        for ev in self.ev_out:
+            if ev is not None:
+                main.wait_event(ev)
 
 
 class Mxfp4Workload:
@@ -352,6 +392,8 @@ def main():
     ap.add_argument("--gemms-per-step", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-operand leg (profiling runs)")
+    ap.add_argument("--nccl-gather", action="store_true",
+                    help="multi-GPU default workload: gather C with NCCL after the GEMM instead of the fused epilogue push")
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
@@ -429,6 +471,8 @@ def main():
     e0.record(stream)
     for i in range(e2e_steps):
         w.e2e_step(i, dist)
+    if hasattr(w, "e2e_finish"):
+        w.e2e_finish()          # the last results' device-to-host copies are inside the timed region
     e1.record(stream)
     barrier()
     e2e_ms = max(e0.elapsed_time(e1), 1e-6)

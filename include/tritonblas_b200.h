@@ -98,6 +98,12 @@ typedef struct tb_gemm_args {
    * same rows of C. group_offsets is a DEVICE array of num_groups + 1 ascending int32. */
   const int32_t* group_offsets;
   int32_t num_groups;
+  /* Fused output fan-out (tb_gemm only): up to 7 further destinations with c's dtype, shape and strides — typically the
+   * same buffer on peer GPUs, mapped into this process (CUDA IPC / symmetric memory). The epilogue stores every tile to c
+   * and to each of them with ordinary stores, so the transfer over NVLink overlaps the remaining tiles' math; the caller
+   * synchronises the ranks before the copies are read. HOST array of device pointers, or NULL. */
+  void* const* c_copies;
+  int32_t num_c_copies;
 } tb_gemm_args;
 
 /* Fill `cfg` for `p`. Stands in for origami.select_config + OrigamiMatmulSelector._compute_sk_grid

@@ -1,0 +1,82 @@
+"""Two-rank NCCL run of the column-sharded GEMM (NCCL all-gather and the fused epilogue push) and of the expert-parallel
+MoE path. Needs two GPUs: skipped otherwise. Runs as child processes, one per GPU."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["TB_ROOT"])
+import tritonblas_b200 as tb
+from tritonblas_b200 import distributed as tbd
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+g = torch.Generator().manual_seed(0)
+M, N, K = 512, 1024, 768
+a = (torch.randn(M, K, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+b = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16).to(dev)       # (N, K): K-contiguous
+lo, hi = tbd.shard_range(N, world, rank)
+layer = tbd.ColumnShardedGemm(b[lo:hi].contiguous())
+ref = a.float() @ b.float().T
+c = tbd.ColumnShardedGemm.as_matrix(layer.forward(a)).float()
+assert torch.allclose(c, ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item()), "nccl all-gather path"
+layer.enable_fused_gather(M)
+for _ in range(2):
+    c2 = tbd.ColumnShardedGemm.as_matrix(layer.forward_fused(a)).float()
+    assert torch.allclose(c2, ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item()), "fused push path"
+# expert-parallel MoE against a single-device evaluation of the same experts
+E, H, F, T, topk = 8, 256, 128, 64, 2
+w1 = (torch.randn(E, 2 * F, H, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+w2 = (torch.randn(E, H, F, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+xs = torch.randn(world, T, H, generator=g).to(torch.bfloat16).to(dev)
+ids = torch.stack([torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)]) for _ in range(world)]).to(dev)
+wts = torch.rand(world, T, topk, generator=g).to(dev)
+epr = E // world
+moe = tbd.ExpertParallelMoE(w1[rank * epr:(rank + 1) * epr].contiguous(), w2[rank * epr:(rank + 1) * epr].contiguous(), E)
+out, _ = moe.forward(xs[rank], ids[rank], wts[rank])
+ref = torch.zeros(T, H, device=dev)
+for t in range(T):
+    for j in range(topk):
+        e = int(ids[rank, t, j])
+        h = xs[rank, t].float() @ w1[e].float().T
+        act = (torch.nn.functional.silu(h[:F]) * h[F:]).to(torch.bfloat16).float()
+        ref[t] += wts[rank, t, j] * (act @ w2[e].float().T).to(torch.bfloat16).float()
+assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item()), "expert-parallel MoE"
+assert tb.device_status(rank) == 0
+dist.barrier()
+dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+def test_two_rank_sharded_gemm_fused_push_and_moe():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   TB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, "-c", WORKER], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+            out += "\n<timed out>"
+        outs.append(out)
+    assert all(p.returncode == 0 for p in procs), "\n----\n".join(o[-3000:] for o in outs)

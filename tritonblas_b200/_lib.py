@@ -50,6 +50,7 @@ class GemmArgs(ctypes.Structure):
         ("allow_tf32", ctypes.c_int32), ("streamk", ctypes.c_int32), ("sk_grid", ctypes.c_int32),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("epoch", ctypes.c_uint32),
         ("group_offsets", ctypes.c_void_p), ("num_groups", ctypes.c_int32),
+        ("c_copies", ctypes.POINTER(ctypes.c_void_p)), ("num_c_copies", ctypes.c_int32),
     ]
 
 

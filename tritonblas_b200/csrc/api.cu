@@ -269,6 +269,9 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   while (tc < 2 * bn) tc <<= 1;
   p.tmem_cols = static_cast<uint32_t>(tc);
   p.C = a.c; p.ldc_m = a.c_stride_m; p.ldc_n = a.c_stride_n; p.c_dtype = a.c_dtype;
+  if (a.num_c_copies < 0 || a.num_c_copies > 7 || (a.num_c_copies > 0 && a.c_copies == nullptr)) return TB_ERR_INVALID;
+  for (int x = 0; x < a.num_c_copies; ++x) p.c_extra[x] = a.c_copies[x];
+  p.num_c_extra = a.num_c_copies;
   p.a_scale = a.a_scale; p.b_scale = a.b_scale;
   p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
   p.bias_along_m = swapped ? 1 : 0;

@@ -47,6 +47,8 @@ struct GemmParams {
   uint32_t idesc;  // tcgen05 instruction descriptor
   uint32_t tmem_cols;
   // output and epilogue
+  void* c_extra[7];  // further destinations with C's shape and strides (peer GPUs' buffers mapped into this process);
+  int num_c_extra;   // every tile is stored to C and to each of them with ordinary stores
   void* C;
   long long ldc_m, ldc_n;
   int c_dtype;
@@ -179,11 +181,11 @@ __device__ __forceinline__ float load_as_float(const void* p, long long idx, int
 }
 
 // Store 32 consecutive columns of one output row. `v` holds fp32 values after scale and bias.
-__device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, int col0, const float (&v)[32]) {
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, void* c_base, int row, int col0, const float (&v)[32]) {
   const int ncols = min(32, p.N - col0);
   if (ncols <= 0) return;
   if (p.c_dtype == TB_BF16 || p.c_dtype == TB_F16) {
-    unsigned short* base = reinterpret_cast<unsigned short*>(p.C) + row * p.ldc_m + col0 * p.ldc_n;
+    unsigned short* base = reinterpret_cast<unsigned short*>(c_base) + row * p.ldc_m + col0 * p.ldc_n;
     if (p.ldc_n == 1 && ncols == 32 && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
       uint4* dst = reinterpret_cast<uint4*>(base);
 #pragma unroll
@@ -219,7 +221,7 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, in
       }
     }
   } else if (p.c_dtype == TB_F32) {
-    float* base = reinterpret_cast<float*>(p.C) + row * p.ldc_m + col0 * p.ldc_n;
+    float* base = reinterpret_cast<float*>(c_base) + row * p.ldc_m + col0 * p.ldc_n;
     if (p.ldc_n == 1 && ncols == 32 && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
       float4* dst = reinterpret_cast<float4*>(base);
 #pragma unroll
@@ -230,7 +232,7 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, in
         if (j < ncols) base[j * p.ldc_n] = v[j];
     }
   } else {  // fp8 e4m3 output, saturating
-    unsigned char* base = reinterpret_cast<unsigned char*>(p.C) + row * p.ldc_m + col0 * p.ldc_n;
+    unsigned char* base = reinterpret_cast<unsigned char*>(c_base) + row * p.ldc_m + col0 * p.ldc_n;
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (j < ncols) base[j * p.ldc_n] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(v[j], __NV_SATFINITE, __NV_E4M3));
@@ -603,7 +605,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if (col0 + j < p.N) v[j] += load_as_float(p.bias, (col0 + j) * p.bias_stride, p.bias_dtype);
             }
           }
-          store_row_chunk(p, row, col0, v);
+          store_row_chunk(p, p.C, row, col0, v);
+          for (int x = 0; x < p.num_c_extra; ++x) store_row_chunk(p, p.c_extra[x], row, col0, v);
         }
       }
       // Hand the accumulator back to the MMA issuer.

@@ -51,6 +51,34 @@ class ColumnShardedGemm:
                                     group=self.group)
         return gathered
 
+    def enable_fused_gather(self, m: int, dtype=None):
+        """Allocate the gathered C (world, M, n_local) in symmetric memory and map every peer's copy, so that
+        forward_fused() can let the GEMM epilogue write each tile straight into all ranks' buffers over NVLink
+        (ordinary stores to peer-mapped memory; no TMA or multicast access to peer memory is involved)."""
+        import torch.distributed._symmetric_memory as symm_mem
+        dtype = dtype or self.b_shard_t.dtype
+        n_local = self.b_shard_t.shape[0]
+        group = self.group if self.group is not None else dist.group.WORLD
+        self._gathered = symm_mem.empty(self.world, m, n_local, dtype=dtype, device=self.b_shard_t.device)
+        self._handle = symm_mem.rendezvous(self._gathered, group=group)
+        slot_bytes = m * n_local * self._gathered.element_size()
+        # address of MY slot inside every rank's buffer
+        self._peer_slots = [int(ptr) + self.rank * slot_bytes for r, ptr in enumerate(self._handle.buffer_ptrs) if r != self.rank]
+        from .origami import OrigamiMatmulSelector
+        self._fused_selector = OrigamiMatmulSelector(m, n_local, self.b_shard_t.shape[1], self.b_shard_t.dtype,
+                                                     self.b_shard_t.dtype, dtype, self.b_shard_t.device)
+        return self._gathered
+
+    def forward_fused(self, a: torch.Tensor) -> torch.Tensor:
+        """One kernel computes this rank's block of C and pushes it into every rank's gathered buffer; a symmetric-memory
+        barrier then orders the ranks. Returns this rank's (world, M, n_local) buffer."""
+        from .matmul import persistent_matmul_lt
+        self._handle.barrier(channel=0)          # nobody is still reading the previous contents
+        persistent_matmul_lt(a, self.b_shard_t.T, self._gathered[self.rank], self._fused_selector, None,
+                             c_copies=self._peer_slots)
+        self._handle.barrier(channel=1)          # every rank's pushes have landed
+        return self._gathered
+
     @staticmethod
     def as_matrix(gathered: torch.Tensor) -> torch.Tensor:
         world, m, n_local = gathered.shape

@@ -73,7 +73,8 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
 
 
-def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, streamk=False, sk_grid=None):
+def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, streamk=False, sk_grid=None,
+          c_copies=None):
     assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
     if not (a.is_cuda and b.is_cuda and c.is_cuda):
         raise RuntimeError("tritonblas_b200 runs on CUDA tensors only (no CPU path)")
@@ -108,6 +109,10 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
         assert bias.numel() == N, "bias must have N elements"
         bias = bias.view(-1)
         args.bias, args.bias_stride, args.bias_dtype = _ptr(bias), bias.stride(0), _lib.DTYPE_CODE[bias.dtype]
+    if c_copies:
+        # raw device addresses of further destinations laid out exactly like c (peer GPUs' buffers)
+        ptrs = (ctypes.c_void_p * len(c_copies))(*[int(p) for p in c_copies])
+        args.c_copies, args.num_c_copies = ptrs, len(c_copies)
     args.allow_tf32 = int(torch.backends.cuda.matmul.allow_tf32)
     args.streamk = int(bool(streamk))
     args.sk_grid = int(sk_grid) if sk_grid else 0
@@ -123,10 +128,11 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
 
 
 def persistent_matmul_lt(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, quantized=False,
-                         work_stealing=False):
+                         work_stealing=False, c_copies=None):
     """Data-parallel persistent GEMM (reference: matmul.py:69-200). ``work_stealing`` is accepted; tiles are
-    scheduled statically."""
-    return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=False)
+    scheduled statically. ``c_copies``: device addresses of further buffers laid out like ``c`` (peer GPUs) that the
+    epilogue also writes."""
+    return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=False, c_copies=c_copies)
 
 
 def streamk_matmul_lt(a, b, c, selector, config=None, bias=None, sk_grid=None, a_scale=None, b_scale=None,
