@@ -136,6 +136,7 @@ def cpu_reference_tflops(M, N, K, dtype, target_seconds, seed=0):
 def run_reference(args, wl, rank):
     if rank != 0:
         return
+    torch.set_num_threads(os.cpu_count() or 1)   # torchrun pins OMP_NUM_THREADS=1; the CPU arm uses every host core
     if args.workload == "moe":
         M, N, K = 2048, MOE["hidden"], MOE["ffn"] * 2   # one average expert's gate/up projection as the sample shape
     else:
@@ -250,7 +251,8 @@ class DenseWorkload:
 
     def step(self, i, dist):
         if self.layers is not None:
-            self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets])
+            # two gathered buffers alternate, so the opening barrier is not needed (see forward_fused)
+            self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets], pre_barrier=self.nsets < 2)
             return
         c = self.gemm(i)
         if self.world > 1:

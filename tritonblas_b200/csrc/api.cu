@@ -272,6 +272,12 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   if (a.num_c_copies < 0 || a.num_c_copies > 7 || (a.num_c_copies > 0 && a.c_copies == nullptr)) return TB_ERR_INVALID;
   for (int x = 0; x < a.num_c_copies; ++x) p.c_extra[x] = a.c_copies[x];
   p.num_c_extra = a.num_c_copies;
+  {
+    bool ok16 = (a.c_dtype == TB_DTYPE_BF16 || a.c_dtype == TB_DTYPE_F16) && a.c_stride_n == 1 && ((a.c_stride_m * 2) & 15) == 0 &&
+                (reinterpret_cast<uintptr_t>(a.c) & 15) == 0;
+    for (int x = 0; x < a.num_c_copies; ++x) ok16 = ok16 && (reinterpret_cast<uintptr_t>(a.c_copies[x]) & 15) == 0;
+    p.staged_store = ok16 ? 1 : 0;
+  }
   p.a_scale = a.a_scale; p.b_scale = a.b_scale;
   p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
   p.bias_along_m = swapped ? 1 : 0;
@@ -395,10 +401,10 @@ static int gemm_mxfp4_impl(const tb_mxfp4_args& a, cudaStream_t stream) {
   if (bn < 64 || bn > 192 || (bn % 64) != 0) return TB_ERR_INVALID;
   const int kbytes = a.k / 2;
   const int stage_bytes = (128 * 128 + (bn / pair) * 128 + (2 + 2 * groups) * 512 + 1023) & ~1023;
-  int stages = (dev->smem_optin - 2048) / stage_bytes;
+  int stages = (dev->smem_optin - 2048 - kEpiStageBytes) / stage_bytes;
   if (stages > 8) stages = 8;
   if (stages < 2) return TB_ERR_INVALID;
-  const int smem_bytes = stages * stage_bytes + (2 * stages + 8) * 8 + 64 + 1024;
+  const int smem_bytes = stages * stage_bytes + kEpiStageBytes + (2 * stages + 8) * 8 + 64 + 1024;
 
   GemmParams p = {};
   p.M = a.m; p.N = a.n; p.K = a.k;
@@ -415,6 +421,8 @@ static int gemm_mxfp4_impl(const tb_mxfp4_args& a, cudaStream_t stream) {
   while (tc < 2 * bn + 8 + 8 * groups) tc <<= 1;
   p.tmem_cols = static_cast<uint32_t>(tc);
   p.C = a.c; p.ldc_m = a.c_stride_m; p.ldc_n = a.c_stride_n; p.c_dtype = a.c_dtype;
+  p.staged_store = ((a.c_dtype == TB_DTYPE_BF16 || a.c_dtype == TB_DTYPE_F16) && a.c_stride_n == 1 &&
+                    ((a.c_stride_m * 2) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.c) & 15) == 0) ? 1 : 0;
   p.status = dev->status;
   p.timeout_ns = 2000000000ull;
   // e2m1 operands (format 1), ue8m0 scales (bit 23), K-major, N >> 3, M >> 4; scale-factor ids are set per MMA
@@ -561,6 +569,8 @@ static int gemm_streamk_builtin_impl(const tb_gemm_args& in, const tb_config* us
   p.a_scale = a.a_scale; p.b_scale = a.b_scale;
   p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
   p.bias_along_m = swapped ? 1 : 0;
+  p.staged_store = ((a.c_dtype == TB_DTYPE_BF16 || a.c_dtype == TB_DTYPE_F16) && a.c_stride_n == 1 &&
+                    ((a.c_stride_m * 2) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.c) & 15) == 0) ? 1 : 0;
   p.status = st->status;
   p.timeout_ns = 2000000000ull;
   const uint32_t fmt = in.a_dtype == TB_DTYPE_BF16 ? 1u : 0u;  // f16 = 0, bf16 = 1, e4m3 = 0

@@ -25,6 +25,8 @@ namespace tb {
 constexpr int kTileM = 128;          // accumulator rows per CTA (TMEM lanes)
 constexpr int kStageRowBytes = 128;  // one swizzle row: K extent of a stage in bytes for K-major operands
 constexpr int kGemmThreads = 192;      // producer + MMA + 4 epilogue warps
+constexpr int kEpiRowPitch = 144;                    // bytes between rows of an epilogue warp's staging buffer (128 + pad)
+constexpr int kEpiStageBytes = 4 * 32 * kEpiRowPitch;  // four epilogue warps x 32 rows
 constexpr int kSfAtomBytes = 512;      // scale factors of 128 rows x 4 K blocks, laid out [32 rows][4 row quads][4 blocks]
 constexpr int kSfGroupsB = 2;          // 128-row scale groups staged for B: tiles are 64, 128 or 192 columns wide and start
                                        // at a multiple of 64 (the MMA takes its scale columns from an even TMEM column),
@@ -57,6 +59,7 @@ struct GemmParams {
   const void* bias;      // (N,) or null
   long long bias_stride;
   int bias_dtype;
+  int staged_store;      // 1: 16-bit output, unit column stride, 16-byte aligned rows in every destination
   int bias_along_m;      // 1: bias indexed by row (set when the problem was transposed to C^T = B^T A^T)
   // schedule
   int dp_tiles;  // tiles [0, dp_tiles) are data-parallel: tile = program + i * programs
@@ -262,7 +265,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int stages = p.stages;
 
   uint8_t* ring = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(stages) * stage_bytes);
+  uint8_t* epi_stage = smem + static_cast<size_t>(stages) * stage_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + kEpiStageBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + stages;
   uint64_t* tmem_full = bars + 2 * stages;
@@ -523,6 +527,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ------------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const int row_in_tile = q * 32 + lane;
+    uint8_t* stg = epi_stage + (warp - 2) * (32 * kEpiRowPitch);
     WorkIter wi(p, pid, nprog, grouped_tiles);
     int acc = 0;
     uint32_t acc_ph = 0;
@@ -563,8 +568,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
 
       const float a_s = (p.a_scale != nullptr && row < row_end) ? p.a_scale[row] : 1.0f;
+      const int nchunks = p.block_n / 32;
+      // staged stores need whole 32-column chunks inside N and 16-byte aligned rows in every destination (host-checked)
+      const bool staged = owner && p.staged_store && (n0 + p.block_n <= p.N);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * acc_stride);
-      for (int c = 0; c < p.block_n / 32; ++c) {
+      for (int c = 0; c < nchunks; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
@@ -585,7 +593,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * kTileM);
         }
         const int col0 = n0 + c * 32;
-        if (row < row_end && col0 < p.N) {
+        if (col0 < p.N && (staged || row < row_end)) {
           if (p.a_scale != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= a_s;
@@ -596,7 +604,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
           if (p.bias != nullptr) {
             if (p.bias_along_m) {
-              const float bv = load_as_float(p.bias, row * p.bias_stride, p.bias_dtype);
+              const float bv = row < row_end ? load_as_float(p.bias, row * p.bias_stride, p.bias_dtype) : 0.0f;
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] += bv;
             } else {
@@ -605,8 +613,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if (col0 + j < p.N) v[j] += load_as_float(p.bias, (col0 + j) * p.bias_stride, p.bias_dtype);
             }
           }
-          store_row_chunk(p, p.C, row, col0, v);
-          for (int x = 0; x < p.num_c_extra; ++x) store_row_chunk(p, p.c_extra[x], row, col0, v);
+          if (!staged) {
+            store_row_chunk(p, p.C, row, col0, v);
+            for (int x = 0; x < p.num_c_extra; ++x) store_row_chunk(p, p.c_extra[x], row, col0, v);
+          }
+        }
+        if (staged) {
+          // 16-bit outputs with unit column stride: the warp's 32 rows x 64 columns pass through shared memory so that
+          // every row leaves as one 128-byte run (8 lanes x 16 bytes), which is what remote (NVLink) and local L2 writes
+          // both want, instead of 16-byte pieces of 32 different rows per store instruction.
+          uint8_t* mine = stg + lane * kEpiRowPitch + (c & 1) * 64;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const float lo = v[j * 8 + h * 2], hi = v[j * 8 + h * 2 + 1];
+              if (p.c_dtype == TB_BF16) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+                w[h] = *reinterpret_cast<uint32_t*>(&t);
+              } else {
+                __half2 t = __floats2half2_rn(lo, hi);
+                w[h] = *reinterpret_cast<uint32_t*>(&t);
+              }
+            }
+            *reinterpret_cast<uint4*>(mine + j * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          if ((c & 1) || c + 1 == nchunks) {
+            __syncwarp();
+            const int ncol = (c & 1) ? 64 : 32;
+            const int colw = n0 + (c & ~1) * 32;  // first column of the staged run
+            const int seg = lane & 7;
+            if (seg * 8 < ncol) {
+#pragma unroll
+              for (int it = 0; it < 8; ++it) {
+                const int row_l = it * 4 + (lane >> 3);
+                const int row_g = m0 + q * 32 + row_l;
+                if (row_g < row_end) {
+                  const uint4 val = *reinterpret_cast<const uint4*>(stg + row_l * kEpiRowPitch + seg * 16);
+                  const long long off = static_cast<long long>(row_g) * p.ldc_m + colw + seg * 8;
+                  *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.C) + off) = val;
+                  for (int x = 0; x < p.num_c_extra; ++x)
+                    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.c_extra[x]) + off) = val;
+                }
+              }
+            }
+            __syncwarp();
+          }
         }
       }
       // Hand the accumulator back to the MMA issuer.

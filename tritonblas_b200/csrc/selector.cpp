@@ -39,7 +39,7 @@ static int next_pow2(int v) {
 
 int smem_bytes_for(int block_n, int cta_pair, int stages) {
   const int stage = 128 * 128 + (block_n / cta_pair) * 128;
-  return stages * stage + (2 * stages + 8) * 8 + 64 + 1024;  // ring + barriers + slots + alignment slack
+  return stages * stage + 18432 + (2 * stages + 8) * 8 + 64 + 1024;  // ring + epilogue staging + barriers + slots + slack
 }
 
 struct Candidate {
@@ -97,7 +97,7 @@ int select_config(const tb_problem& p_in, const MachineModel& hw, tb_config* out
       const long long tiles = tiles_m * tiles_n;
       const int programs = std::max(1, sms / pair);
       const int sf_bytes = mx ? (2 + 2 * 2) * 512 : 0;
-      int stages = (hw.smem_optin - 2048) / ((128 * 128 + bn_local * 128 + sf_bytes + 1023) & ~1023);
+      int stages = (hw.smem_optin - 2048 - 18432) / ((128 * 128 + bn_local * 128 + sf_bytes + 1023) & ~1023);
       stages = std::min(stages, 12);
       if (stages < 2) continue;
       const double mma_clk = mma_clk_per_stage_per_bn * bn;

@@ -69,11 +69,18 @@ class ColumnShardedGemm:
                                                      self.b_shard_t.dtype, dtype, self.b_shard_t.device)
         return self._gathered
 
-    def forward_fused(self, a: torch.Tensor) -> torch.Tensor:
+    def forward_fused(self, a: torch.Tensor, pre_barrier: bool = True) -> torch.Tensor:
         """One kernel computes this rank's block of C and pushes it into every rank's gathered buffer; a symmetric-memory
-        barrier then orders the ranks. Returns this rank's (world, M, n_local) buffer."""
+        barrier then orders the ranks. Returns this rank's (world, M, n_local) buffer.
+
+        ``pre_barrier`` makes every rank wait until all ranks have finished reading the previous contents before anyone
+        overwrites them. It can be dropped (one barrier less per call) when calls alternate between two or more
+        gathered buffers and each buffer is read on this stream before the next call is enqueued: a rank can then only
+        start overwriting a buffer after every rank has passed the closing barrier of the call in between, which on each
+        rank's stream comes after its reads."""
         from .matmul import persistent_matmul_lt
-        self._handle.barrier(channel=0)          # nobody is still reading the previous contents
+        if pre_barrier:
+            self._handle.barrier(channel=0)      # nobody is still reading the previous contents
         persistent_matmul_lt(a, self.b_shard_t.T, self._gathered[self.rank], self._fused_selector, None,
                              c_copies=self._peer_slots)
         self._handle.barrier(channel=1)          # every rank's pushes have landed
