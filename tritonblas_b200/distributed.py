@@ -102,6 +102,8 @@ class DispatchPlan:
     recv_splits: List[int]
     regroup_idx: Optional[torch.Tensor]   # received rows (source-major) -> expert-major order
     group_offsets: torch.Tensor     # int32 (experts_per_rank + 1,) row offsets of the expert-major buffer
+    regroup_inv: Optional[torch.Tensor] = None   # expert-major -> source-major (inverse of regroup_idx)
+    pos: Optional[torch.Tensor] = None           # position of every (token, k) pair in expert order (inverse of sort_idx)
 
 
 def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None) -> DispatchPlan:
@@ -123,7 +125,9 @@ def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None) -> Dispa
     per_expert = recv_counts.sum(0)
     group_offsets = torch.zeros(epr + 1, dtype=torch.int32, device=topk_ids.device)
     group_offsets[1:] = per_expert.cumsum(0).to(torch.int32)
-    regroup_idx = None
+    regroup_idx = regroup_inv = None
+    pos = torch.empty_like(sort_idx)
+    pos[sort_idx] = torch.arange(sort_idx.numel(), device=sort_idx.device)
     if world > 1:
         total = int(sum(recv_splits))
         seg_start_src = (recv_counts.reshape(-1).cumsum(0) - recv_counts.reshape(-1)).reshape(world, epr)   # source-major
@@ -134,18 +138,21 @@ def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None) -> Dispa
         seg_id = torch.repeat_interleave(torch.arange(seg_len.numel(), device=seg_len.device), seg_len, output_size=total)
         within = torch.arange(total, device=seg_len.device) - seg_start_dst.reshape(-1)[seg_id]
         regroup_idx = seg_src[seg_id] + within
-    return DispatchPlan(sort_idx, send_counts, recv_counts, send_splits, recv_splits, regroup_idx, group_offsets)
+        regroup_inv = torch.empty_like(regroup_idx)
+        regroup_inv[regroup_idx] = torch.arange(total, device=regroup_idx.device)
+    return DispatchPlan(sort_idx, send_counts, recv_counts, send_splits, recv_splits, regroup_idx, group_offsets,
+                        regroup_inv, pos)
 
 
 def dispatch(x: torch.Tensor, topk: int, plan: DispatchPlan, group=None) -> torch.Tensor:
     """Rows of x (T, H), replicated topk times and ordered by expert, sent to the experts' owners. Returns the rows this
     rank's experts must process, expert-major (aligned with plan.group_offsets)."""
-    rows = x[plan.sort_idx // topk]
+    rows = x.index_select(0, plan.sort_idx // topk)
     if plan.regroup_idx is None:
         return rows
     recv = rows.new_empty(int(sum(plan.recv_splits)), x.shape[1])
     dist.all_to_all_single(recv, rows, plan.recv_splits, plan.send_splits, group=group)
-    return recv[plan.regroup_idx]
+    return recv.index_select(0, plan.regroup_idx)
 
 
 def combine(y: torch.Tensor, topk_weights: torch.Tensor, plan: DispatchPlan, group=None) -> torch.Tensor:
@@ -153,15 +160,12 @@ def combine(y: torch.Tensor, topk_weights: torch.Tensor, plan: DispatchPlan, gro
     (fp32 accumulate in k order, one cast)."""
     tokens, topk = topk_weights.shape
     if plan.regroup_idx is not None:
-        src_major = torch.empty_like(y)
-        src_major[plan.regroup_idx] = y
+        src_major = y.index_select(0, plan.regroup_inv)          # a gather; the scatter form is several times slower
         back = y.new_empty(int(sum(plan.send_splits)), y.shape[1])
         dist.all_to_all_single(back, src_major, plan.send_splits, plan.recv_splits, group=group)
     else:
         back = y
-    # position of every (token, k) pair in the expert-sorted order: the inverse of sort_idx
-    pos = torch.empty_like(plan.sort_idx)
-    pos[plan.sort_idx] = torch.arange(plan.sort_idx.numel(), device=plan.sort_idx.device)
+    pos = plan.pos
     if back.is_cuda:
         return _combine_cuda(back, pos, topk_weights, tokens, topk)
     return (back[pos].reshape(tokens, topk, -1).float() * topk_weights.unsqueeze(-1).float()).sum(1).to(y.dtype)
