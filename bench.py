@@ -361,7 +361,12 @@ class MoeWorkload:
         self.x, self.ids = self.x_host.to(dev), self.ids_host.to(dev)
         w1 = (torch.randn(epr, 2 * F, H, generator=gl) * 0.02).to(torch.bfloat16).to(dev)
         w2 = (torch.randn(epr, H, F, generator=gl) * 0.02).to(torch.bfloat16).to(dev)
-        self.moe = tbd.ExpertParallelMoE(w1, w2, E, None)
+        if world > 1 and not args.nccl_moe:
+            # token exchange over peer-mapped memory (one dispatch kernel, one combine kernel, two barriers)
+            self.moe = tbd.PeerMemoryMoE(w1, w2, E, capacity=T * topk)
+        else:
+            self.moe = tbd.ExpertParallelMoE(w1, w2, E, None)
+        self.peer_path = isinstance(self.moe, tbd.PeerMemoryMoE)
         self.out_host = torch.empty(self.t_local, H, dtype=torch.bfloat16).pin_memory()
         rows = T * topk
         self.flops = 2.0 * rows * (H * 2 * F + F * H)
@@ -371,7 +376,8 @@ class MoeWorkload:
         counts = torch.bincount(ids_all.flatten(), minlength=E).reshape(world, epr).sum(1).tolist()
         self.label = (f"grouped MoE GEMM bf16: {E} experts, top-{topk} of {T} tokens, hidden {H}, ffn {F}, gate/up + down "
                       f"projections, Zipf(1.1) routing (seeded), SwiGLU between (torch elementwise, outside the FLOP count)")
-        self.extra = {"parallelism": f"expert-parallel x{world}, NCCL all-to-all dispatch/combine" if world > 1
+        self.extra = {"parallelism": (f"expert-parallel x{world}, " + ("dispatch/combine kernels over NVLink peer memory"
+                                      if self.peer_path else "NCCL all-to-all dispatch/combine")) if world > 1
                       else "single GPU", "rows_per_rank": counts}
 
     def step(self, i, dist):
@@ -394,6 +400,8 @@ def main():
     ap.add_argument("--gemms-per-step", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-operand leg (profiling runs)")
+    ap.add_argument("--nccl-moe", action="store_true",
+                    help="moe workload on several GPUs: NCCL all-to-all dispatch/combine instead of the peer-memory kernels")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="multi-GPU default workload: gather C with NCCL after the GEMM instead of the fused epilogue push")
     args = ap.parse_args()

@@ -149,6 +149,22 @@ int tb_swiglu(const void* h, int64_t h_row_stride, void* out, int64_t out_row_st
 int tb_moe_combine(const void* y, int64_t y_row_stride, const int64_t* pos, const float* weights, void* out,
                    int64_t out_row_stride, int32_t tokens, int32_t topk, int32_t hidden, int32_t dtype, void* stream);
 
+/* Expert-parallel dispatch and combine over peer-mapped memory (each rank's receive / output buffer mapped into every
+ * process, e.g. by CUDA IPC or torch symmetric memory), in place of all-to-all collectives. Ordinary loads and stores.
+ *   tb_moe_dispatch_peers: for i < n, row src_token[i] of x is copied to row dest_row[i] of peer_bufs[dest_rank[i]];
+ *                          rows outside [0, capacity_rows) are dropped and counted in *overflow_count (device int, may
+ *                          be NULL).
+ *   tb_moe_combine_peers:  out[t, :] = sum_k weights[t,k] * y_peers[pair_rank[t,k]][pair_row[t,k], :] (fp32, k order).
+ * peer_bufs / y_peers are HOST arrays of up to 8 device pointers; index arrays are device memory. The caller orders the
+ * phases across ranks (barrier after dispatch, barrier before combine). No reference counterpart. */
+int tb_moe_dispatch_peers(const void* x, int64_t x_row_stride, const int64_t* src_token, const int32_t* dest_rank,
+                          const int64_t* dest_row, void* const* peer_bufs, int32_t num_peers, int64_t dest_row_stride,
+                          int64_t capacity_rows, int32_t* overflow_count, int64_t n, int32_t hidden, int32_t dtype,
+                          void* stream);
+int tb_moe_combine_peers(void* const* y_peers, int32_t num_peers, int64_t y_row_stride, const int32_t* pair_rank,
+                         const int64_t* pair_row, const float* weights, void* out, int64_t out_row_stride, int32_t tokens,
+                         int32_t topk, int32_t hidden, int32_t dtype, void* stream);
+
 /* MXFP4 GEMM: C (m, n) = sum over 32-element K blocks of (A_e2m1 * 2^(sa-127)) . (B_e2m1 * 2^(sb-127)), fp32
  * accumulate, one cast. A is (m, k/2) bytes and B is (n, k/2) bytes, two e2m1 codes per byte (even element in the low
  * nibble), K contiguous, row strides in bytes (multiples of 16). Scales are e8m0 bytes in the "atom" arrangement the

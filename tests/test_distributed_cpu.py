@@ -87,3 +87,38 @@ def test_single_rank_plan_is_identity_routing():
     assert rows.shape == (6, 2)
     back = tbd.combine(rows, torch.ones(3, 2), plan)
     assert torch.allclose(back, 2 * x)
+
+
+def test_peer_dispatch_plan_places_every_row_once_and_expert_major():
+    """The index arithmetic of the peer-memory MoE path, emulated for 4 ranks in one process: after every rank has
+    "written" its rows, each rank's receive buffer holds its experts back to back, each expert's rows complete, and the
+    combine indices point back at the row that carries the pair's token."""
+    world, E, T, topk = 4, 16, 37, 3
+    g = torch.Generator().manual_seed(5)
+    ids = [torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)]) for _ in range(world)]
+    counts_all = torch.stack([torch.bincount(i.flatten(), minlength=E) for i in ids])
+    plans = [tbd.plan_peer_dispatch(ids[r], counts_all, r) for r in range(world)]
+    epr = E // world
+    cap = int(counts_all.sum())
+    token_tag = [torch.full((cap,), -1, dtype=torch.int64) for _ in range(world)]     # what landed where: (src, token)
+    expert_tag = [torch.full((cap,), -1, dtype=torch.int64) for _ in range(world)]
+    for r, p in enumerate(plans):
+        flat = ids[r].flatten()
+        sort_idx = torch.argsort(flat, stable=True)
+        for i in range(p.src_token.numel()):
+            d, row = int(p.dest_rank[i]), int(p.dest_row[i])
+            assert token_tag[d][row] == -1, "two rows written to the same place"
+            token_tag[d][row] = r * 1000 + int(p.src_token[i])
+            expert_tag[d][row] = int(flat[sort_idx[i]])
+    for d in range(world):
+        offs = plans[d].group_offsets.tolist()
+        assert offs[-1] == int(counts_all[:, d * epr:(d + 1) * epr].sum())
+        for e in range(epr):
+            seg = expert_tag[d][offs[e]:offs[e + 1]]
+            assert (seg == d * epr + e).all()
+        assert (token_tag[d][offs[-1]:] == -1).all()
+    for r, p in enumerate(plans):
+        for f in range(T * topk):
+            d, row = int(p.pair_rank[f]), int(p.pair_row[f])
+            assert token_tag[d][row] == r * 1000 + f // topk
+            assert expert_tag[d][row] == int(ids[r].flatten()[f])

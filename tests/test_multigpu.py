@@ -51,6 +51,12 @@ for t in range(T):
         act = (torch.nn.functional.silu(h[:F]) * h[F:]).to(torch.bfloat16).float()
         ref[t] += wts[rank, t, j] * (act @ w2[e].float().T).to(torch.bfloat16).float()
 assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item()), "expert-parallel MoE"
+peer = tbd.PeerMemoryMoE(w1[rank * epr:(rank + 1) * epr].contiguous(), w2[rank * epr:(rank + 1) * epr].contiguous(), E,
+                         capacity=world * T * topk)
+for _ in range(2):
+    out2, _ = peer.forward(xs[rank], ids[rank], wts[rank])
+    assert torch.allclose(out2.float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item()), "peer-memory MoE"
+assert int(peer.overflow.item()) == 0
 assert tb.device_status(rank) == 0
 dist.barrier()
 dist.destroy_process_group()

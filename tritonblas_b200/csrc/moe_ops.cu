@@ -158,3 +158,124 @@ extern "C" int tb_moe_combine(const void* y, int64_t y_row_stride, const int64_t
   tb::g_launches.fetch_add(1, std::memory_order_relaxed);
   return TB_OK;
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Expert-parallel dispatch / combine over peer-mapped memory (NVLink / NVSwitch), replacing all-to-all collectives:
+//   dispatch: row i of the send list (token src_token[i]) is written straight into the receive buffer of the rank that
+//             owns its expert, at the row that rank's grouped GEMM expects (dest_row[i]); rows are 16-byte vector copies,
+//             so every row crosses NVLink as one contiguous run.
+//   combine:  out[t, :] = sum_k w[t, k] * y_{pair_rank[t,k]}[pair_row[t,k], :], reading the experts' outputs from the
+//             owners' buffers with ordinary peer loads.
+// Ordinary loads and stores only: no TMA, no multicast, no multimem on peer memory. The caller places barriers between
+// the phases (rows landed before the GEMMs read them; outputs complete before they are combined).
+namespace tb {
+namespace {
+
+struct PeerPtrs {
+  void* p[8];
+};
+
+__global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restrict__ x, long long x_stride_vec,
+                                                             const long long* __restrict__ src_token,
+                                                             const int* __restrict__ dest_rank,
+                                                             const long long* __restrict__ dest_row, PeerPtrs peers,
+                                                             long long dest_stride_vec, long long n, int vec_per_row,
+                                                             long long capacity_rows, int* __restrict__ overflow) {
+  // one warp per row
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; r < n; r += warps) {
+    const long long row = dest_row[r];
+    if (row < 0 || row >= capacity_rows) {  // a receive buffer too small for this routing: drop the row, tell the host
+      if (lane == 0 && overflow != nullptr) atomicAdd(overflow, 1);
+      continue;
+    }
+    const uint4* src = x + src_token[r] * x_stride_vec;
+    uint4* dst = reinterpret_cast<uint4*>(peers.p[dest_rank[r]]) + row * dest_stride_vec;
+    for (int v = lane; v < vec_per_row; v += 32) dst[v] = src[v];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) combine_peers_kernel(PeerPtrs y_peers, long long y_stride,
+                                                              const int* __restrict__ pair_rank,
+                                                              const long long* __restrict__ pair_row,
+                                                              const float* __restrict__ w, T* __restrict__ out,
+                                                              long long out_stride, int tokens, int topk, int hidden) {
+  const int vec_per_row = hidden / 8;
+  const long long total = static_cast<long long>(tokens) * vec_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / vec_per_row);
+    const int c = static_cast<int>(i - static_cast<long long>(t) * vec_per_row) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < topk; ++k) {
+      const long long f = static_cast<long long>(t) * topk + k;
+      const T* y = static_cast<const T*>(y_peers.p[pair_rank[f]]);
+      const float wk = w[f];
+      float v[8];
+      Vec8<T>::load(y + pair_row[f] * y_stride + c, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(v[j], wk, acc[j]);
+    }
+    Vec8<T>::store(out + static_cast<long long>(t) * out_stride + c, acc);
+  }
+}
+
+}  // namespace
+}  // namespace tb
+
+extern "C" int tb_moe_dispatch_peers(const void* x, int64_t x_row_stride, const int64_t* src_token, const int32_t* dest_rank,
+                                     const int64_t* dest_row, void* const* peer_bufs, int32_t num_peers,
+                                     int64_t dest_row_stride, int64_t capacity_rows, int32_t* overflow_count, int64_t n,
+                                     int32_t hidden, int32_t dtype, void* stream) {
+  if (x == nullptr || src_token == nullptr || dest_rank == nullptr || dest_row == nullptr || peer_bufs == nullptr) return TB_ERR_INVALID;
+  if (num_peers < 1 || num_peers > 8 || n < 0 || hidden <= 0 || (hidden % 8) != 0) return TB_ERR_INVALID;
+  if (dtype != TB_DTYPE_BF16 && dtype != TB_DTYPE_F16) return TB_ERR_UNSUPPORTED;
+  if (n == 0) return TB_OK;
+  if (!tb::aligned16(x, x_row_stride) || ((dest_row_stride * 2) & 15) != 0) return TB_ERR_ALIGNMENT;
+  tb::PeerPtrs peers = {};
+  for (int i = 0; i < num_peers; ++i) {
+    if ((reinterpret_cast<uintptr_t>(peer_bufs[i]) & 15) != 0) return TB_ERR_ALIGNMENT;
+    peers.p[i] = peer_bufs[i];
+  }
+  long long blocks = (n + 7) / 8;  // 8 warps per block, one row per warp
+  if (blocks > 148LL * 8 * 4) blocks = 148LL * 8 * 4;
+  tb::moe_dispatch_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), x_row_stride / 8, reinterpret_cast<const long long*>(src_token), dest_rank,
+      reinterpret_cast<const long long*>(dest_row), peers, dest_row_stride / 8, n, hidden / 8, capacity_rows, overflow_count);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return tb::cuda_fail(e, "moe_dispatch_kernel launch");
+  tb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return TB_OK;
+}
+
+extern "C" int tb_moe_combine_peers(void* const* y_peers, int32_t num_peers, int64_t y_row_stride, const int32_t* pair_rank,
+                                    const int64_t* pair_row, const float* weights, void* out, int64_t out_row_stride,
+                                    int32_t tokens, int32_t topk, int32_t hidden, int32_t dtype, void* stream) {
+  if (y_peers == nullptr || pair_rank == nullptr || pair_row == nullptr || weights == nullptr || out == nullptr) return TB_ERR_INVALID;
+  if (num_peers < 1 || num_peers > 8 || tokens < 0 || topk <= 0 || hidden <= 0 || (hidden % 8) != 0) return TB_ERR_INVALID;
+  if (tokens == 0) return TB_OK;
+  if (((y_row_stride * 2) & 15) != 0 || !tb::aligned16(out, out_row_stride)) return TB_ERR_ALIGNMENT;
+  tb::PeerPtrs peers = {};
+  for (int i = 0; i < num_peers; ++i) {
+    if ((reinterpret_cast<uintptr_t>(y_peers[i]) & 15) != 0) return TB_ERR_ALIGNMENT;
+    peers.p[i] = y_peers[i];
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = tb::grid_for(static_cast<long long>(tokens) * (hidden / 8));
+  if (dtype == TB_DTYPE_BF16)
+    tb::combine_peers_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(peers, y_row_stride, pair_rank,
+                                                                 reinterpret_cast<const long long*>(pair_row), weights,
+                                                                 static_cast<__nv_bfloat16*>(out), out_row_stride, tokens, topk, hidden);
+  else if (dtype == TB_DTYPE_F16)
+    tb::combine_peers_kernel<__half><<<grid, 256, 0, st>>>(peers, y_row_stride, pair_rank,
+                                                          reinterpret_cast<const long long*>(pair_row), weights,
+                                                          static_cast<__half*>(out), out_row_stride, tokens, topk, hidden);
+  else
+    return TB_ERR_UNSUPPORTED;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return tb::cuda_fail(e, "combine_peers_kernel launch");
+  tb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return TB_OK;
+}

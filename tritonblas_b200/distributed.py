@@ -222,3 +222,111 @@ class ExpertParallelMoE:
         h = self.grouped_fn(rows, self.w1, plan.group_offsets)
         y = self.grouped_fn(swiglu(h), self.w2, plan.group_offsets)
         return combine(y, topk_weights, plan, self.group), plan
+
+
+# ---------------------------------------------------------------------------------------------- peer-memory MoE path
+@dataclass
+class PeerDispatchPlan:
+    """Where every (token, k) pair of this rank goes when rows are written straight into the owners' receive buffers."""
+    src_token: torch.Tensor      # int64 (n,)  token of the i-th row in expert-sorted order
+    dest_rank: torch.Tensor      # int32 (n,)  rank that owns the row's expert
+    dest_row: torch.Tensor       # int64 (n,)  row in that rank's receive buffer
+    pair_rank: torch.Tensor      # int32 (tokens*topk,)  the same, indexed by the flattened (token, k) pair
+    pair_row: torch.Tensor       # int64 (tokens*topk,)
+    group_offsets: torch.Tensor  # int32 (experts_per_rank + 1,) row offsets of this rank's experts in its receive buffer
+
+
+def plan_peer_dispatch(topk_ids: torch.Tensor, counts_all: torch.Tensor, rank: int) -> PeerDispatchPlan:
+    """Pure index arithmetic on the device (no host synchronisation).
+
+    counts_all: int64 (world, num_experts), counts_all[r, e] = pairs of rank r routed to expert e (every rank holds the
+    same matrix after an all-gather of its own bincount). Expert e lives on rank e // experts_per_rank; inside that
+    rank's receive buffer the experts follow each other, and inside an expert the source ranks follow each other, each
+    source's rows in its own stable expert-sorted order.
+    """
+    world, num_experts = counts_all.shape
+    epr = num_experts // world
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    n = flat.numel()
+    sort_idx = torch.argsort(flat, stable=True)
+    e_sorted = flat[sort_idx]
+    totals = counts_all.sum(0)                                              # rows per expert over all sources
+    per_owner = totals.view(world, epr)
+    owner_off = (per_owner.cumsum(1) - per_owner).reshape(-1)               # start of expert e inside its owner's buffer
+    dest_base = owner_off + counts_all[:rank].sum(0)                        # + rows of lower-ranked sources
+    mine = counts_all[rank]
+    my_start = mine.cumsum(0) - mine                                        # start of expert e in my sorted list
+    i = torch.arange(n, device=flat.device)
+    dest_row = dest_base[e_sorted] + (i - my_start[e_sorted])
+    dest_rank = (e_sorted // epr).to(torch.int32)
+    pair_row = torch.empty_like(dest_row)
+    pair_row[sort_idx] = dest_row
+    pair_rank = torch.empty_like(dest_rank)
+    pair_rank[sort_idx] = dest_rank
+    group_offsets = torch.zeros(epr + 1, dtype=torch.int32, device=flat.device)
+    group_offsets[1:] = per_owner[rank].cumsum(0).to(torch.int32)
+    topk = topk_ids.shape[1]
+    return PeerDispatchPlan(sort_idx // topk, dest_rank, dest_row, pair_rank, pair_row, group_offsets)
+
+
+class PeerMemoryMoE:
+    """Expert-parallel MoE feed-forward whose token exchange runs over peer-mapped memory instead of collectives.
+
+    Every rank allocates a receive buffer and an output buffer of ``capacity`` rows in symmetric memory. dispatch is ONE
+    kernel that writes each routed row into its owner's receive buffer over NVLink, already in the order the grouped GEMM
+    wants; combine is ONE kernel that reads the experts' outputs from the owners' buffers and forms the top-k weighted
+    sum. Two symmetric-memory barriers per call order the phases; the only collective is an all-gather of the per-expert
+    counts (world x experts integers), and nothing synchronises with the host.
+    """
+
+    def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, capacity: int, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.w1, self.w2, self.num_experts, self.group = w1, w2, num_experts, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        hidden = w1.shape[2]
+        self.capacity, self.hidden = int(capacity), hidden
+        pg = group if group is not None else dist.group.WORLD
+        self.recv = symm_mem.empty(self.capacity, hidden, dtype=w1.dtype, device=w1.device)
+        self.recv_h = symm_mem.rendezvous(self.recv, group=pg)
+        self.y = symm_mem.empty(self.capacity, hidden, dtype=w1.dtype, device=w1.device)
+        self.y_h = symm_mem.rendezvous(self.y, group=pg)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=w1.device)   # rows dropped because capacity was too small
+        import ctypes
+        self._recv_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.recv_h.buffer_ptrs])
+        self._y_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.y_h.buffer_ptrs])
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor):
+        import ctypes
+        from . import _lib
+        from .matmul import grouped_matmul
+        tokens, topk = topk_ids.shape
+        mine = torch.bincount(topk_ids.reshape(-1).to(torch.int64), minlength=self.num_experts)
+        counts_all = torch.empty(self.world, self.num_experts, dtype=mine.dtype, device=mine.device)
+        dist.all_gather_into_tensor(counts_all.view(-1), mine, group=self.group)
+        plan = plan_peer_dispatch(topk_ids, counts_all, self.rank)
+        stream = _lib.current_stream_ptr(x.device)
+        code = _lib.DTYPE_CODE[x.dtype]
+        x = x if x.stride(1) == 1 else x.contiguous()
+        with torch.cuda.device(x.device):
+            rc = _lib.lib.tb_moe_dispatch_peers(ctypes.c_void_p(x.data_ptr()), x.stride(0),
+                                                ctypes.c_void_p(plan.src_token.data_ptr()),
+                                                ctypes.c_void_p(plan.dest_rank.data_ptr()),
+                                                ctypes.c_void_p(plan.dest_row.data_ptr()), self._recv_ptrs, self.world,
+                                                self.recv.stride(0), self.capacity, ctypes.c_void_p(self.overflow.data_ptr()),
+                                                plan.src_token.numel(), self.hidden, code, stream)
+        _lib.check(rc, "tb_moe_dispatch_peers")
+        self.recv_h.barrier(channel=0)                      # every rank's rows have landed in every receive buffer
+        h = grouped_matmul(self.recv, self.w1, plan.group_offsets)
+        grouped_matmul(swiglu(h), self.w2, plan.group_offsets, out=self.y)
+        self.y_h.barrier(channel=0)                         # every rank's expert outputs are complete
+        w = topk_weights.to(torch.float32).contiguous()
+        out = x.new_empty(tokens, self.hidden)
+        with torch.cuda.device(x.device):
+            rc = _lib.lib.tb_moe_combine_peers(self._y_ptrs, self.world, self.y.stride(0),
+                                               ctypes.c_void_p(plan.pair_rank.data_ptr()),
+                                               ctypes.c_void_p(plan.pair_row.data_ptr()), ctypes.c_void_p(w.data_ptr()),
+                                               ctypes.c_void_p(out.data_ptr()), out.stride(0), tokens, topk, self.hidden,
+                                               code, stream)
+        _lib.check(rc, "tb_moe_combine_peers")
+        return out, plan
