@@ -25,7 +25,8 @@ enum {
   TB_DTYPE_E4M3 = 3,
   TB_DTYPE_E5M2 = 4,
   TB_DTYPE_U8 = 5, /* packed e2m1 pairs / e8m0 scale bytes */
-  TB_DTYPE_F4 = 6  /* selector only: 4-bit e2m1 operand */
+  TB_DTYPE_F4 = 6, /* selector only: 4-bit e2m1 operand */
+  TB_DTYPE_I8 = 7  /* signed 8-bit integers: int32 accumulate on the tensor cores, fp32 epilogue */
 };
 
 /* host-side error codes; codes >= 100 are device-side wait time-outs reported through tb_device_status() */
@@ -205,6 +206,13 @@ int tb_mxfp4_quant(const void* x, int32_t x_dtype, int64_t rows, int64_t k, int6
 int tb_mxfp4_quant_atoms(const void* x, int32_t x_dtype, int64_t rows, int64_t k, int64_t x_row_stride, void* codes,
                          int64_t codes_row_stride, void* scales, int64_t scales_row_stride, void* atoms, int32_t hadamard,
                          void* stream);
+
+/* Per-row symmetric FP8 e4m3 quantiser: scales[r] = max(amax(x[r,:]), 1e-8) / 448, q[r,:] = cast(x[r,:] * (1/scales[r])).
+ * x is f16/bf16 (rows, k), k % 8 == 0. Rows of an activation are tokens, rows of a weight stored (N, K) are output
+ * channels. Replaces the torch-op fixture quantize_tensor_per_channel(axis=1) (include/tritonblas/utils.py:340-377), same
+ * arithmetic in the same order. */
+int tb_fp8_quant_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t k, int64_t x_row_stride, void* q,
+                      int64_t q_row_stride, float* scales, void* stream);
 
 /* Reads (synchronously: waits for the device) and clears the per-device status word that kernels set when a bounded
  * wait gives up. 0 = no failure since the last call. No reference counterpart (its waits are unbounded,

@@ -10,7 +10,12 @@ import torch
 def gemm_ref(a, b, out_dtype=None, a_scale=None, b_scale=None, bias=None):
     """C = cast(((A.float() @ B.float()) * a_scale[:, None]) * b_scale[None, :] + bias[None, :]) on the CPU."""
     out_dtype = out_dtype or a.dtype
-    acc = torch.matmul(a.detach().cpu().to(torch.float32), b.detach().cpu().to(torch.float32))
+    if a.dtype == torch.int8:
+        # integer operands accumulate exactly in int32 on the tensor cores (reference: acc_dtype int32 for int8,
+        # kernels/persistent_gemm.py:75); fp64 holds those sums exactly, then the epilogue runs in fp32
+        acc = torch.matmul(a.detach().cpu().to(torch.float64), b.detach().cpu().to(torch.float64)).to(torch.float32)
+    else:
+        acc = torch.matmul(a.detach().cpu().to(torch.float32), b.detach().cpu().to(torch.float32))
     if a_scale is not None:
         acc = acc * a_scale.detach().cpu().to(torch.float32).reshape(-1, 1)
     if b_scale is not None:
@@ -19,6 +24,8 @@ def gemm_ref(a, b, out_dtype=None, a_scale=None, b_scale=None, bias=None):
         acc = acc + bias.detach().cpu().to(torch.float32).reshape(1, -1)
     if out_dtype == torch.float8_e4m3fn:
         acc = acc.clamp(-448.0, 448.0)  # saturating cast, tests/test_matmul_a8w8_lt.py:27-32
+    if out_dtype == torch.int8:
+        acc = acc.round().clamp(-128.0, 127.0)
     return acc.to(out_dtype)
 
 

@@ -64,3 +64,51 @@ def test_a8w8_config3_shapes(m):
     cols = torch.cat([cols, torch.tensor([0, 255, 256, n - 1])]).cuda()
     rows = None if m <= 256 else torch.randint(0, m, (64,), generator=torch.Generator().manual_seed(10)).tolist()
     assert_close_to_oracle(c[:, cols], a8, b8[:, cols], a_scale=a_s, b_scale=b_s[cols], rows=rows, what=f"cfg3 m={m}")
+
+
+@pytest.mark.parametrize("streamk", [False, True])
+@pytest.mark.parametrize("ta,tb_", [("T", "T"), ("N", "N")])
+@pytest.mark.parametrize("m,n,k", [(256, 384, 512), (100, 200, 1024), (16, 1024, 2048)])
+def test_int8_a8w8(m, n, k, ta, tb_, streamk):
+    """INT8 operands, int32 accumulation on the tensor cores, per-row x per-column fp32 scales, bf16 output."""
+    g = torch.Generator().manual_seed(m + k)
+    a16 = torch.randn(m, k, generator=g).cuda()
+    b16 = (torch.randn(k, n, generator=g) * 0.02).cuda()
+    a8, a_s = utils.quantize_tensor_per_channel(a16, torch.int8, axis=1)
+    b8, b_s = utils.quantize_tensor_per_channel(b16, torch.int8, axis=0)
+    if ta == "N":
+        a8 = a8.T.contiguous().T
+    b8 = b8.T.contiguous().T if tb_ == "T" else b8.contiguous()
+    c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    tb.matmul_a8w8(a8, b8, a_s, b_s, c, enable_streamk=streamk)
+    assert_close_to_oracle(c, a8, b8, a_scale=a_s, b_scale=b_s, what=f"int8 {(m, n, k)} {ta}{tb_} sk={streamk}")
+
+
+def test_int8_output_saturates():
+    m, n, k = 128, 256, 256
+    g = torch.Generator().manual_seed(2)
+    a8 = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8).cuda()
+    b8 = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8).cuda().T
+    a_s = torch.full((m,), 1e-3, device="cuda")
+    b_s = torch.full((n,), 1.0, device="cuda")
+    c = torch.empty(m, n, dtype=torch.int8, device="cuda")
+    tb.matmul_a8w8(a8, b8, a_s, b_s, c)
+    from oracle import gemm_oracle
+    ref = gemm_oracle.gemm_ref(a8, b8, torch.int8, a_s, b_s)
+    diff = (c.cpu().int() - ref.int()).abs()
+    assert diff.max() <= 1 and (diff > 0).float().mean() < 0.01     # ties may round differently at .5 exactly
+    assert c.max() == 127 or c.min() == -128 or ref.abs().max() < 127
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,k", [(1, 8), (37, 264), (256, 8192), (1000, 1536)])
+def test_fp8_row_quantiser_is_bit_exact_against_the_fixture(rows, k, dtype):
+    g = torch.Generator().manual_seed(rows + k)
+    x = (torch.randn(rows, k, generator=g) * 3).to(dtype).cuda()
+    x[0, 0] = 0.0
+    if rows > 2:
+        x[2] = 0.0                                    # all-zero row: scale clamps at 1e-8 / 448
+    q, s = utils.quantize_fp8_rows(x)
+    q_ref, s_ref = utils.quantize_tensor_per_channel(x, FP8, axis=1)
+    assert torch.equal(s, s_ref)
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))

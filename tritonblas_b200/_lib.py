@@ -11,7 +11,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtritonblas_b200.so")
 
 # element type codes (TB_DTYPE_* in the header)
-F16, BF16, F32, E4M3, E5M2, U8, F4 = range(7)
+F16, BF16, F32, E4M3, E5M2, U8, F4, I8 = range(8)
 
 DTYPE_CODE = {
     torch.float16: F16,
@@ -20,6 +20,7 @@ DTYPE_CODE = {
     torch.float8_e4m3fn: E4M3,
     torch.float8_e5m2: E5M2,
     torch.uint8: U8,
+    torch.int8: I8,
 }
 
 
@@ -112,6 +113,9 @@ def _load():
     lib.tb_mxfp4_scales_to_atoms.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                              ctypes.c_void_p, ctypes.c_void_p]
     lib.tb_mxfp4_scales_to_atoms.restype = ctypes.c_int
+    lib.tb_fp8_quant_rows.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                      ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
+    lib.tb_fp8_quant_rows.restype = ctypes.c_int
     lib.tb_device_status.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)]
     lib.tb_device_status.restype = ctypes.c_int
     lib.tb_device_info.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]

@@ -134,6 +134,7 @@ static int esize_of(int dtype) {
     case TB_DTYPE_F32: return 4;
     case TB_DTYPE_E4M3:
     case TB_DTYPE_E5M2:
+    case TB_DTYPE_I8:
     case TB_DTYPE_U8: return 1;
     default: return 0;
   }
@@ -189,7 +190,8 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   if (a.k == 0) return TB_ERR_UNSUPPORTED;
   const int es = esize_of(a.a_dtype);
   if (es == 0 || a.a_dtype == TB_DTYPE_U8) return TB_ERR_UNSUPPORTED;
-  if (a.c_dtype != TB_DTYPE_F16 && a.c_dtype != TB_DTYPE_BF16 && a.c_dtype != TB_DTYPE_F32 && a.c_dtype != TB_DTYPE_E4M3)
+  if (a.c_dtype != TB_DTYPE_F16 && a.c_dtype != TB_DTYPE_BF16 && a.c_dtype != TB_DTYPE_F32 && a.c_dtype != TB_DTYPE_E4M3 &&
+      a.c_dtype != TB_DTYPE_I8)
     return TB_ERR_UNSUPPORTED;
 
   DeviceState* dev = nullptr;
@@ -302,9 +304,11 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
     case TB_DTYPE_F32: kind = 1; fmt = 2; break;
     case TB_DTYPE_E4M3: kind = 2; fmt = 0; break;
     case TB_DTYPE_E5M2: kind = 2; fmt = 1; break;
+    case TB_DTYPE_I8: kind = 4; fmt = 1; break;   // signed 8-bit
     default: return TB_ERR_UNSUPPORTED;
   }
-  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
+  const uint32_t c_fmt = kind == 4 ? 2u : 1u;     // accumulator: int32 for the integer kind, fp32 otherwise
+  p.idesc = (c_fmt << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
             (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>((128 * pair) >> 4) << 24);
 
   // schedule
@@ -361,10 +365,12 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   if (pair == 1) {
     if (kind == 0) TB_LAUNCH(0, 1);
     if (kind == 1) TB_LAUNCH(1, 1);
+    if (kind == 4) TB_LAUNCH(4, 1);
     TB_LAUNCH(2, 1);
   } else {
     if (kind == 0) TB_LAUNCH(0, 2);
     if (kind == 1) TB_LAUNCH(1, 2);
+    if (kind == 4) TB_LAUNCH(4, 2);
     TB_LAUNCH(2, 2);
   }
 #undef TB_LAUNCH

@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB = os.path.join(PKG, "libtritonblas_b200.so")
-SOURCES = ["api.cu", "simt_gemm.cu", "quant_mxfp4.cu", "moe_ops.cu", "selector.cpp"]
+SOURCES = ["api.cu", "simt_gemm.cu", "quant_mxfp4.cu", "quant_fp8.cu", "moe_ops.cu", "selector.cpp"]
 HEADERS_DIRS = [HERE, os.path.join(os.path.dirname(PKG), "include")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

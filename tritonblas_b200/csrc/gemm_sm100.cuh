@@ -35,7 +35,7 @@ template <int KIND>
 constexpr int gemm_threads() { return kGemmThreads; }
 constexpr int kATileBytes = kTileM * kStageRowBytes;  // 16 KB
 
-enum : int { TB_F16 = 0, TB_BF16 = 1, TB_F32 = 2, TB_E4M3 = 3, TB_E5M2 = 4, TB_U8 = 5 };
+enum : int { TB_F16 = 0, TB_BF16 = 1, TB_F32 = 2, TB_E4M3 = 3, TB_E5M2 = 4, TB_U8 = 5, TB_I8 = 7 };
 
 struct GemmParams {
   int M, N, K;
@@ -234,6 +234,11 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, void* c_bas
       for (int j = 0; j < 32; ++j)
         if (j < ncols) base[j * p.ldc_n] = v[j];
     }
+  } else if (p.c_dtype == TB_I8) {  // int8 output: round to nearest even, saturate
+    signed char* base = reinterpret_cast<signed char*>(c_base) + row * p.ldc_m + col0 * p.ldc_n;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) base[j * p.ldc_n] = static_cast<signed char>(__float2int_rn(fminf(fmaxf(v[j], -128.0f), 127.0f)));
   } else {  // fp8 e4m3 output, saturating
     unsigned char* base = reinterpret_cast<unsigned char*>(c_base) + row * p.ldc_m + col0 * p.ldc_n;
 #pragma unroll
@@ -578,7 +583,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         tmem_ld_wait();
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j)
+          v[j] = (KIND == 4) ? __int2float_rn(static_cast<int>(r[j])) : __uint_as_float(r[j]);  // int8 kind: int32 sums
         if (!owner) {
           // Publish a partial tile: column-major inside the slot so that a warp writes 128 contiguous bytes.
           float* dst = p.partials + slot * slot_elems + static_cast<size_t>(c * 32) * kTileM + row_in_tile;

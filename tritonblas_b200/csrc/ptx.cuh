@@ -235,7 +235,7 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// MMA kinds: 0 = f16/bf16 operands, 1 = tf32, 2 = 8-bit floats (e4m3/e5m2).
+// MMA kinds: 0 = f16/bf16 operands, 1 = tf32, 2 = 8-bit floats (e4m3/e5m2), 4 = signed 8-bit integers (int32 accumulate).
 template <int KIND, int CTAS>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
 #define TB_UMMA(G, K)                                                                            \
@@ -246,10 +246,12 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
   if constexpr (CTAS == 1) {
     if constexpr (KIND == 0) TB_UMMA("1", "f16");
     else if constexpr (KIND == 1) TB_UMMA("1", "tf32");
+    else if constexpr (KIND == 4) TB_UMMA("1", "i8");
     else TB_UMMA("1", "f8f6f4");
   } else {
     if constexpr (KIND == 0) TB_UMMA("2", "f16");
     else if constexpr (KIND == 1) TB_UMMA("2", "tf32");
+    else if constexpr (KIND == 4) TB_UMMA("2", "i8");
     else TB_UMMA("2", "f8f6f4");
   }
 #undef TB_UMMA

@@ -26,6 +26,7 @@ static int esize_of(int dtype) {
     case TB_DTYPE_F32: return 4;
     case TB_DTYPE_E4M3:
     case TB_DTYPE_E5M2:
+    case TB_DTYPE_I8:
     case TB_DTYPE_U8: return 1;
     default: return 0;
   }

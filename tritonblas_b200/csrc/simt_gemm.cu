@@ -39,6 +39,7 @@ __device__ __forceinline__ float ld_elem(const void* p, long long i, int dtype) 
       __half_raw h = __nv_cvt_fp8_to_halfraw(reinterpret_cast<const unsigned char*>(p)[i], __NV_E5M2);
       return __half2float(*reinterpret_cast<__half*>(&h));
     }
+    case TB_DTYPE_I8: return static_cast<float>(reinterpret_cast<const signed char*>(p)[i]);
     default: return 0.f;
   }
 }
@@ -50,6 +51,9 @@ __device__ __forceinline__ void st_elem(void* p, long long i, int dtype, float v
     case TB_DTYPE_F32: reinterpret_cast<float*>(p)[i] = v; break;
     case TB_DTYPE_E4M3:
       reinterpret_cast<unsigned char*>(p)[i] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+      break;
+    case TB_DTYPE_I8:
+      reinterpret_cast<signed char*>(p)[i] = static_cast<signed char>(__float2int_rn(fminf(fmaxf(v, -128.0f), 127.0f)));
       break;
     default: break;
   }

@@ -36,7 +36,7 @@ class _Hardware:
         self.lds_capacity = smem
 
 
-_STR_DTYPES = {"f16": _lib.F16, "bf16": _lib.BF16, "f32": _lib.F32, "f8": _lib.E4M3, "f4": _lib.F4}
+_STR_DTYPES = {"f16": _lib.F16, "bf16": _lib.BF16, "f32": _lib.F32, "f8": _lib.E4M3, "f4": _lib.F4, "i8": _lib.I8}
 
 
 def _dtype_code(dt):

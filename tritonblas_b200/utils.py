@@ -140,6 +140,29 @@ def mxfp4_scales_to_atoms(scales, k=None):
     return Mxfp4ScaleAtoms(atoms, rows, k)
 
 
+def quantize_fp8_rows(x: torch.Tensor):
+    """Per-row FP8 e4m3 quantisation on the GPU (one CUDA kernel): returns (q (rows, K) float8_e4m3fn, scale (rows,)
+    fp32) with scale = max(amax, 1e-8) / 448 and q = (x * (1 / scale)).to(e4m3), the arithmetic of
+    quantize_tensor_per_channel(x, float8_e4m3fn, axis=1). Use it on activations (per token) and on weights stored
+    (N, K) (per output channel)."""
+    assert x.ndim == 2 and x.shape[1] % 8 == 0, "x must be (rows, K) with K a multiple of 8"
+    if not x.is_cuda:
+        raise RuntimeError("the FP8 quantiser runs on CUDA tensors only (no CPU path)")
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError(f"Unsupported input dtype: {x.dtype}")
+    if x.stride(1) != 1 or (x.stride(0) * 2) % 16 != 0 or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+    if x.numel():
+        with torch.cuda.device(x.device):
+            rc = _lib.lib.tb_fp8_quant_rows(ctypes.c_void_p(x.data_ptr()), _lib.DTYPE_CODE[x.dtype], x.shape[0], x.shape[1],
+                                            x.stride(0), ctypes.c_void_p(q.data_ptr()), q.stride(0),
+                                            ctypes.c_void_p(scale.data_ptr()), _lib.current_stream_ptr(x.device))
+        _lib.check(rc, "tb_fp8_quant_rows")
+    return q, scale
+
+
 def _mxfp4_quant(x, hadamard, scale_atoms=False):
     assert x.ndim == 2, "Input must be 2D tensor"
     M, N = x.shape
