@@ -38,16 +38,20 @@ def test_grouped_matches_oracle(counts, n, k):
 
 
 def test_grouped_moe_projection_shapes():
-    """BASELINE config 5 geometry at 1/8 token count: 64 experts, Zipf(1.1)-skewed counts, hidden 4096, ffn 1536;
-    gate/up (N = 3072) and down (N = 4096) projections, 48 sampled rows checked per projection."""
+    """BASELINE config 5 at full size: 64 experts, top-8 of 16384 tokens (131072 rows), Zipf(1.1)-skewed counts, hidden
+    4096, ffn 1536; gate/up (N = 3072) and down (N = 4096) projections, 48 sampled rows checked per projection."""
     g = torch.Generator().manual_seed(7)
-    E, tokens, topk = 64, 2048, 8
+    E, tokens, topk = 64, 16384, 8
     p = (torch.arange(1, E + 1, dtype=torch.float64) ** -1.1)
     p = (p / p.sum())[torch.randperm(E, generator=g)]
     choice = torch.multinomial(p.expand(tokens, E), topk, replacement=False, generator=g)
     counts = torch.bincount(choice.flatten(), minlength=E).tolist()
+    gd = torch.Generator(device="cuda").manual_seed(11)
     for n, k in ((3072, 4096), (4096, 1536)):
-        x, w, offs = _case(counts, n, k, seed=n)
+        # generated on the device: the host copy of these operands would be several GB of fp32
+        x = torch.randn(sum(counts), k, device="cuda", generator=gd).to(torch.bfloat16)
+        w = (torch.randn(E, n, k, device="cuda", generator=gd) * 0.05).to(torch.bfloat16)
+        offs = torch.tensor([0] + torch.tensor(counts).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
         y = tb.grouped_matmul(x, w, offs)
         rows = torch.randint(0, x.shape[0], (48,), generator=g)
         # oracle on the sampled rows only: find each row's expert from the offsets

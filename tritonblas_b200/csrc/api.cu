@@ -285,6 +285,10 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   p.bias_along_m = swapped ? 1 : 0;
   p.status = dev->status;
   p.timeout_ns = 2000000000ull;
+  {
+    const char* tmo = getenv("TB_WAIT_TIMEOUT_MS");  // bound of every device-side wait (default 2 s)
+    if (tmo != nullptr && atoi(tmo) > 0) p.timeout_ns = static_cast<unsigned long long>(atoi(tmo)) * 1000000ull;
+  }
   if (grouped) {
     p.group_offsets = a.group_offsets;
     p.num_groups = a.num_groups;

@@ -77,7 +77,8 @@ struct GemmParams {
   // block-scaled (MXFP4) operands: scale factors arrive through two extra tensor maps over the pre-arranged
   // ("atom") layout [128-row group][K atom of 128 elements][512 bytes]
   long long* debug_out;  // bit 1 of debug_flags: per-CTA cycle counters of each role are written here
-  int debug_flags;  // measurement-only knobs (results are wrong when set): bit 0 = do not reload B on odd K blocks
+  int debug_flags;  // test / measurement knobs (results are wrong when set): bit 0 = do not reload B on odd K blocks,
+                    // bit 1 = per-role cycle counters, bit 2 = stream-K programs never publish their partial-tile flag
 };
 
 struct WorkItem {
@@ -682,7 +683,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(publish_bar);
         if (warp == 2 && lane == 0) {
-          if (mbar_wait(publish_bar, 0, wctx, TB_DEV_TIMEOUT_STORE)) flag_release(&p.flags[slot], p.epoch);
+          // debug bit 2 (value 4) withholds the flag: the failure-path test uses it to make the owner's bounded wait run out
+          if (mbar_wait(publish_bar, 0, wctx, TB_DEV_TIMEOUT_STORE) && !(p.debug_flags & 4)) flag_release(&p.flags[slot], p.epoch);
         }
       }
       if (++acc == 2) {
