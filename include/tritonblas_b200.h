@@ -70,6 +70,9 @@ typedef struct tb_config {
   int32_t tmem_cols;
   float predicted_us;     /* model estimate for the data-parallel schedule */
   float predicted_sk_us;  /* model estimate for the stream-K schedule */
+  int32_t n_halves;  /* 1, or 2: a work tile is two block_n-wide accumulators side by side that share every A stage
+                        (tile = block_m x 2*block_n; fewer L2 -> shared-memory bytes per flop, no cross-tile epilogue
+                        overlap). 0 is read as 1. */
   int32_t swap_ab;   /* 1: the kernel computes C^T = B^T A^T (few rows of A: the weight matrix takes the 128-row side of
                         the tile); block_m/block_n then describe the swapped problem */
 } tb_config;

@@ -49,6 +49,37 @@ def test_tile_shapes(dt, pair, bn):
     assert_close_to_oracle(c, a, b, what=f"{dt} pair={pair} bn={bn}")
 
 
+@pytest.mark.parametrize("pair,bn", [(1, 128), (1, 256), (2, 128), (2, 256)])
+@pytest.mark.parametrize("ta,tb_", LAYOUTS)
+@pytest.mark.parametrize("m,n,k", [(512, 1024, 512), (300, 700, 264), (1024, 520, 1024), (256, 4104, 512)])
+def test_wide_tiles(m, n, k, ta, tb_, pair, bn):
+    """n_halves = 2: a work tile is two accumulators side by side that share every A stage. Covers widths that end
+    inside the first half, inside the second half and exactly on a tile, for every operand layout."""
+    a, b = make_operands(m, n, k, torch.bfloat16, ta, tb_, seed=11)
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    tb.matmul_lt(a, b, c, _selector(m, n, k, torch.bfloat16, cta_pair=pair, block_n=bn, n_halves=2), None)
+    assert_close_to_oracle(c, a, b, what=f"wide {(m, n, k)} {ta}{tb_} pair={pair} bn={bn}")
+
+
+def test_wide_tiles_with_bias_and_fp32_output():
+    m, n, k = 384, 1536, 512
+    a, b = make_operands(m, n, k, torch.float16, "T", "T", seed=12)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(4)).to(torch.float16).cuda()
+    for out_dt in (torch.float16, torch.float32):
+        c = torch.empty(m, n, dtype=out_dt, device="cuda")
+        sel = _selector(m, n, k, torch.float16, out_dt=out_dt, block_n=256, n_halves=2)
+        tb.persistent_matmul_lt(a, b, c, sel, None, bias=bias)
+        assert_close_to_oracle(c, a, b, bias=bias, what=f"wide bias out={out_dt}")
+
+
+def test_selector_takes_wide_tiles_for_large_k_only():
+    dev = torch.device("cuda", 0)
+    bf = torch.bfloat16
+    assert tb.OrigamiMatmulSelector(8192, 8192, 8192, bf, bf, bf, dev).config_for(False, False).n_halves == 2
+    assert tb.OrigamiMatmulSelector(8192, 8192, 512, bf, bf, bf, dev).config_for(False, False).n_halves == 1
+    assert tb.OrigamiMatmulSelector(8192, 8192, 8192, bf, bf, bf, dev, streamk=True).config_for(False, False).n_halves == 1
+
+
 @pytest.mark.parametrize("m,n,k", STANDARD_DIMS + EDGE_CASE_DIMS)
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 def test_matmul_default_selector(m, n, k, dt):

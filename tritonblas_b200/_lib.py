@@ -33,7 +33,8 @@ class Problem(ctypes.Structure):
 class Config(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in (
         "block_m", "block_n", "block_k", "group_m", "stages", "cta_pair", "grid", "sk_grid", "num_sms", "smem_bytes",
-        "tmem_cols")] + [("predicted_us", ctypes.c_float), ("predicted_sk_us", ctypes.c_float), ("swap_ab", ctypes.c_int32)]
+        "tmem_cols")] + [("predicted_us", ctypes.c_float), ("predicted_sk_us", ctypes.c_float), ("n_halves", ctypes.c_int32),
+                                ("swap_ab", ctypes.c_int32)]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}

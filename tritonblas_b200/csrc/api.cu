@@ -154,7 +154,11 @@ MachineModel machine_for(const DeviceState* d) {
 template <int KIND, int CTAS>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const GemmParams& p, int programs, int smem_bytes,
                        cudaStream_t stream, const CUtensorMap* tsfa = nullptr, const CUtensorMap* tsfb = nullptr) {
-  auto kernel = gemm_kernel<KIND, CTAS>;
+  auto kernel = gemm_kernel<KIND, CTAS, false>;
+  // The instantiation with per-role cycle counters exists for 16-bit operands only (measurement runs).
+  if constexpr (KIND == 0) {
+    if ((p.debug_flags & 2) && p.debug_out != nullptr) kernel = gemm_kernel<KIND, CTAS, true>;
+  }
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
   cudaLaunchConfig_t lc = {};
@@ -249,20 +253,23 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   if ((bn / pair) % 16 != 0) return TB_ERR_INVALID;
   if (b_mn && ((bn / pair) % mn_atom) != 0) return TB_ERR_INVALID;
   const int bk = 128 / es;
+  // wide tiles (two accumulators sharing A) only for the data-parallel schedule: stream-K partials are per accumulator
+  const int halves = (cfg.n_halves == 2 && !a.streamk && !grouped) ? 2 : 1;
   int stages = cfg.stages;
   if (stages < 2) stages = 2;
   const int extra_smem = grouped ? 8 * (a.num_groups + 2) : 0;  // per-group tile prefix + copy of the row offsets
-  while (stages > 2 && smem_bytes_for(bn, pair, stages) + extra_smem > dev->smem_optin) --stages;
-  const int smem_bytes = smem_bytes_for(bn, pair, stages) + extra_smem;
+  while (stages > 2 && smem_bytes_for(bn, pair, stages, halves) + extra_smem > dev->smem_optin) --stages;
+  const int smem_bytes = smem_bytes_for(bn, pair, stages, halves) + extra_smem;
   if (smem_bytes > dev->smem_optin) return TB_ERR_INVALID;
 
   GemmParams p = {};
   p.M = a.m; p.N = a.n; p.K = a.k;
   p.block_n = bn;
+  p.n_halves = halves;
   p.k_per_stage = bk;
   p.num_k_blocks = (a.k + bk - 1) / bk;
   p.tiles_m = (a.m + 128 * pair - 1) / (128 * pair);
-  p.tiles_n = (a.n + bn - 1) / bn;
+  p.tiles_n = (a.n + bn * halves - 1) / (bn * halves);
   p.group_m = cfg.group_m > 0 ? cfg.group_m : 8;
   p.stages = stages;
   p.esize = es;
@@ -419,6 +426,7 @@ static int gemm_mxfp4_impl(const tb_mxfp4_args& a, cudaStream_t stream) {
   GemmParams p = {};
   p.M = a.m; p.N = a.n; p.K = a.k;
   p.block_n = bn;
+  p.n_halves = 1;
   p.k_per_stage = 128;  // bytes of packed K per stage (256 elements)
   p.num_k_blocks = (kbytes + 127) / 128;
   p.tiles_m = (a.m + 128 * pair - 1) / (128 * pair);
@@ -565,6 +573,7 @@ static int gemm_streamk_builtin_impl(const tb_gemm_args& in, const tb_config* us
   GemmParams p = {};
   p.M = a.m; p.N = a.n; p.K = a.k;
   p.block_n = bn;
+  p.n_halves = 1;
   p.k_per_stage = bk;
   p.num_k_blocks = (a.k + bk - 1) / bk;
   p.tiles_m = (a.m + 128 * pair - 1) / (128 * pair);

@@ -7,13 +7,17 @@
 // Roles inside a CTA of 192 threads:
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocator + MMA issuer (one elected lane; in a CTA pair only the even CTA issues)
-//   warps 2..5  epilogue: TMEM -> registers -> (stream-K fix-up) -> scale, bias, cast -> global
+//   warps 2..5  epilogue: TMEM -> registers -> (stream-K fix-up) -> scale, bias, cast -> global. A TMEM load takes
+//               several hundred clocks to return and a warp can only wait for all of its loads at once, so each warp
+//               issues the loads of a 64-column run together before it waits.
 // The accumulator is double-buffered in TMEM so the epilogue of one work item overlaps the main loop of the next.
 //
 // Semantics follow the reference kernels: tile order with GROUP_SIZE_M swizzle (kernels/stages/schedule.py:124-145),
 // epilogue order scale -> bias -> cast -> masked store (kernels/stages/matrix_view.py:263-301), hybrid stream-K with
 // fp32 partial tiles reduced by the tile owner in increasing program order (kernels/streamk_gemm.py:175-324).
 #pragma once
+#include <type_traits>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -24,9 +28,12 @@ namespace tb {
 
 constexpr int kTileM = 128;          // accumulator rows per CTA (TMEM lanes)
 constexpr int kStageRowBytes = 128;  // one swizzle row: K extent of a stage in bytes for K-major operands
-constexpr int kGemmThreads = 192;      // producer + MMA + 4 epilogue warps
-constexpr int kEpiRowPitch = 144;                    // bytes between rows of an epilogue warp's staging buffer (128 + pad)
-constexpr int kEpiStageBytes = 4 * 32 * kEpiRowPitch;  // four epilogue warps x 32 rows
+constexpr int kEpiWarps = 4;                         // one per TMEM lane quarter
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;    // producer + MMA + epilogue warps
+constexpr int kEpiWarp0 = 2;                         // first epilogue warp
+constexpr int kEpiRowPitch = 128;                    // bytes per row of an epilogue warp's staging buffer; the eight 16-byte
+                                                     // pieces of a row are XOR-swizzled with the row index (no padding)
+constexpr int kEpiStageBytes = kEpiWarps * 32 * kEpiRowPitch;
 constexpr int kSfAtomBytes = 512;      // scale factors of 128 rows x 4 K blocks, laid out [32 rows][4 row quads][4 blocks]
 constexpr int kSfGroupsB = 2;          // 128-row scale groups staged for B: tiles are 64, 128 or 192 columns wide and start
                                        // at a multiple of 64 (the MMA takes its scale columns from an even TMEM column),
@@ -39,7 +46,9 @@ enum : int { TB_F16 = 0, TB_BF16 = 1, TB_F32 = 2, TB_E4M3 = 3, TB_E5M2 = 4, TB_U
 
 struct GemmParams {
   int M, N, K;
-  int block_n;       // output tile width (columns), multiple of 32, <= 256. For a CTA pair: the pair's tile width.
+  int block_n;       // accumulator width (columns), multiple of 32, <= 256. For a CTA pair: the pair's width.
+  int n_halves;      // 1, or 2: a work tile is two accumulators side by side (2 * block_n columns) that share the A
+                     // tile of every stage; both TMEM accumulator stages then belong to one tile (no cross-tile overlap)
   int num_k_blocks;  // ceil(K / k elements per stage)
   int k_per_stage;   // K elements per stage
   int tiles_m, tiles_n, group_m;
@@ -77,7 +86,7 @@ struct GemmParams {
   // block-scaled (MXFP4) operands: scale factors arrive through two extra tensor maps over the pre-arranged
   // ("atom") layout [128-row group][K atom of 128 elements][512 bytes]
   long long* debug_out;  // bit 1 of debug_flags: per-CTA cycle counters of each role are written here
-  int debug_flags;  // test / measurement knobs (results are wrong when set): bit 0 = do not reload B on odd K blocks,
+  int debug_flags;  // test / measurement knobs (results are wrong when set): bit 0 = unused,
                     // bit 1 = per-role cycle counters, bit 2 = stream-K programs never publish their partial-tile flag
 };
 
@@ -155,7 +164,7 @@ __device__ __forceinline__ TileGeom tile_geometry(const GemmParams& p, int tile,
     tile_coords(p, tile, tm, tn);
     g.m0 = tm * tile_m;
     g.row_end = p.M;
-    g.n0 = tn * p.block_n;
+    g.n0 = tn * p.block_n * p.n_halves;
     g.b_row0 = g.n0;
     return g;
   }
@@ -171,7 +180,7 @@ __device__ __forceinline__ TileGeom tile_geometry(const GemmParams& p, int tile,
   tile_coords_dims(tile - tile_prefix[lo], tiles_m, p.tiles_n, p.group_m, tm, tn);
   g.m0 = row0 + tm * tile_m;
   g.row_end = row1;
-  g.n0 = tn * p.block_n;
+  g.n0 = tn * p.block_n * p.n_halves;
   g.b_row0 = lo * p.N + g.n0;
   return g;
 }
@@ -248,7 +257,100 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, void* c_bas
   }
 }
 
-template <int KIND, int CTAS>
+// Fast-path epilogue math for 32 columns of one row: scale -> bias -> cast to the 16-bit output type, then the 64 bytes
+// go into this lane's staging row as four 16-byte pieces, XOR-swizzled with the row index.
+template <int KIND, bool BF16, bool MATH>
+__device__ __forceinline__ void pack_chunk(const GemmParams& p, const uint32_t (&r)[32], uint8_t* mine, int lane, int col0,
+                                           int piece0, float a_s, int row, int row_end) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = (KIND == 4) ? __int2float_rn(static_cast<int>(r[j])) : __uint_as_float(r[j]);
+  if constexpr (MATH) {
+    if (p.a_scale != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= a_s;
+    }
+    if (p.b_scale != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= p.b_scale[col0 + j];
+    }
+    if (p.bias != nullptr) {
+      if (p.bias_along_m) {
+        const float bv = row < row_end ? load_as_float(p.bias, row * p.bias_stride, p.bias_dtype) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += bv;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += load_as_float(p.bias, (col0 + j) * p.bias_stride, p.bias_dtype);
+      }
+    }
+  }
+  uint32_t w[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    if constexpr (BF16) {
+      __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&t);
+    } else {
+      __half2 t = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&t);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(mine + (((piece0 + j) ^ (lane & 7)) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+}
+
+// Drain of one whole 128 x block_n accumulator to a 16-bit row-major C (block_n a multiple of 64), straight-line per
+// 64-column run: two TMEM loads in flight, pack into the warp's staging rows, read back as 128-byte row runs, store.
+// `release` hands the accumulator back to the MMA issuer; it is called once the last columns sit in registers.
+template <int KIND, bool kBf16, bool kMath, bool kExtra, typename Release>
+__device__ __forceinline__ void fast_drain(const GemmParams& p, uint8_t* stg, uint32_t t_row, int nchunks, int lane, int q,
+                                           int m0, int n0, int row, int row_end, float a_s, Release&& release_accumulator) {
+
+  const int seg = lane & 7, sub = lane >> 3;
+  uint8_t* mine = stg + lane * kEpiRowPitch;
+  unsigned short* c_rows = reinterpret_cast<unsigned short*>(p.C) +
+                           static_cast<long long>(m0 + q * 32 + sub) * p.ldc_m + n0 + seg * 8;
+  const long long off_base = static_cast<long long>(m0 + q * 32 + sub) * p.ldc_m + n0 + seg * 8;
+  const int rows_left = row_end - (m0 + q * 32 + sub);  // this lane stores rows it*4 < rows_left
+  for (int c0 = 0; c0 < nchunks; c0 += 2) {
+    uint32_t r0[32], r1[32];
+    tmem_ld_32x32(t_row + c0 * 32, r0);
+    tmem_ld_32x32(t_row + (c0 + 1) * 32, r1);
+    tmem_ld_wait(r0);
+    tmem_ld_wait(r1);
+    if (c0 + 2 >= nchunks) release_accumulator();  // the last columns sit in registers
+    pack_chunk<KIND, kBf16, kMath>(p, r0, mine, lane, n0 + c0 * 32, 0, a_s, row, row_end);
+    pack_chunk<KIND, kBf16, kMath>(p, r1, mine, lane, n0 + c0 * 32 + 32, 4, a_s, row, row_end);
+    __syncwarp();
+    uint4 val[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int row_l = it * 4 + sub;
+      val[it] = *reinterpret_cast<const uint4*>(stg + row_l * kEpiRowPitch + ((seg ^ (row_l & 7)) << 4));
+    }
+#pragma unroll
+    for (int it = 0; it < 8; ++it)
+      if (it * 4 < rows_left)
+        *reinterpret_cast<uint4*>(c_rows + static_cast<long long>(it * 4) * p.ldc_m + c0 * 32) = val[it];
+    if constexpr (kExtra) {
+      for (int x = 0; x < p.num_c_extra; ++x) {
+        unsigned short* e_rows = reinterpret_cast<unsigned short*>(p.c_extra[x]) + off_base + c0 * 32;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          // read the staged piece again rather than keep 32 registers live across this loop
+          const int row_l = it * 4 + sub;
+          const uint4 again = *reinterpret_cast<const uint4*>(stg + row_l * kEpiRowPitch + ((seg ^ (row_l & 7)) << 4));
+          if (it * 4 < rows_left) *reinterpret_cast<uint4*>(e_rows + static_cast<long long>(it * 4) * p.ldc_m) = again;
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
+template <int KIND, int CTAS, bool PROF = false>
 __global__ void __launch_bounds__(gemm_threads<KIND>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p) {
@@ -267,7 +369,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   // Block-scaled kinds append the stage's scale factors: two K atoms for this CTA's A rows, then two K atoms for each
   // of the two 128-row groups of B that can overlap the tile.
   const int sf_bytes = (KIND == 3) ? (2 + 2 * kSfGroupsB) * kSfAtomBytes : 0;
-  const int stage_bytes = (kATileBytes + b_tile_bytes + sf_bytes + 1023) & ~1023;
+  const int nh = (KIND == 3) ? 1 : p.n_halves;  // B tiles (and accumulators) per work tile
+  const int stage_bytes = (kATileBytes + nh * b_tile_bytes + sf_bytes + 1023) & ~1023;
   const int stages = p.stages;
 
   uint8_t* ring = smem;
@@ -283,7 +386,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   int* tile_prefix = reinterpret_cast<int*>(tmem_ptr_slot + 2);  // grouped mode: [num_groups + 1]
 
   WaitCtx wctx{abort_flag, p.status, p.timeout_ns};
-  const bool prof = (p.debug_flags & 2) != 0;  // measurement builds: per-role cycle counters
+  constexpr bool prof = PROF;  // measurement instantiation: per-role cycle counters written to debug_out
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -293,9 +396,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4 * CTAS);  // one arrival per epilogue warp of every CTA that shares the accumulator
+      mbar_init(&tmem_empty[a], kEpiWarps * CTAS);  // one arrival per epilogue warp of every CTA that shares the accumulator
     }
-    mbar_init(publish_bar, 4);
+    mbar_init(publish_bar, kEpiWarps);
     mbar_fence_init();
     if (p.group_offsets != nullptr) {
       // tile_prefix[0 .. G] = tiles before each group, followed by a copy of the G + 1 row offsets
@@ -341,7 +444,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t ph = 0;
       const int a_atom = kStageRowBytes / p.esize;  // elements per 128-byte row
       // In a pair, transaction bytes of both CTAs land on the even CTA's barrier, which expects the sum.
-      const uint32_t expect = static_cast<uint32_t>(kATileBytes + b_tile_bytes + sf_bytes) * CTAS;
+      const uint32_t expect = static_cast<uint32_t>(kATileBytes + nh * b_tile_bytes + sf_bytes) * CTAS;
       const int mn_box_bytes = p.k_per_stage * kStageRowBytes;
       bool ok = true;
       long long prof_wait = 0, prof_t0 = clock64();
@@ -358,22 +461,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           uint8_t* sa = ring + static_cast<size_t>(s) * stage_bytes;
           uint8_t* sb = sa + kATileBytes;
           const int k0 = kb * p.k_per_stage;
-          const bool skip_b = (p.debug_flags & 1) && (kb & 1);
           if (elect_one()) {
             if constexpr (CTAS == 1) {
-              mbar_arrive_expect_tx(&full_bar[s], skip_b ? static_cast<uint32_t>(kATileBytes) : expect);
+              mbar_arrive_expect_tx(&full_bar[s], expect);
               if (!p.a_mn) {
                 tma_load_2d(sa, &tmap_a, &full_bar[s], k0, m0);
               } else {
                 for (int j = 0; j < kTileM / a_atom; ++j)
                   tma_load_2d(sa + j * mn_box_bytes, &tmap_a, &full_bar[s], m0 + j * a_atom, k0);
               }
-              if (skip_b) {
-              } else if (!p.b_mn) {
-                tma_load_2d(sb, &tmap_b, &full_bar[s], k0, n0);
-              } else {
-                for (int j = 0; j < bn_local / a_atom; ++j)
-                  tma_load_2d(sb + j * mn_box_bytes, &tmap_b, &full_bar[s], n0 + j * a_atom, k0);
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                if (h >= nh) break;
+                uint8_t* sbh = sb + h * b_tile_bytes;
+                const int nh0 = n0 + h * p.block_n;
+                if (!p.b_mn) {
+                  tma_load_2d(sbh, &tmap_b, &full_bar[s], k0, nh0);
+                } else {
+                  for (int j = 0; j < bn_local / a_atom; ++j)
+                    tma_load_2d(sbh + j * mn_box_bytes, &tmap_b, &full_bar[s], nh0 + j * a_atom, k0);
+                }
               }
               if constexpr (KIND == 3) {
                 uint8_t* sf = sb + b_tile_bytes;
@@ -385,19 +492,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               }
             } else {
               const uint32_t bar = mapa_cluster(smem_u32(&full_bar[s]), 0);
-              if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], skip_b ? 2u * kATileBytes : expect);
+              if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], expect);
               if (!p.a_mn) {
                 tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
               } else {
                 for (int j = 0; j < kTileM / a_atom; ++j)
                   tma_load_2d_pair(sa + j * mn_box_bytes, &tmap_a, bar, m0 + j * a_atom, k0);
               }
-              if (skip_b) {
-              } else if (!p.b_mn) {
-                tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
-              } else {
-                for (int j = 0; j < bn_local / a_atom; ++j)
-                  tma_load_2d_pair(sb + j * mn_box_bytes, &tmap_b, bar, n0 + j * a_atom, k0);
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                if (h >= nh) break;
+                uint8_t* sbh = sb + h * b_tile_bytes;
+                const int nh0 = n0 + h * p.block_n;
+                if (!p.b_mn) {
+                  tma_load_2d_pair(sbh, &tmap_b, bar, k0, nh0);
+                } else {
+                  for (int j = 0; j < bn_local / a_atom; ++j)
+                    tma_load_2d_pair(sbh + j * mn_box_bytes, &tmap_b, bar, nh0 + j * a_atom, k0);
+                }
               }
               if constexpr (KIND == 3) {
                 // Each CTA of the pair needs the scales of its own A rows and of every B row of the tile.
@@ -429,7 +541,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
-      uint32_t acc_ph = 0;
       // Byte distances inside one operand tile (see make_smem_desc).
       const uint32_t mn_atom_stride = static_cast<uint32_t>(p.k_per_stage) * kStageRowBytes;
       const uint32_t a_lead = p.a_mn ? mn_atom_stride : 16u, b_lead = p.b_mn ? mn_atom_stride : 16u;
@@ -447,79 +558,131 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t idesc = p.idesc;
       bool ok = true;
       long long prof_full = 0, prof_tmem = 0, prof_issue = 0, prof_t0 = clock64();
+      uint32_t acc_parity = 0u;  // bit a: parity of how often TMEM accumulator a has been handed to the epilogue
+      // The four MMAs of one stage (32 bytes of K each) into one accumulator; called by the elected lane.
+      auto issue_stage = [&](uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t first) {
+        umma<KIND, CTAS>(d_tmem, adesc, bdesc, idesc, first);
+        umma<KIND, CTAS>(d_tmem, adesc + a_kstep, bdesc + b_kstep, idesc, 1u);
+        umma<KIND, CTAS>(d_tmem, adesc + 2 * a_kstep, bdesc + 2 * b_kstep, idesc, 1u);
+        umma<KIND, CTAS>(d_tmem, adesc + 3 * a_kstep, bdesc + 3 * b_kstep, idesc, 1u);
+      };
+      auto commit = [&](uint64_t* bar) {
+        if constexpr (CTAS == 1) umma_commit(bar);
+        else umma_commit_pair(bar, 3);
+      };
+      // This warp runs alone on its scheduler, so every instruction and every taken branch of the per-stage loop is
+      // exposed latency; the narrow and the wide tile therefore get a loop each, with nothing in it that can be
+      // decided per work item.
       for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
-        const long long pt0 = prof ? clock64() : 0;
-        ok = mbar_wait_warp(&tmem_empty[acc], acc_ph ^ 1, wctx, TB_DEV_TIMEOUT_TMEM_EMPTY);
+        // One accumulator per work item, alternating (the epilogue of one item overlaps the next item's main loop), or
+        // both accumulators for the two halves of a wide tile.
+        const int acc0 = (nh == 2) ? 0 : acc;
+        // the epilogue must have drained the accumulator before the first MMA of the item overwrites it
+        const long long pt0 = PROF ? clock64() : 0;
+        ok = mbar_wait_warp(&tmem_empty[acc0], ((acc_parity >> acc0) & 1u) ^ 1u, wctx, TB_DEV_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
-        if (prof) prof_tmem += clock64() - pt0;
+        if (PROF) prof_tmem += clock64() - pt0;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * acc_stride);
-        // Block-scaled kinds: where the tile's first column sits inside its first 128-row scale group.
-        const int mma_n0 = (KIND == 3) ? tile_geometry(p, w.tile, kPairTileM, tile_prefix).n0 : 0;
-        const uint32_t sfb_col0 = static_cast<uint32_t>(mma_n0 & 127) >> 5;
-        const int sf_groups_used = ((mma_n0 & 127) + p.block_n + 127) >> 7;
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          const long long pf0 = prof ? clock64() : 0;
-          ok = mbar_wait_warp(&full_bar[s], ph, wctx, TB_DEV_TIMEOUT_SMEM_FULL);
-          if (!ok) break;
-          const long long pf1 = prof ? clock64() : 0;
-          prof_full += pf1 - pf0;
-          const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * stage_step);
-          const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * stage_step);
-          const uint32_t first = (kb > w.kb0) ? 1u : 0u;
-          if (elect_one()) {
-            if constexpr (KIND == 3) {
-              // Scale factors of this stage: shared memory -> TMEM (one buffer, rewritten every stage; the copies and
-              // the MMAs that follow execute in issue order). TMEM columns, one per 32 rows:
-              //   [A atom0 (4) | A atom1 (4) | B atom0: 2 groups (8) | B atom1: 2 groups (8)].
-              const uint32_t sf_smem = ring_addr + static_cast<uint32_t>(s) * stage_bytes + kATileBytes + b_tile_bytes;
-              const uint32_t sfa_t = tmem_base + 2u * acc_stride;
-              const uint32_t sfb_t = sfa_t + 8u;
+        const uint32_t d0 = tmem_base + static_cast<uint32_t>(acc0 * acc_stride);
+        if (nh == 1) {
+          // Block-scaled kinds: where the tile's first column sits inside its first 128-row scale group.
+          const int mma_n0 = (KIND == 3) ? tile_geometry(p, w.tile, kPairTileM, tile_prefix).n0 : 0;
+          const uint32_t sfb_col0 = static_cast<uint32_t>(mma_n0 & 127) >> 5;
+          const int sf_groups_used = ((mma_n0 & 127) + p.block_n + 127) >> 7;
+          for (int kb = w.kb0; kb < w.kb1; ++kb) {
+            const long long pf0 = PROF ? clock64() : 0;
+            ok = mbar_wait_warp(&full_bar[s], ph, wctx, TB_DEV_TIMEOUT_SMEM_FULL);
+            if (!ok) break;
+            const long long pf1 = PROF ? clock64() : 0;
+            if (PROF) prof_full += pf1 - pf0;
+            const uint64_t soff = static_cast<uint64_t>(s * stage_step);
+            const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
+            const uint32_t first = (kb > w.kb0) ? 1u : 0u;
+            if (elect_one()) {
+              if constexpr (KIND == 3) {
+                // Scale factors of this stage: shared memory -> TMEM (one buffer, rewritten every stage; the copies and
+                // the MMAs that follow execute in issue order). TMEM columns, one per 32 rows:
+                //   [A atom0 (4) | A atom1 (4) | B atom0: 2 groups (8) | B atom1: 2 groups (8)].
+                const uint32_t sf_smem = ring_addr + static_cast<uint32_t>(s) * stage_bytes + kATileBytes + b_tile_bytes;
+                const uint32_t sfa_t = tmem_base + 2u * acc_stride;
+                const uint32_t sfb_t = sfa_t + 8u;
 #pragma unroll
-              for (int t = 0; t < 2; ++t)
-                tmem_cp_32x128b_warpx4<CTAS>(sfa_t + 4u * t, make_smem_desc_noswizzle(sf_smem + t * kSfAtomBytes, 16, 128));
+                for (int t = 0; t < 2; ++t)
+                  tmem_cp_32x128b_warpx4<CTAS>(sfa_t + 4u * t, make_smem_desc_noswizzle(sf_smem + t * kSfAtomBytes, 16, 128));
 #pragma unroll
-              for (int t = 0; t < 2; ++t)
+                for (int t = 0; t < 2; ++t)
 #pragma unroll
-                for (int g = 0; g < kSfGroupsB; ++g)
-                  if (g < sf_groups_used)
-                    tmem_cp_32x128b_warpx4<CTAS>(
-                        sfb_t + 4u * (t * kSfGroupsB + g),
-                        make_smem_desc_noswizzle(sf_smem + (2 + g * 2 + t) * kSfAtomBytes, 16, 128));
+                  for (int g = 0; g < kSfGroupsB; ++g)
+                    if (g < sf_groups_used)
+                      tmem_cp_32x128b_warpx4<CTAS>(
+                          sfb_t + 4u * (t * kSfGroupsB + g),
+                          make_smem_desc_noswizzle(sf_smem + (2 + g * 2 + t) * kSfAtomBytes, 16, 128));
 #pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                // an MMA covers 64 K elements = two scale bytes: bytes {0,1} or {2,3} of the atom's columns
-                const uint32_t sf_id = (k & 1) * 2u;
-                const uint32_t id = idesc | (sf_id << 4) | (sf_id << 29);
-                umma_mxf4<CTAS>(d_tmem, adesc + k * a_kstep, bdesc + k * b_kstep, id,
-                                (sfa_t + 4u * (k >> 1)) | (sf_id << 30),
-                                (sfb_t + 4u * (k >> 1) * kSfGroupsB + sfb_col0) | (sf_id << 30), k == 0 ? first : 1u);
+                for (int k = 0; k < 4; ++k) {
+                  // an MMA covers 64 K elements = two scale bytes: bytes {0,1} or {2,3} of the atom's columns
+                  const uint32_t sf_id = (k & 1) * 2u;
+                  const uint32_t id = idesc | (sf_id << 4) | (sf_id << 29);
+                  umma_mxf4<CTAS>(d0, adesc + k * a_kstep, bdesc + k * b_kstep, id,
+                                  (sfa_t + 4u * (k >> 1)) | (sf_id << 30),
+                                  (sfb_t + 4u * (k >> 1) * kSfGroupsB + sfb_col0) | (sf_id << 30), k == 0 ? first : 1u);
+                }
+              } else {
+                issue_stage(d0, adesc, bdesc, first);
               }
-            } else {
-              umma<KIND, CTAS>(d_tmem, adesc, bdesc, idesc, first);
-              umma<KIND, CTAS>(d_tmem, adesc + a_kstep, bdesc + b_kstep, idesc, 1u);
-              umma<KIND, CTAS>(d_tmem, adesc + 2 * a_kstep, bdesc + 2 * b_kstep, idesc, 1u);
-              umma<KIND, CTAS>(d_tmem, adesc + 3 * a_kstep, bdesc + 3 * b_kstep, idesc, 1u);
+              commit(&empty_bar[s]);  // frees the stage once every MMA that reads it has finished
+              if (kb + 1 == w.kb1) commit(&tmem_full[acc0]);
             }
-            // Free the stage once these MMAs have read it.
-            if constexpr (CTAS == 1) umma_commit(&empty_bar[s]);
-            else umma_commit_pair(&empty_bar[s], 3);
-            if (kb + 1 == w.kb1) {
-              if constexpr (CTAS == 1) umma_commit(&tmem_full[acc]);
-              else umma_commit_pair(&tmem_full[acc], 3);
+            __syncwarp();
+            if (PROF) prof_issue += clock64() - pf1;
+            if (++s == stages) {
+              s = 0;
+              ph ^= 1;
             }
           }
-          __syncwarp();
-          if (prof) prof_issue += clock64() - pf1;
-          if (++s == stages) {
-            s = 0;
-            ph ^= 1;
+          if (!ok) break;
+          acc_parity ^= 1u << acc0;
+          acc ^= 1;
+        } else {
+          // wide tile: accumulators 0 and 1 side by side, both fed from every stage's A tile
+          const uint32_t d1 = tmem_base + static_cast<uint32_t>(acc_stride);
+          const uint64_t half_off = static_cast<uint64_t>(b_tile_bytes >> 4);
+          for (int kb = w.kb0; kb < w.kb1; ++kb) {
+            const long long pf0 = PROF ? clock64() : 0;
+            ok = mbar_wait_warp(&full_bar[s], ph, wctx, TB_DEV_TIMEOUT_SMEM_FULL);
+            if (!ok) break;
+            const long long pf1 = PROF ? clock64() : 0;
+            if (PROF) prof_full += pf1 - pf0;
+            const uint64_t soff = static_cast<uint64_t>(s * stage_step);
+            const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
+            const uint32_t first = (kb > w.kb0) ? 1u : 0u;
+            const bool last = kb + 1 == w.kb1;
+            if (elect_one()) {
+              issue_stage(d0, adesc, bdesc, first);
+              if (last) commit(&tmem_full[0]);
+            }
+            __syncwarp();
+            if (kb == w.kb0) {
+              // the second accumulator may still be draining while the first already takes this stage
+              const long long pt1 = PROF ? clock64() : 0;
+              ok = mbar_wait_warp(&tmem_empty[1], ((acc_parity >> 1) & 1u) ^ 1u, wctx, TB_DEV_TIMEOUT_TMEM_EMPTY);
+              if (!ok) break;
+              if (PROF) prof_tmem += clock64() - pt1;
+              tc_fence_after();
+            }
+            if (elect_one()) {
+              issue_stage(d1, adesc, bdesc + half_off, first);
+              commit(&empty_bar[s]);
+              if (last) commit(&tmem_full[1]);
+            }
+            __syncwarp();
+            if (PROF) prof_issue += clock64() - pf1;
+            if (++s == stages) {
+              s = 0;
+              ph ^= 1;
+            }
           }
-        }
-        if (!ok) break;
-        if (++acc == 2) {
-          acc = 0;
-          acc_ph ^= 1;
+          if (!ok) break;
+          acc_parity ^= 3u;
         }
       }
       if (prof && p.debug_out != nullptr && lane == 0) {
@@ -529,30 +692,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         p.debug_out[blockIdx.x * 16 + 5] = clock64() - prof_t0;
       }
     }
-  } else {
+  } else if (warp >= kEpiWarp0) {
     // ------------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const int row_in_tile = q * 32 + lane;
-    uint8_t* stg = epi_stage + (warp - 2) * (32 * kEpiRowPitch);
+    uint8_t* stg = epi_stage + (warp - kEpiWarp0) * (32 * kEpiRowPitch);
     WorkIter wi(p, pid, nprog, grouped_tiles);
     int acc = 0;
-    uint32_t acc_ph = 0;
+    uint32_t epi_parity = 0u;  // bit a: parity of how often TMEM accumulator a has been drained
     const int slot = pid * CTAS + static_cast<int>(cta_rank);
     const size_t slot_elems = static_cast<size_t>(p.block_n) * kTileM;
     const uint32_t tmem_empty_remote = (CTAS == 2) ? mapa_cluster(smem_u32(&tmem_empty[0]), 0) : 0u;
     bool ok = true;
-    long long prof_wait = 0, prof_t0 = clock64();
+    long long prof_wait = 0, prof_t0 = clock64(), prof_drain = 0;
     for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
       const TileGeom tg = tile_geometry(p, w.tile, kPairTileM, tile_prefix);
       const int m0 = tg.m0 + static_cast<int>(cta_rank) * kTileM;
-      const int n0 = tg.n0;
       const int row_end = tg.row_end;
+      // A wide tile is two accumulators side by side: drain them one after the other.
+      for (int h = 0; h < nh && ok; ++h) {
+      const int acc_i = (nh == 2) ? h : acc;
+      const int n0 = tg.n0 + h * p.block_n;
       const long long pe0 = prof ? clock64() : 0;
       const int row = m0 + row_in_tile;
       const bool owner = (w.kb0 == 0);
       const bool complete = owner && (w.kb1 == p.num_k_blocks);
       // Every decision to unwind is made warp-uniform: the TMEM loads below need the whole warp.
-      ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_ph, wctx, TB_DEV_TIMEOUT_TMEM_FULL));
+      ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[acc_i], (epi_parity >> acc_i) & 1u, wctx, TB_DEV_TIMEOUT_TMEM_FULL));
       if (!ok) break;
       if (prof) prof_wait += clock64() - pe0;
       tc_fence_after();
@@ -577,104 +743,137 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int nchunks = p.block_n / 32;
       // staged stores need whole 32-column chunks inside N and 16-byte aligned rows in every destination (host-checked)
       const bool staged = owner && p.staged_store && (n0 + p.block_n <= p.N);
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * acc_stride);
-      for (int c = 0; c < nchunks; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c * 32, r);
-        tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          v[j] = (KIND == 4) ? __int2float_rn(static_cast<int>(r[j])) : __uint_as_float(r[j]);  // int8 kind: int32 sums
-        if (!owner) {
-          // Publish a partial tile: column-major inside the slot so that a warp writes 128 contiguous bytes.
-          float* dst = p.partials + slot * slot_elems + static_cast<size_t>(c * 32) * kTileM + row_in_tile;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) dst[j * kTileM] = v[j];
-          continue;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc_i * acc_stride);
+      // Hand the accumulator back to the MMA issuer: called once the last chunk sits in registers, before it is stored.
+      auto release_accumulator = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CTAS == 1) mbar_arrive(&tmem_empty[acc_i]);
+          else mbar_arrive_remote(tmem_empty_remote + acc_i * 8);
         }
-        for (int pp = pid + 1; pp < peer_end; ++pp) {
-          const float* src =
-              p.partials + (pp * CTAS + static_cast<int>(cta_rank)) * slot_elems + static_cast<size_t>(c * 32) * kTileM + row_in_tile;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * kTileM);
+      };
+      if (complete && staged && (p.block_n & 63) == 0) {
+        // Common case (whole tile, 16-bit row-major output, tile width a multiple of 64). Every taken branch inside
+        // the drain loop costs an instruction refetch, and a handful of them per 64 columns is what made a drain
+        // through the general path three to four times slower than its loads and stores take; so the loop below is
+        // straight-line, and the choices (output type, scales or bias, extra destinations) are made once per tile
+        // by picking one of its instantiations.
+        const bool has_math = p.a_scale != nullptr || p.b_scale != nullptr || p.bias != nullptr;
+        const long long q0 = prof ? clock64() : 0;
+#define TB_FAST_DRAIN(BF, MATH, EXTRA) \
+  fast_drain<KIND, BF, MATH, EXTRA>(p, stg, t_row, nchunks, lane, q, m0, n0, row, row_end, a_s, release_accumulator)
+        if (p.num_c_extra > 0) {
+          if (p.c_dtype == TB_BF16) { if (has_math) TB_FAST_DRAIN(true, true, true); else TB_FAST_DRAIN(true, false, true); }
+          else { if (has_math) TB_FAST_DRAIN(false, true, true); else TB_FAST_DRAIN(false, false, true); }
+        } else if (p.c_dtype == TB_BF16) {
+          if (has_math) TB_FAST_DRAIN(true, true, false); else TB_FAST_DRAIN(true, false, false);
+        } else {
+          if (has_math) TB_FAST_DRAIN(false, true, false); else TB_FAST_DRAIN(false, false, false);
         }
-        const int col0 = n0 + c * 32;
-        if (col0 < p.N && (staged || row < row_end)) {
-          if (p.a_scale != nullptr) {
+#undef TB_FAST_DRAIN
+        if (prof) prof_drain += clock64() - q0;
+      } else {
+        // General path: partial tiles of a stream-K launch, their fix-up, and every other output type and layout.
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait(r);
+          if (c + 1 == nchunks) release_accumulator();
+          float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= a_s;
+          for (int j = 0; j < 32; ++j)
+            v[j] = (KIND == 4) ? __int2float_rn(static_cast<int>(r[j])) : __uint_as_float(r[j]);  // int8 kind: int32 sums
+          if (!owner) {
+            // Publish a partial tile: column-major inside the slot so that a warp writes 128 contiguous bytes.
+            float* dst = p.partials + slot * slot_elems + static_cast<size_t>(c * 32) * kTileM + row_in_tile;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) dst[j * kTileM] = v[j];
+            continue;
           }
-          if (p.b_scale != nullptr) {
+          for (int pp = pid + 1; pp < peer_end; ++pp) {
+            const float* src =
+                p.partials + (pp * CTAS + static_cast<int>(cta_rank)) * slot_elems + static_cast<size_t>(c * 32) * kTileM + row_in_tile;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= (col0 + j < p.N) ? p.b_scale[col0 + j] : 1.0f;
+            for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * kTileM);
           }
-          if (p.bias != nullptr) {
-            if (p.bias_along_m) {
-              const float bv = row < row_end ? load_as_float(p.bias, row * p.bias_stride, p.bias_dtype) : 0.0f;
+          const int col0 = n0 + c * 32;
+          if (col0 < p.N && (staged || row < row_end)) {
+            if (p.a_scale != nullptr) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] += bv;
+              for (int j = 0; j < 32; ++j) v[j] *= a_s;
+            }
+            if (p.b_scale != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] *= (col0 + j < p.N) ? p.b_scale[col0 + j] : 1.0f;
+            }
+            if (p.bias != nullptr) {
+              if (p.bias_along_m) {
+                const float bv = row < row_end ? load_as_float(p.bias, row * p.bias_stride, p.bias_dtype) : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += bv;
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) v[j] += load_as_float(p.bias, (col0 + j) * p.bias_stride, p.bias_dtype);
+              }
+            }
+            if (!staged) {
+              store_row_chunk(p, p.C, row, col0, v);
+              for (int x = 0; x < p.num_c_extra; ++x) store_row_chunk(p, p.c_extra[x], row, col0, v);
+            }
+          }
+          if (staged) {
+            // 16-bit outputs with unit column stride: the warp's 32 rows x 64 columns pass through shared memory so that
+            // every row leaves as one 128-byte run (8 lanes x 16 bytes), which is what remote (NVLink) and local L2 writes
+            // both want, instead of 16-byte pieces of 32 different rows per store instruction.
+            uint8_t* mine = stg + lane * kEpiRowPitch;
+            const int piece0 = (c & 1) * 4;
+            uint32_t w[16];
+            if (p.c_dtype == TB_BF16) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                w[j] = *reinterpret_cast<uint32_t*>(&t);
+              }
             } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) v[j] += load_as_float(p.bias, (col0 + j) * p.bias_stride, p.bias_dtype);
-            }
-          }
-          if (!staged) {
-            store_row_chunk(p, p.C, row, col0, v);
-            for (int x = 0; x < p.num_c_extra; ++x) store_row_chunk(p, p.c_extra[x], row, col0, v);
-          }
-        }
-        if (staged) {
-          // 16-bit outputs with unit column stride: the warp's 32 rows x 64 columns pass through shared memory so that
-          // every row leaves as one 128-byte run (8 lanes x 16 bytes), which is what remote (NVLink) and local L2 writes
-          // both want, instead of 16-byte pieces of 32 different rows per store instruction.
-          uint8_t* mine = stg + lane * kEpiRowPitch + (c & 1) * 64;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t w[4];
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const float lo = v[j * 8 + h * 2], hi = v[j * 8 + h * 2 + 1];
-              if (p.c_dtype == TB_BF16) {
-                __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
-                w[h] = *reinterpret_cast<uint32_t*>(&t);
-              } else {
-                __half2 t = __floats2half2_rn(lo, hi);
-                w[h] = *reinterpret_cast<uint32_t*>(&t);
+              for (int j = 0; j < 16; ++j) {
+                __half2 t = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                w[j] = *reinterpret_cast<uint32_t*>(&t);
               }
             }
-            *reinterpret_cast<uint4*>(mine + j * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-          if ((c & 1) || c + 1 == nchunks) {
-            __syncwarp();
-            const int ncol = (c & 1) ? 64 : 32;
-            const int colw = n0 + (c & ~1) * 32;  // first column of the staged run
-            const int seg = lane & 7;
-            if (seg * 8 < ncol) {
 #pragma unroll
-              for (int it = 0; it < 8; ++it) {
-                const int row_l = it * 4 + (lane >> 3);
-                const int row_g = m0 + q * 32 + row_l;
-                if (row_g < row_end) {
-                  const uint4 val = *reinterpret_cast<const uint4*>(stg + row_l * kEpiRowPitch + seg * 16);
-                  const long long off = static_cast<long long>(row_g) * p.ldc_m + colw + seg * 8;
-                  *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.C) + off) = val;
-                  for (int x = 0; x < p.num_c_extra; ++x)
-                    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.c_extra[x]) + off) = val;
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(mine + (((piece0 + j) ^ (lane & 7)) << 4)) =
+                  make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+            if ((c & 1) || c + 1 == nchunks) {
+              __syncwarp();
+              const int ncol = (c & 1) ? 64 : 32;
+              const int colw = n0 + (c & ~1) * 32;  // first column of the staged run
+              const int seg = lane & 7;
+              if (seg * 8 < ncol) {
+                uint4 val[8];
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                  const int row_l = it * 4 + (lane >> 3);
+                  val[it] = *reinterpret_cast<const uint4*>(stg + row_l * kEpiRowPitch + ((seg ^ (row_l & 7)) << 4));
+                }
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                  const int row_g = m0 + q * 32 + it * 4 + (lane >> 3);
+                  if (row_g < row_end) {
+                    const long long off = static_cast<long long>(row_g) * p.ldc_m + colw + seg * 8;
+                    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.C) + off) = val[it];
+                    for (int x = 0; x < p.num_c_extra; ++x)
+                      *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.c_extra[x]) + off) = val[it];
+                  }
                 }
               }
+              __syncwarp();
             }
-            __syncwarp();
           }
         }
-      }
-      // Hand the accumulator back to the MMA issuer.
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (CTAS == 1) mbar_arrive(&tmem_empty[acc]);
-        else mbar_arrive_remote(tmem_empty_remote + acc * 8);
       }
       if (!owner) {
         // A program publishes at most one partial tile per launch (only its first stream-K segment can start
@@ -682,19 +881,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         __threadfence();
         __syncwarp();
         if (lane == 0) mbar_arrive(publish_bar);
-        if (warp == 2 && lane == 0) {
+        if (warp == kEpiWarp0 && lane == 0) {
           // debug bit 2 (value 4) withholds the flag: the failure-path test uses it to make the owner's bounded wait run out
           if (mbar_wait(publish_bar, 0, wctx, TB_DEV_TIMEOUT_STORE) && !(p.debug_flags & 4)) flag_release(&p.flags[slot], p.epoch);
         }
       }
-      if (++acc == 2) {
-        acc = 0;
-        acc_ph ^= 1;
-      }
+      epi_parity ^= 1u << acc_i;
+      }  // halves
+      if (nh == 1) acc ^= 1;
     }
-    if ((p.debug_flags & 2) && p.debug_out != nullptr && threadIdx.x == 64) {
+    if (prof && p.debug_out != nullptr && threadIdx.x == kEpiWarp0 * 32) {
       p.debug_out[blockIdx.x * 16 + 6] = prof_wait;
       p.debug_out[blockIdx.x * 16 + 7] = clock64() - prof_t0;
+      p.debug_out[blockIdx.x * 16 + 8] = prof_drain;
     }
   }
 

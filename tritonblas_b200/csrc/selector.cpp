@@ -38,13 +38,13 @@ static int next_pow2(int v) {
   return r;
 }
 
-int smem_bytes_for(int block_n, int cta_pair, int stages) {
-  const int stage = 128 * 128 + (block_n / cta_pair) * 128;
-  return stages * stage + 18432 + (2 * stages + 8) * 8 + 64 + 1024;  // ring + epilogue staging + barriers + slots + slack
+int smem_bytes_for(int block_n, int cta_pair, int stages, int n_halves) {
+  const int stage = 128 * 128 + n_halves * (block_n / cta_pair) * 128;
+  return stages * stage + 16384 + (2 * stages + 8) * 8 + 64 + 1024;  // ring + epilogue staging + barriers + slots + slack
 }
 
 struct Candidate {
-  int bn, pair;
+  int bn, pair, halves;
   double dp_us, sk_us;
   int grid, sk_grid, stages, group_m;
 };
@@ -93,33 +93,46 @@ int select_config(const tb_problem& p_in, const MachineModel& hw, tb_config* out
       if (p.b_mn_major && (bn_local % mn_atom) != 0) continue;
       if (bn >= 2 * p.n && bn > 32 && !(p.b_mn_major && bn <= mn_atom)) continue;  // more than half the tile would be padding
       if (bn_local < 16) continue;
+      // A wide tile (two bn-wide accumulators that share every A stage) only pays at the full accumulator width, and
+      // the stream-K, block-scaled and grouped paths do not take it.
+      const int max_halves = (!mx && !p.streamk && bn == 256 && p.n >= 2 * bn) ? 2 : 1;
+      for (int halves = max_halves; halves >= 1; --halves) {
       const int tile_m = 128 * pair;
-      const long long tiles_m = (p.m + tile_m - 1) / tile_m, tiles_n = (p.n + bn - 1) / bn;
+      const int tile_n = bn * halves;
+      const long long tiles_m = (p.m + tile_m - 1) / tile_m, tiles_n = (p.n + tile_n - 1) / tile_n;
       const long long tiles = tiles_m * tiles_n;
       const int programs = std::max(1, sms / pair);
       const int sf_bytes = mx ? (2 + 2 * 2) * 512 : 0;
-      int stages = (hw.smem_optin - 2048 - 18432) / ((128 * 128 + bn_local * 128 + sf_bytes + 1023) & ~1023);
+      const int stage_bytes = (128 * 128 + halves * bn_local * 128 + sf_bytes + 1023) & ~1023;
+      int stages = (hw.smem_optin - 2048 - 16384) / stage_bytes;
       stages = std::min(stages, 12);
       if (stages < 2) continue;
-      const double mma_clk = mma_clk_per_stage_per_bn * bn;
-      const double fill_clk = (128.0 + bn_local) * 128.0 / hw.fabric_bytes_per_clk;
+      const long long active_ctas = std::min<long long>(tiles, programs) * pair;
+      // L2 -> shared memory: one SM alone pulls fabric_bytes_per_clk, all of them together share the L2's total
+      const double fabric = std::min(hw.fabric_bytes_per_clk, hw.l2_bytes_per_clk / static_cast<double>(active_ctas));
+      const double mma_clk = mma_clk_per_stage_per_bn * bn * halves;
+      const double fill_clk = (128.0 + halves * bn_local) * 128.0 / fabric;
       const double stage_clk = std::max(mma_clk, fill_clk);
       const double ramp_clk = hw.tile_ramp_clk;  // first-stage latency + epilogue drain not hidden by the next tile
       const double clk_to_us = 1.0 / (hw.sm_mhz);
+      // Draining one 128 x bn accumulator. Two accumulator stages hide it behind the next tile's main loop unless
+      // that loop is shorter; a wide tile owns both stages, so its two drains are exposed.
+      const double drain_clk = 1000.0 + 12.0 * bn;
       // HBM floor: one SM cannot pull its share of the full bandwidth alone, so idle SMs cost bandwidth
-      auto hbm_floor = [&](long long active_ctas) {
-        const double share = std::min(1.0, 1.15 * static_cast<double>(active_ctas) / hw.num_sms);
+      auto hbm_floor = [&](long long active) {
+        const double share = std::min(1.0, 1.15 * static_cast<double>(active) / hw.num_sms);
         return hbm_us / share;
       };
       // data-parallel
       const long long waves = (tiles + programs - 1) / programs;
-      double dp = (waves * nkb * stage_clk + ramp_clk + bn * 8.0) * clk_to_us;
-      dp = std::max(dp, hbm_floor(std::min<long long>(tiles, programs) * pair)) + hw.launch_us;
+      const double tile_clk = halves == 2 ? nkb * stage_clk + 2.0 * drain_clk : std::max(nkb * stage_clk, drain_clk);
+      double dp = (waves * tile_clk + ramp_clk + drain_clk) * clk_to_us;
+      dp = std::max(dp, hbm_floor(active_ctas)) + hw.launch_us;
       // stream-K: stages per program, plus one partial tile written and read back through L2, plus the flag hop
       const int sk_grid = static_cast<int>(std::min<long long>(programs, tiles * nkb));
       const double per_prog = std::ceil(static_cast<double>(tiles) * nkb / sk_grid);
       const bool needs_fix = (tiles % sk_grid) != 0;
-      double sk = (per_prog * stage_clk + ramp_clk + bn * 8.0) * clk_to_us;
+      double sk = (per_prog * stage_clk + ramp_clk + drain_clk) * clk_to_us;
       if (needs_fix) sk += 2.0 * 128.0 * bn * 4.0 / (hw.fabric_bytes_per_clk * hw.sm_mhz) + hw.flag_us;
       sk = std::max(sk, hbm_floor(static_cast<long long>(sk_grid) * pair)) + hw.launch_us;
       const double cost = p.streamk ? sk : dp;
@@ -128,14 +141,16 @@ int select_config(const tb_problem& p_in, const MachineModel& hw, tb_config* out
         best_cost = cost;
         best.bn = bn;
         best.pair = pair;
+        best.halves = halves;
         best.dp_us = dp;
         best.sk_us = sk;
         best.grid = static_cast<int>(std::min<long long>(programs, tiles));
         best.sk_grid = sk_grid;
         best.stages = stages;
-        const double g = std::sqrt(static_cast<double>(programs) * bn / tile_m);
+        const double g = std::sqrt(static_cast<double>(programs) * tile_n / tile_m);
         best.group_m = static_cast<int>(std::max<long long>(1, std::min<long long>(tiles_m, std::llround(g))));
       }
+      }  // halves
     }
   }
   if (best_cost >= 1e30) return TB_ERR_UNSUPPORTED;
@@ -149,12 +164,13 @@ int select_config(const tb_problem& p_in, const MachineModel& hw, tb_config* out
   out->grid = best.grid;
   out->sk_grid = best.sk_grid;
   out->num_sms = sms;
-  out->smem_bytes = smem_bytes_for(best.bn, best.pair, best.stages) +
+  out->smem_bytes = smem_bytes_for(best.bn, best.pair, best.stages, best.halves) +
                     (mx ? best.stages * (2 + 2 * 2) * 512 : 0);
   out->tmem_cols = next_pow2(2 * best.bn + (mx ? 8 + 8 * 2 : 0));
   out->predicted_us = static_cast<float>(best.dp_us);
   out->predicted_sk_us = static_cast<float>(best.sk_us);
   out->swap_ab = swap ? 1 : 0;
+  out->n_halves = best.halves;
   return TB_OK;
 }
 

@@ -9,7 +9,8 @@ struct MachineModel {
   int smem_optin = 232448;       // bytes of shared memory one CTA may opt in to (227 KB)
   double sm_mhz = 1850.0;        // clock the model converts clocks to microseconds with
   double hbm_gbs = 6500.0;       // streaming HBM3e bandwidth
-  double fabric_bytes_per_clk = 72.0;  // L2 -> one SM fill rate
+  double fabric_bytes_per_clk = 72.0;  // L2 -> one SM fill rate when few SMs pull
+  double l2_bytes_per_clk = 48.0 * 148;  // L2 -> all SMs together (measured: 48 B/clk per SM with every SM pulling)
   double tile_ramp_clk = 2500.0;       // first TMA round trip + last MMA drain of a program
   double launch_us = 3.0;
   double flag_us = 2.0;          // one global-memory flag hop between programs
@@ -17,6 +18,6 @@ struct MachineModel {
 };
 
 int select_config(const tb_problem& p, const MachineModel& hw, tb_config* out);
-int smem_bytes_for(int block_n, int cta_pair, int stages);
+int smem_bytes_for(int block_n, int cta_pair, int stages, int n_halves = 1);
 
 }  // namespace tb

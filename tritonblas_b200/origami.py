@@ -110,7 +110,7 @@ class OrigamiMatmulSelector:
         return self._configs[key]
 
     def override(self, **fields):
-        """Force fields of the launch configuration (block_n, cta_pair, stages, group_m, grid, sk_grid) for every
+        """Force fields of the launch configuration (block_n, n_halves, cta_pair, stages, group_m, grid, sk_grid) for every
         layout; block_m follows cta_pair. For tuning sweeps and tests; the library re-validates the result."""
         for key in [(False, False), (False, True), (True, False), (True, True)]:
             cfg = self.config_for(*key)
@@ -119,11 +119,11 @@ class OrigamiMatmulSelector:
                     raise AttributeError(name)
                 setattr(cfg, name, int(value))
             cfg.block_m = 128 * (2 if cfg.cta_pair == 2 else 1)
-            if "cta_pair" in fields or "block_n" in fields:
+            if "cta_pair" in fields or "block_n" in fields or "n_halves" in fields:
                 # grids follow the tile shape unless they are forced as well
                 pair = 2 if cfg.cta_pair == 2 else 1
                 programs = max(cfg.num_sms // pair, 1)
-                tiles = -(-self._m // cfg.block_m) * -(-self._n // cfg.block_n)
+                tiles = -(-self._m // cfg.block_m) * -(-self._n // (cfg.block_n * max(cfg.n_halves, 1)))
                 if "grid" not in fields:
                     cfg.grid = min(programs, tiles)
                 if "sk_grid" not in fields:
