@@ -51,6 +51,8 @@ typedef struct tb_problem {
   int32_t mx_block_size; /* 0, or 32 for MXFP4 */
   int32_t num_sms;       /* 0: all SMs of the device; else restrict the model and the grid to this many */
   int32_t device;
+  int32_t max_halves;    /* 0: the model may pick wide tiles (tb_config.n_halves = 2); 1: narrow tiles only (what grouped
+                            launches want) */
 } tb_problem;
 
 /* Launch configuration chosen by the analytical model. Replaces the attribute surface of the selector
@@ -72,7 +74,7 @@ typedef struct tb_config {
   float predicted_sk_us;  /* model estimate for the stream-K schedule */
   int32_t n_halves;  /* 1, or 2: a work tile is two block_n-wide accumulators side by side that share every A stage
                         (tile = block_m x 2*block_n; fewer L2 -> shared-memory bytes per flop, no cross-tile epilogue
-                        overlap). 0 is read as 1. */
+                        overlap). 0 is read as 1. Ignored by stream-K launches; measured no gain for grouped launches. */
   int32_t swap_ab;   /* 1: the kernel computes C^T = B^T A^T (few rows of A: the weight matrix takes the 128-row side of
                         the tile); block_m/block_n then describe the swapped problem */
 } tb_config;

@@ -35,5 +35,5 @@ def test_status_strings():
 
 def test_struct_sizes_match_header_layout():
     from tritonblas_b200 import _lib
-    assert ctypes.sizeof(_lib.Problem) == 12 * 4
+    assert ctypes.sizeof(_lib.Problem) == 13 * 4
     assert ctypes.sizeof(_lib.Config) == 15 * 4

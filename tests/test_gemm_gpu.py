@@ -98,6 +98,16 @@ def test_ragged_shapes_all_layouts(m, n, k, ta, tb_):
     assert_close_to_oracle(c, a, b, what=f"{(m, n, k)} {ta}{tb_}")
 
 
+@pytest.mark.parametrize("ta,tb_", LAYOUTS)
+def test_large_unaligned_operands_take_the_tensor_core_path(ta, tb_):
+    """K and N not multiples of 8: the operands' pitches are not 16-byte aligned, so the host re-pitches them (one copy
+    each) instead of leaving a product this size to the CUDA-core kernel; results still match the oracle."""
+    m, n, k = 1000, 1001, 1027
+    a, b = make_operands(m, n, k, torch.bfloat16, ta, tb_, seed=21)
+    c = tb.matmul(a, b)
+    assert_close_to_oracle(c, a, b, what=f"unaligned {ta}{tb_}")
+
+
 @pytest.mark.parametrize("pair", [1, 2])
 def test_strided_output_and_out_argument(pair):
     m, n, k = 300, 200, 256

@@ -37,6 +37,22 @@ def test_grouped_matches_oracle(counts, n, k):
     assert tb.device_status() == 0
 
 
+@pytest.mark.parametrize("pair", [1, 2])
+@pytest.mark.parametrize("counts", [[256, 0, 300, 1, 77], [5, 9, 1000, 130, 0, 0, 513]])
+@pytest.mark.parametrize("n,k", [(512, 256), (768, 512), (1100, 320)])
+def test_grouped_wide_tiles(counts, n, k, pair):
+    """Wide tiles (two accumulators per work tile) in grouped mode, with group widths that end on a tile, in the first
+    half of one and in the second half of one."""
+    x, w, offs = _case(counts, n, k, seed=len(counts) + n)
+    y = torch.full((x.shape[0], n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    bf = torch.bfloat16
+    sel = tb.OrigamiMatmulSelector(x.shape[0], n, k, bf, bf, bf, torch.device("cuda", 0))
+    sel.override(cta_pair=pair, block_n=256, n_halves=2)
+    tb.grouped_matmul(x, w, offs, out=y, selector=sel)
+    _check(y, x, w, offs, f"grouped wide {counts} n={n} k={k} pair={pair}")
+    assert tb.device_status() == 0
+
+
 def test_grouped_moe_projection_shapes():
     """BASELINE config 5 at full size: 64 experts, top-8 of 16384 tokens (131072 rows), Zipf(1.1)-skewed counts, hidden
     4096, ffn 1536; gate/up (N = 3072) and down (N = 4096) projections, 48 sampled rows checked per projection."""

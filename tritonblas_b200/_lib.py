@@ -27,7 +27,7 @@ DTYPE_CODE = {
 class Problem(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in (
         "m", "n", "k", "a_dtype", "b_dtype", "c_dtype", "a_mn_major", "b_mn_major", "streamk", "mx_block_size",
-        "num_sms", "device")]
+        "num_sms", "device", "max_halves")]
 
 
 class Config(ctypes.Structure):

@@ -253,8 +253,8 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   if ((bn / pair) % 16 != 0) return TB_ERR_INVALID;
   if (b_mn && ((bn / pair) % mn_atom) != 0) return TB_ERR_INVALID;
   const int bk = 128 / es;
-  // wide tiles (two accumulators sharing A) only for the data-parallel schedule: stream-K partials are per accumulator
-  const int halves = (cfg.n_halves == 2 && !a.streamk && !grouped) ? 2 : 1;
+  // wide tiles (two accumulators sharing A) only for the data-parallel and grouped schedules: stream-K partials are per accumulator
+  const int halves = (cfg.n_halves == 2 && !a.streamk) ? 2 : 1;
   int stages = cfg.stages;
   if (stages < 2) stages = 2;
   const int extra_smem = grouped ? 8 * (a.num_groups + 2) : 0;  // per-group tile prefix + copy of the row offsets
@@ -304,6 +304,9 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
     const char* dbg = getenv("TB_DEBUG_FLAGS");
     p.debug_flags = dbg != nullptr ? atoi(dbg) : 0;
     p.debug_out = (p.debug_flags & 2) ? reinterpret_cast<long long*>(a.workspace) : nullptr;
+    // Data-parallel launches of more than one wave: odd items walk K backwards (L2 reuse between consecutive tiles).
+    // Bit 3 of the debug flags turns it off for A/B measurements.
+    p.k_serpentine = (!a.streamk && !(p.debug_flags & 8)) ? 1 : 0;
   }
 
   // instruction descriptor: fp32 accumulate; operand formats; majors; N >> 3; M >> 4

@@ -51,6 +51,7 @@ struct GemmParams {
                      // tile of every stage; both TMEM accumulator stages then belong to one tile (no cross-tile overlap)
   int num_k_blocks;  // ceil(K / k elements per stage)
   int k_per_stage;   // K elements per stage
+  int k_serpentine;  // 1: odd work items of a program load their K blocks in descending order
   int tiles_m, tiles_n, group_m;
   int stages;
   int esize;       // operand element size in bytes
@@ -440,7 +441,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // The whole warp walks the schedule (warp-uniform control flow); one elected lane issues the copies.
     {
       WorkIter wi(p, pid, nprog, grouped_tiles);
-      int s = 0;
+      int s = 0, item = 0;
       uint32_t ph = 0;
       const int a_atom = kStageRowBytes / p.esize;  // elements per 128-byte row
       // In a pair, transaction bytes of both CTAs land on the even CTA's barrier, which expects the sum.
@@ -453,7 +454,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int m0 = tg.m0 + static_cast<int>(cta_rank) * kTileM;
         const int n0 = tg.b_row0 + static_cast<int>(cta_rank) * bn_local;  // row of the B map
         const int sf_n0 = tg.n0;
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+        // Every other work item walks its K range backwards: the A and B slices the previous item touched last are the
+        // ones most likely still in L2 (the accumulation order of those items is reversed with it).
+        const bool backwards = p.k_serpentine && (item & 1);
+        ++item;
+        for (int it = w.kb0; it < w.kb1; ++it) {
+          const int kb = backwards ? w.kb0 + w.kb1 - 1 - it : it;
           const long long pw0 = prof ? clock64() : 0;
           ok = mbar_wait_warp(&empty_bar[s], ph ^ 1, wctx, TB_DEV_TIMEOUT_SMEM_EMPTY);
           if (!ok) break;

@@ -95,7 +95,7 @@ int select_config(const tb_problem& p_in, const MachineModel& hw, tb_config* out
       if (bn_local < 16) continue;
       // A wide tile (two bn-wide accumulators that share every A stage) only pays at the full accumulator width, and
       // the stream-K, block-scaled and grouped paths do not take it.
-      const int max_halves = (!mx && !p.streamk && bn == 256 && p.n >= 2 * bn) ? 2 : 1;
+      const int max_halves = (!mx && !p.streamk && p.max_halves != 1 && bn == 256 && p.n >= 2 * bn) ? 2 : 1;
       for (int halves = max_halves; halves >= 1; --halves) {
       const int tile_m = 128 * pair;
       const int tile_n = bn * halves;
@@ -135,7 +135,8 @@ int select_config(const tb_problem& p_in, const MachineModel& hw, tb_config* out
       double sk = (per_prog * stage_clk + ramp_clk + drain_clk) * clk_to_us;
       if (needs_fix) sk += 2.0 * 128.0 * bn * 4.0 / (hw.fabric_bytes_per_clk * hw.sm_mhz) + hw.flag_us;
       sk = std::max(sk, hbm_floor(static_cast<long long>(sk_grid) * pair)) + hw.launch_us;
-      const double cost = p.streamk ? sk : dp;
+      // A wide tile moves a quarter fewer bytes per flop; on long launches the power-limited clock rises by a few percent.
+      const double cost = p.streamk ? sk : (halves == 2 ? 0.96 * dp : dp);
       // Prefer, on ties, the wider tile and the pair (fewer fabric bytes per flop).
       if (cost < best_cost * 0.995) {
         best_cost = cost;

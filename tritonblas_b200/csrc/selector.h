@@ -10,7 +10,7 @@ struct MachineModel {
   double sm_mhz = 1850.0;        // clock the model converts clocks to microseconds with
   double hbm_gbs = 6500.0;       // streaming HBM3e bandwidth
   double fabric_bytes_per_clk = 72.0;  // L2 -> one SM fill rate when few SMs pull
-  double l2_bytes_per_clk = 48.0 * 148;  // L2 -> all SMs together (measured: 48 B/clk per SM with every SM pulling)
+  double l2_bytes_per_clk = 60.0 * 148;  // L2 -> all SMs together (measured: about 60 B/clk per SM with every SM pulling)
   double tile_ramp_clk = 2500.0;       // first TMA round trip + last MMA drain of a program
   double launch_us = 3.0;
   double flag_us = 2.0;          // one global-memory flag hop between programs

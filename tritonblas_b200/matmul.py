@@ -39,9 +39,10 @@ def _workspace_for(device, nbytes):
 
 
 def _make_matmul_selector(M, N, K, a_dtype, b_dtype, c_dtype, device, mx_block_size=0, streamk=False, num_stages=2,
-                          a_mn_major=False, b_mn_major=False):
+                          a_mn_major=False, b_mn_major=False, max_halves=0):
     return OrigamiMatmulSelector(M, N, K, a_dtype, b_dtype, c_dtype, device, mx_block_size=mx_block_size,
-                                 streamk=streamk, num_stages=num_stages, a_mn_major=a_mn_major, b_mn_major=b_mn_major)
+                                 streamk=streamk, num_stages=num_stages, a_mn_major=a_mn_major, b_mn_major=b_mn_major,
+                                 max_halves=max_halves)
 
 
 def _unit_stride_2d(t):
@@ -57,6 +58,36 @@ def _is_mn_major(t, contiguous_axis_is_k_index):
     if t.stride(contiguous_axis_is_k_index) == 1 or t.shape[contiguous_axis_is_k_index] == 1:
         return False
     return t.stride(other) == 1 or t.shape[other] == 1
+
+
+def _tma_loadable(t):
+    """True when a 2-D operand can be described by a TMA tensor map: 16-byte aligned base and pitch."""
+    if t.data_ptr() % 16:
+        return False
+    pitch_axis = 0 if t.stride(1) == 1 else 1
+    return t.shape[pitch_axis] == 1 or (t.stride(pitch_axis) * t.element_size()) % 16 == 0
+
+
+def _repitch(t):
+    """Copy of a 2-D operand with the same logical shape and unit-stride axis, its pitch rounded up to 16 bytes.
+
+    The tensor-core kernels load operands with TMA, which needs a 16-byte aligned base and pitch; operands that miss
+    that (K or M/N not a multiple of 8 for 16-bit types, odd views) would otherwise run on the CUDA-core kernel, which
+    is ~30x slower on large products. The padding is never read: the tensor map keeps the logical extents.
+    """
+    per16 = 16 // t.element_size()
+    if t.stride(1) == 1:
+        rows, cols = t.shape
+        buf = torch.empty((rows, -(-cols // per16) * per16), dtype=t.dtype, device=t.device)[:, :cols]
+    else:
+        rows, cols = t.shape
+        buf = torch.empty((cols, -(-rows // per16) * per16), dtype=t.dtype, device=t.device)[:, :rows].T
+    buf.copy_(t)
+    return buf
+
+
+# Below this many multiply-adds an unaligned product stays on the CUDA-core kernel (a re-pitch costs two small launches).
+_REPITCH_MIN_MACS = 1 << 27
 
 
 def _strides(t):
@@ -91,6 +122,11 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
         return c
     a = _unit_stride_2d(a)
     b = _unit_stride_2d(b)
+    if M * N * K >= _REPITCH_MIN_MACS and a.dtype != torch.float32:
+        if not _tma_loadable(a):
+            a = _repitch(a)
+        if not _tma_loadable(b):
+            b = _repitch(b)
     a_mn, b_mn = _is_mn_major(a, 1), _is_mn_major(b, 0)
     cfg = selector.config_for(a_mn, b_mn)
 
@@ -234,14 +270,14 @@ def matmul_a8w8(a, b, a_scale, b_scale, c, enable_streamk=False, work_stealing=F
     return persistent_matmul_lt(a, b, c, selector, None, a_scale=a_scale, b_scale=b_scale, quantized=True)
 
 
-def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None):
+def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, selector=None):
     """Grouped (MoE) GEMM: out[r] = x[r] @ w[g].T for every row r of group g, rows of group g being
     [group_offsets[g], group_offsets[g+1]).
 
     x: (rows, K) K-contiguous; w: (G, N, K) contiguous (each expert's weight stored N x K, the K-contiguous fast layout);
     group_offsets: int32 CUDA tensor of G + 1 ascending offsets (it stays on the device: no host synchronisation);
     out: (rows, N), allocated in x.dtype when omitted. The reference has no grouped kernel; per group this is its dense
-    contract (fp32 accumulate, one cast).
+    contract (fp32 accumulate, one cast). ``selector`` overrides the tile configuration (tuning and tests).
     """
     assert x.ndim == 2 and w.ndim == 3 and x.shape[1] == w.shape[2], "Incompatible Dimensions"
     if not (x.is_cuda and w.is_cuda and group_offsets.is_cuda):
@@ -257,7 +293,9 @@ def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None):
     w = w if w.is_contiguous() else w.contiguous()
     group_offsets = group_offsets.contiguous()
     # tiles of all groups are pooled over the SMs, so the tile model sees the total row count
-    selector = _make_matmul_selector(rows, N, K, x.dtype, w.dtype, out.dtype, x.device)
+    if selector is None:
+        # narrow tiles: with many short groups the wide tile's exposed drains outweigh its smaller operand traffic
+        selector = _make_matmul_selector(rows, N, K, x.dtype, w.dtype, out.dtype, x.device, max_halves=1)
     cfg = selector.config_for(False, False)
     args = _lib.GemmArgs()
     args.m, args.n, args.k = rows, N, K

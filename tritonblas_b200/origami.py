@@ -63,8 +63,9 @@ class OrigamiMatmulSelector:
         return estimate_triton_lds_bytes(block_m, block_n, block_k, bytes_a, bytes_b, num_stages)
 
     def __init__(self, m, n, k, a_dtype, b_dtype, out_dtype, device=None, mx_block_size=0, streamk=False,
-                 total_cus=None, active_cus=None, num_stages=2, a_mn_major=False, b_mn_major=False):
+                 total_cus=None, active_cus=None, num_stages=2, a_mn_major=False, b_mn_major=False, max_halves=0):
         self._m, self._n, self._k = int(m), int(n), int(k)
+        self._max_halves = int(max_halves)  # 1: narrow tiles only (grouped launches)
         self.streamk = bool(streamk)
         self._num_stages = num_stages
         self._mx_block_size = mx_block_size
@@ -100,7 +101,8 @@ class OrigamiMatmulSelector:
             p = _lib.Problem(m=self._m, n=self._n, k=self._k, a_dtype=self._a_code, b_dtype=self._b_code,
                              c_dtype=self._c_code, a_mn_major=int(key[0]), b_mn_major=int(key[1]),
                              streamk=int(self.streamk), mx_block_size=int(self._mx_block_size or 0),
-                             num_sms=min(self._ACTIVE_CU, self._N_CU), device=self._device_index)
+                             num_sms=min(self._ACTIVE_CU, self._N_CU), device=self._device_index,
+                             max_halves=self._max_halves)
             cfg = _lib.Config()
             rc = _lib.lib.tb_select(ctypes.byref(p), ctypes.byref(cfg))
             if rc != 0:
@@ -120,14 +122,22 @@ class OrigamiMatmulSelector:
                 setattr(cfg, name, int(value))
             cfg.block_m = 128 * (2 if cfg.cta_pair == 2 else 1)
             if "cta_pair" in fields or "block_n" in fields or "n_halves" in fields:
-                # grids follow the tile shape unless they are forced as well
+                # grids, ring depth and tile order follow the tile shape unless they are forced as well
                 pair = 2 if cfg.cta_pair == 2 else 1
+                halves = max(cfg.n_halves, 1)
                 programs = max(cfg.num_sms // pair, 1)
-                tiles = -(-self._m // cfg.block_m) * -(-self._n // (cfg.block_n * max(cfg.n_halves, 1)))
+                tiles_m = -(-self._m // cfg.block_m)
+                tiles = tiles_m * -(-self._n // (cfg.block_n * halves))
                 if "grid" not in fields:
                     cfg.grid = min(programs, tiles)
                 if "sk_grid" not in fields:
                     cfg.sk_grid = min(programs, tiles * -(-self._k // cfg.block_k))
+                if "stages" not in fields and not self._mx_block_size:
+                    stage = (128 * 128 + halves * (cfg.block_n // pair) * 128 + 1023) & ~1023
+                    cfg.stages = max(2, min(12, (self._hardware.lds_capacity - 2048 - 16384) // stage))
+                if "group_m" not in fields:
+                    g = round((programs * cfg.block_n * halves / cfg.block_m) ** 0.5)
+                    cfg.group_m = max(1, min(tiles_m, g))
         return self
 
     def hierarchical_split(self, num_xcds):
