@@ -110,6 +110,13 @@ typedef struct tb_gemm_args {
    * synchronises the ranks before the copies are read. HOST array of device pointers, or NULL. */
   void* const* c_copies;
   int32_t num_c_copies;
+  /* Dynamic tile schedule, the reference's work_stealing=True (kernels/persistent_gemm_work_stealing.py:106-116,
+   * config.py:104-121): DEVICE pointer to two uint32 words, zero when first used, or NULL for the static schedule. Every
+   * program starts with its own first tile and takes the following ones from a shared counter, so programs that start
+   * late (another kernel holds their SMs) take fewer tiles. The last program leaves both words zero again, so launches
+   * that follow each other on one stream share the buffer without a reset; after a failed launch the caller zeroes it.
+   * Ignored by stream-K launches (as the reference's a8w8 path does, matmul.py:387-388). */
+  void* tile_counter;
 } tb_gemm_args;
 
 /* Fill `cfg` for `p`. Stands in for origami.select_config + OrigamiMatmulSelector._compute_sk_grid

@@ -98,6 +98,36 @@ def test_ragged_shapes_all_layouts(m, n, k, ta, tb_):
     assert_close_to_oracle(c, a, b, what=f"{(m, n, k)} {ta}{tb_}")
 
 
+@pytest.mark.parametrize("pair,bn,nh", [(1, 128, 1), (2, 256, 1), (2, 256, 2), (1, 256, 2), (2, 64, 1)])
+@pytest.mark.parametrize("m,n,k", [(2048, 4096, 512), (1000, 3000, 264), (256, 256, 1024)])
+def test_work_stealing_schedule_matches_oracle(m, n, k, pair, bn, nh):
+    """work_stealing=True: tiles after each program's first come from a device counter. Three launches in a row share the
+    counter words, which the kernel leaves zeroed every time; results equal the static schedule's bit for bit (the same
+    tiles are computed the same way, only by different programs)."""
+    a, b = make_operands(m, n, k, torch.bfloat16, "T", "T", seed=31)
+    sel = _selector(m, n, k, torch.bfloat16, cta_pair=pair, block_n=bn, n_halves=nh)
+    cfg = tb.matmul_preamble(sel)
+    ref = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    tb.matmul_lt(a, b, ref, sel, cfg)
+    assert_close_to_oracle(ref, a, b, what=f"static {(m, n, k)} pair={pair} bn={bn} nh={nh}")
+    for rep in range(3):
+        c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        tb.matmul_lt(a, b, c, sel, cfg, work_stealing=True)
+        assert torch.equal(c, ref), f"launch {rep}"
+        assert int(cfg.tile_counter[:2].abs().sum()) == 0
+
+
+def test_work_stealing_through_matmul_and_addmm():
+    m, n, k = 1536, 2048, 1024
+    a, b = make_operands(m, n, k, torch.float16, "T", "N", seed=32)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(5)).to(torch.float16).cuda()
+    for _ in range(2):
+        c = tb.matmul(a, b, work_stealing=True)
+        assert_close_to_oracle(c, a, b, what="matmul work_stealing")
+        d = tb.addmm(bias, a, b, work_stealing=True)
+        assert_close_to_oracle(d, a, b, bias=bias, what="addmm work_stealing")
+
+
 @pytest.mark.parametrize("ta,tb_", LAYOUTS)
 def test_large_unaligned_operands_take_the_tensor_core_path(ta, tb_):
     """K and N not multiples of 8: the operands' pitches are not 16-byte aligned, so the host re-pitches them (one copy

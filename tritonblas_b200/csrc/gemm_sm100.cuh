@@ -34,6 +34,7 @@ constexpr int kEpiWarp0 = 2;                         // first epilogue warp
 constexpr int kEpiRowPitch = 128;                    // bytes per row of an epilogue warp's staging buffer; the eight 16-byte
                                                      // pieces of a row are XOR-swizzled with the row index (no padding)
 constexpr int kEpiStageBytes = kEpiWarps * 32 * kEpiRowPitch;
+constexpr int kSchedDepth = 4;         // tile indices in flight between the fetching warp and the other roles
 constexpr int kSfAtomBytes = 512;      // scale factors of 128 rows x 4 K blocks, laid out [32 rows][4 row quads][4 blocks]
 constexpr int kSfGroupsB = 2;          // 128-row scale groups staged for B: tiles are 64, 128 or 192 columns wide and start
                                        // at a multiple of 64 (the MMA takes its scale columns from an even TMEM column),
@@ -79,6 +80,10 @@ struct GemmParams {
   unsigned epoch;    // value that marks a partial as published for this launch
   // grouped (MoE) mode: group g owns rows [group_offsets[g], group_offsets[g+1]) of A and C and rows
   // [g * N, (g + 1) * N) of B; null for a plain GEMM
+  // Dynamic tile schedule (the reference's work-stealing mode): two zero-initialised words, [0] = tiles handed out beyond
+  // every program's first one, [1] = programs that have finished fetching. The last program to finish zeroes both, so
+  // launches that follow each other on a stream need no reset in between. nullptr: static round-robin schedule.
+  unsigned* tile_counter;
   const int* group_offsets;
   int num_groups;
   // failure reporting
@@ -382,9 +387,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint64_t* tmem_full = bars + 2 * stages;
   uint64_t* tmem_empty = tmem_full + 2;
   uint64_t* publish_bar = tmem_empty + 2;  // the four epilogue warps have all written their part of a partial tile
-  uint32_t* tmem_ptr_slot = reinterpret_cast<uint32_t*>(publish_bar + 1);
+  // dynamic schedule: a queue of tile indices from the fetching warp (producer of the even CTA) to every other role
+  uint64_t* sched_full = publish_bar + 1;               // [kSchedDepth], one arrival: the fetcher
+  uint64_t* sched_empty = sched_full + kSchedDepth;     // [kSchedDepth], one arrival per consuming warp of the pair
+  uint32_t* tmem_ptr_slot = reinterpret_cast<uint32_t*>(sched_empty + kSchedDepth);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_slot + 1);
-  int* tile_prefix = reinterpret_cast<int*>(tmem_ptr_slot + 2);  // grouped mode: [num_groups + 1]
+  volatile int* sched_q = reinterpret_cast<volatile int*>(tmem_ptr_slot + 2);  // [kSchedDepth]
+  int* tile_prefix = reinterpret_cast<int*>(tmem_ptr_slot + 2 + kSchedDepth);  // grouped mode: [num_groups + 1]
 
   WaitCtx wctx{abort_flag, p.status, p.timeout_ns};
   constexpr bool prof = PROF;  // measurement instantiation: per-role cycle counters written to debug_out
@@ -400,6 +409,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       mbar_init(&tmem_empty[a], kEpiWarps * CTAS);  // one arrival per epilogue warp of every CTA that shares the accumulator
     }
     mbar_init(publish_bar, kEpiWarps);
+    for (int i = 0; i < kSchedDepth; ++i) {
+      mbar_init(&sched_full[i], 1);
+      // consumers: MMA issuer + 4 epilogue warps in the even CTA, producer + 4 epilogue warps in the odd one
+      mbar_init(&sched_empty[i], 5 * CTAS);
+    }
     mbar_fence_init();
     if (p.group_offsets != nullptr) {
       // tile_prefix[0 .. G] = tiles before each group, followed by a copy of the G + 1 row offsets
@@ -436,6 +450,64 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int acc_stride = p.block_n;  // TMEM columns per accumulator stage
 
+  // ---- dynamic tile schedule -------------------------------------------------------------------------------------
+  // Every program starts with tile `pid`; after that the fetching warp (the producer of the even CTA) takes tile indices
+  // from a global counter and hands each one to the other roles of the CTA (pair) through a small shared-memory queue.
+  // Programs that start late, because other kernels hold their SMs, simply take fewer tiles.
+  const bool dyn = p.tile_counter != nullptr;
+  const int dyn_tiles = grouped_tiles >= 0 ? grouped_tiles : p.dp_tiles;
+  // A consuming role's next work item (whole tiles only). seq counts the items this role has taken.
+  auto dyn_take = [&](int seq, bool& ok) -> WorkItem {
+    const int slot = seq & (kSchedDepth - 1);
+    const uint32_t parity = (seq / kSchedDepth) & 1u;
+    ok = __all_sync(0xffffffffu, (CTAS == 2) ? mbar_wait_cluster(&sched_full[slot], parity, wctx, TB_DEV_TIMEOUT_TILE_QUEUE)
+                                             : mbar_wait(&sched_full[slot], parity, wctx, TB_DEV_TIMEOUT_TILE_QUEUE));
+    WorkItem w;
+    w.tile = ok ? sched_q[slot] : -1;
+    w.kb0 = 0;
+    w.kb1 = p.num_k_blocks;
+    w.valid = w.tile >= 0;
+    __syncwarp();
+    if (lane == 0 && ok) {  // the slot may be refilled once every consumer has read it
+      if (CTAS == 1 || cta_rank == 0) mbar_arrive(&sched_empty[slot]);
+      else mbar_arrive_remote(mapa_cluster(smem_u32(&sched_empty[slot]), 0));
+    }
+    return w;
+  };
+  // The fetching warp's next work item; it also publishes it. Called by the whole producer warp of the even CTA.
+  auto dyn_fetch = [&](int seq, bool& ok) -> WorkItem {
+    const int slot = seq & (kSchedDepth - 1);
+    const uint32_t parity = ((seq / kSchedDepth) & 1u) ^ 1u;  // passes at once the first time round
+    ok = mbar_wait_warp(&sched_empty[slot], parity, wctx, TB_DEV_TIMEOUT_TILE_QUEUE);
+    int t = -1;
+    if (lane == 0 && ok) {
+      if (seq == 0) t = pid;
+      else t = static_cast<int>(atomicAdd(p.tile_counter, 1u)) + nprog;
+      if (t >= dyn_tiles) {
+        t = -1;
+        // Every program ends with exactly one failed fetch (or an empty first tile); the last one to get here leaves the
+        // counters zeroed for the next launch.
+        if (atomicAdd(p.tile_counter + 1, 1u) == static_cast<unsigned>(nprog - 1)) {
+          p.tile_counter[0] = 0u;
+          p.tile_counter[1] = 0u;
+        }
+      }
+      sched_q[slot] = t;
+      if constexpr (CTAS == 2) {
+        st_shared_cluster_u32(mapa_cluster(smem_u32(const_cast<int*>(&sched_q[slot])), 1), static_cast<uint32_t>(t));
+        mbar_arrive_remote(mapa_cluster(smem_u32(&sched_full[slot]), 1));
+      }
+      mbar_arrive(&sched_full[slot]);
+    }
+    t = __shfl_sync(0xffffffffu, t, 0);
+    WorkItem w;
+    w.tile = t;
+    w.kb0 = 0;
+    w.kb1 = p.num_k_blocks;
+    w.valid = ok && t >= 0;
+    return w;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the schedule (warp-uniform control flow); one elected lane issues the copies.
@@ -449,7 +521,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int mn_box_bytes = p.k_per_stage * kStageRowBytes;
       bool ok = true;
       long long prof_wait = 0, prof_t0 = clock64();
-      for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
+      int seq = 0;
+      auto next_item = [&]() -> WorkItem {
+        if (!dyn) return wi.next();
+        bool got = true;
+        const WorkItem w = (cta_rank == 0) ? dyn_fetch(seq, got) : dyn_take(seq, got);
+        ++seq;
+        if (!got) ok = false;
+        return w;
+      };
+      for (WorkItem w = next_item(); w.valid && ok; w = next_item()) {
         const TileGeom tg = tile_geometry(p, w.tile, kPairTileM, tile_prefix);
         const int m0 = tg.m0 + static_cast<int>(cta_rank) * kTileM;
         const int n0 = tg.b_row0 + static_cast<int>(cta_rank) * bn_local;  // row of the B map
@@ -579,7 +660,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       // This warp runs alone on its scheduler, so every instruction and every taken branch of the per-stage loop is
       // exposed latency; the narrow and the wide tile therefore get a loop each, with nothing in it that can be
       // decided per work item.
-      for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
+      int seq = 0;
+      auto next_item = [&]() -> WorkItem {
+        if (!dyn) return wi.next();
+        bool got = true;
+        const WorkItem w = dyn_take(seq, got);
+        ++seq;
+        if (!got) ok = false;
+        return w;
+      };
+      for (WorkItem w = next_item(); w.valid && ok; w = next_item()) {
         // One accumulator per work item, alternating (the epilogue of one item overlaps the next item's main loop), or
         // both accumulators for the two halves of a wide tile.
         const int acc0 = (nh == 2) ? 0 : acc;
@@ -711,7 +801,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const uint32_t tmem_empty_remote = (CTAS == 2) ? mapa_cluster(smem_u32(&tmem_empty[0]), 0) : 0u;
     bool ok = true;
     long long prof_wait = 0, prof_t0 = clock64(), prof_drain = 0;
-    for (WorkItem w = wi.next(); w.valid && ok; w = wi.next()) {
+    int seq = 0;
+    auto next_item = [&]() -> WorkItem {
+      if (!dyn) return wi.next();
+      bool got = true;
+      const WorkItem w = dyn_take(seq, got);
+      ++seq;
+      if (!got) ok = false;
+      return w;
+    };
+    for (WorkItem w = next_item(); w.valid && ok; w = next_item()) {
       const TileGeom tg = tile_geometry(p, w.tile, kPairTileM, tile_prefix);
       const int m0 = tg.m0 + static_cast<int>(cta_rank) * kTileM;
       const int row_end = tg.row_end;

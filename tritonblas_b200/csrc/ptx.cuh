@@ -17,6 +17,7 @@ enum : int {
   TB_DEV_TIMEOUT_PEER_FLAG = 105,    // stream-K tile owner waited for a peer's partial tile
   TB_DEV_TIMEOUT_SCALE = 106,        // block-scale copy wait
   TB_DEV_TIMEOUT_STORE = 107,
+  TB_DEV_TIMEOUT_TILE_QUEUE = 108,   // a role waited for the next tile index of the dynamic schedule
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -78,6 +79,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Store to the shared memory of another CTA of the cluster (address from mapa_cluster).
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// try_wait that also acquires writes made by other CTAs of the cluster before their (cluster-scope) arrive.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Shared by all waits of one CTA: where to record a failure and how long to wait.
 struct WaitCtx {
   volatile int* abort_flag;   // in shared memory; set by the first wait that gives up
@@ -92,6 +110,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0xFF) == 0) {
+      if (*w.abort_flag) return false;
+      if (global_timer_ns() - t0 > w.timeout_ns) {
+        *w.abort_flag = 1;
+        atomicCAS(w.status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+// The same bounded wait with a cluster-scope acquire (data written by the other CTA of a pair before its arrive).
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const WaitCtx& w, int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
     if ((++spins & 0xFF) == 0) {
       if (*w.abort_flag) return false;
       if (global_timer_ns() - t0 > w.timeout_ns) {

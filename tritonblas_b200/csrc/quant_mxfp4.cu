@@ -10,10 +10,9 @@
 //   fp32 butterflies with strides 1, 2, 4, 8, 16, each (a, b) -> (a + b, a - b), no fused multiply-add, then one fp32
 //   multiply by 0.17677669529663687 (1/sqrt(32)).
 //
-// Four lanes own one 32-element block, eight consecutive elements each: a warp reads 512 contiguous bytes per load
-// instruction (16-bit inputs) and writes 128 contiguous code bytes. The butterflies with strides 1, 2, 4 stay inside a
-// lane; strides 8 and 16 exchange with lanes ^1 and ^2, as does the block maximum. Same additions in the same order as a
-// single-thread butterfly, so the bits are the same. Pure HBM streaming: 2.53 bytes per input element for 16-bit inputs.
+// One thread owns one 32-element block: 64 bytes in (16-bit inputs), 16 code bytes + 1 scale byte out. Consecutive lanes
+// own consecutive blocks of a row, so a warp reads 2 KB and writes 512 + 32 contiguous bytes. Pure HBM streaming:
+// 2.53 bytes per input element for 16-bit inputs.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -21,6 +20,68 @@
 
 namespace tb {
 namespace {
+
+template <typename T>
+__device__ __forceinline__ void load_block(const T* src, float (&v)[32]);
+
+template <>
+__device__ __forceinline__ void load_block<__nv_bfloat16>(const __nv_bfloat16* src, float (&v)[32]) {
+  const uint4* p = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 w = __ldcs(p + i);  // streamed once
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[i * 8 + j * 2] = __uint_as_float(u[j] << 16);
+      v[i * 8 + j * 2 + 1] = __uint_as_float(u[j] & 0xFFFF0000u);
+    }
+  }
+}
+template <>
+__device__ __forceinline__ void load_block<__half>(const __half* src, float (&v)[32]) {
+  const uint4* p = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 w = __ldcs(p + i);
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2 h = *reinterpret_cast<const __half2*>(&u[j]);
+      const float2 f = __half22float2(h);
+      v[i * 8 + j * 2] = f.x;
+      v[i * 8 + j * 2 + 1] = f.y;
+    }
+  }
+}
+template <>
+__device__ __forceinline__ void load_block<float>(const float* src, float (&v)[32]) {
+  const float4* p = reinterpret_cast<const float4*>(src);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 w = __ldcs(p + i);
+    v[i * 4] = w.x;
+    v[i * 4 + 1] = w.y;
+    v[i * 4 + 2] = w.z;
+    v[i * 4 + 3] = w.w;
+  }
+}
+
+__device__ __forceinline__ void hadamard32(float (&v)[32]) {
+#pragma unroll
+  for (int stride = 1; stride < 32; stride <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if ((i & stride) == 0) {
+        const float a = v[i], b = v[i + stride];
+        v[i] = __fadd_rn(a, b);
+        v[i + stride] = __fsub_rn(a, b);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(v[i], 0.17677669529663687f);
+}
 
 // Eight fp32 values (already divided by the block scale) -> eight e2m1 codes, v[0] in the lowest nibble.
 // The reference's integer recipe is round-to-nearest with ties away from zero and saturation at 6.0. The hardware
@@ -71,90 +132,23 @@ __global__ void __launch_bounds__(256) scales_to_atoms_kernel(const unsigned cha
   }
 }
 
-template <typename T>
-__device__ __forceinline__ void load8(const T* src, float (&v)[8]);
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* src, float (&v)[8]) {
-  const uint4 w = __ldcs(reinterpret_cast<const uint4*>(src));  // streamed once
-  const uint32_t u[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    v[j * 2] = __uint_as_float(u[j] << 16);
-    v[j * 2 + 1] = __uint_as_float(u[j] & 0xFFFF0000u);
-  }
-}
-template <>
-__device__ __forceinline__ void load8<__half>(const __half* src, float (&v)[8]) {
-  const uint4 w = __ldcs(reinterpret_cast<const uint4*>(src));
-  const uint32_t u[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[j]));
-    v[j * 2] = f.x;
-    v[j * 2 + 1] = f.y;
-  }
-}
-template <>
-__device__ __forceinline__ void load8<float>(const float* src, float (&v)[8]) {
-  const float4 a = __ldcs(reinterpret_cast<const float4*>(src)), b = __ldcs(reinterpret_cast<const float4*>(src) + 1);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-
-// The kernel: lane = 4 * block + part; `part` holds elements 8 * part .. 8 * part + 7 of its block.
-template <typename T, bool HADAMARD, typename Idx>
+template <typename T, bool HADAMARD>
 __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const T* __restrict__ x, long long x_row_stride,
                                                             unsigned char* __restrict__ codes, long long codes_row_stride,
                                                             unsigned char* __restrict__ scales, long long scales_row_stride,
                                                             unsigned char* __restrict__ atoms, int k_atoms, int rows,
                                                             int blocks_per_row) {
-  // Idx is 32-bit whenever the lane count fits (the per-lane row/column split is a division, and a 64-bit one costs as
-  // much as the rest of the loop body).
-  const Idx total = static_cast<Idx>(rows) * static_cast<Idx>(blocks_per_row) * 4;  // four lanes per block
-  const int part = threadIdx.x & 3;
-  // The trip count is the same for every lane of a warp, so the shuffles below always run with all 32 lanes; lanes past
-  // the end redo the last block and store nothing.
-  const Idx first = static_cast<Idx>(blockIdx.x) * blockDim.x + (threadIdx.x & ~31u);
-  const Idx step = static_cast<Idx>(gridDim.x) * blockDim.x;
-#pragma unroll 2
-  for (Idx base = first; base < total; base += step) {
-    const Idx t = base + (threadIdx.x & 31);
-    const bool live = t < total;
-    const Idx idx = (live ? t : total - 4 + part) >> 2;
-    const int row = static_cast<int>(idx / static_cast<Idx>(blocks_per_row));
-    const int blk = static_cast<int>(idx - static_cast<Idx>(row) * static_cast<Idx>(blocks_per_row));
-    constexpr unsigned quad = 0xFFFFFFFFu;
-    float v[8];
-    load8<T>(x + row * x_row_stride + blk * 32 + part * 8, v);
-    if (HADAMARD) {
-#pragma unroll
-      for (int stride = 1; stride < 8; stride <<= 1) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if ((i & stride) == 0) {
-            const float a = v[i], b = v[i + stride];
-            v[i] = __fadd_rn(a, b);
-            v[i + stride] = __fsub_rn(a, b);
-          }
-        }
-      }
-#pragma unroll
-      for (int bit = 1; bit <= 2; bit <<= 1) {  // element strides 8 and 16
-        const bool upper = (part & bit) != 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float o = __shfl_xor_sync(quad, v[i], bit);
-          v[i] = upper ? __fsub_rn(o, v[i]) : __fadd_rn(v[i], o);
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], 0.17677669529663687f);
-    }
+  const long long total = static_cast<long long>(rows) * blocks_per_row;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(idx / blocks_per_row);
+    const int blk = static_cast<int>(idx - static_cast<long long>(row) * blocks_per_row);
+    float v[32];
+    load_block<T>(x + row * x_row_stride + blk * 32, v);
+    if (HADAMARD) hadamard32(v);
     float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = fmaxf(amax, __shfl_xor_sync(quad, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(quad, amax, 2));
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
     // block exponent
     const uint32_t p2 = (__float_as_uint(amax) + 0x200000u) & 0xFF800000u;
     const int exp_field = static_cast<int>(p2 >> 23);
@@ -162,17 +156,19 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const T* __restrict__ 
     e = e < -127 ? -127 : (e > 127 ? 127 : e);
     // 2^-e as bits (2^-127 is the denormal 0x00400000)
     const float inv_scale = __uint_as_float(e == 127 ? 0x00400000u : static_cast<uint32_t>(127 - e) << 23);
-    float q[8];
+    uint32_t packed[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = __fmul_rn(v[i], inv_scale);
-    const uint32_t code = encode_e2m1x8(q);
-    if (live) *reinterpret_cast<uint32_t*>(codes + row * codes_row_stride + blk * 16 + part * 4) = code;
-    if (live && part == 0) {
-      const unsigned char sbyte = static_cast<unsigned char>((e + 127) & 0xFF);
-      if (scales != nullptr) scales[row * scales_row_stride + blk] = sbyte;
-      if (atoms != nullptr)  // the arrangement the block-scaled MMA's scale copy consumes (see atom_offset)
-        atoms[atom_offset(row, blk, k_atoms)] = sbyte;
+    for (int w = 0; w < 4; ++w) {
+      float q[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = __fmul_rn(v[w * 8 + i], inv_scale);
+      packed[w] = encode_e2m1x8(q);
     }
+    *reinterpret_cast<uint4*>(codes + row * codes_row_stride + blk * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    const unsigned char sbyte = static_cast<unsigned char>((e + 127) & 0xFF);
+    if (scales != nullptr) scales[row * scales_row_stride + blk] = sbyte;
+    if (atoms != nullptr)  // the arrangement the block-scaled MMA's scale copy consumes (see atom_offset)
+      atoms[atom_offset(row, blk, k_atoms)] = sbyte;
   }
 }
 
@@ -181,24 +177,19 @@ int launch(const void* x, long long xs, void* codes, long long cs, void* scales,
            int hadamard, int num_sms, cudaStream_t stream) {
   const int k_atoms = (k + 127) / 128;
   const int bpr = k / 32;
-  const long long total = static_cast<long long>(rows) * bpr * 4;  // four lanes per 32-element block
+  const long long total = static_cast<long long>(rows) * bpr;
   long long blocks = (total + 255) / 256;
   const long long cap = static_cast<long long>(num_sms) * 8 * 4;  // a few waves of 8 resident CTAs per SM
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  const bool small = total + static_cast<long long>(blocks) * 256 < 0x7FFFFFFFll;  // the loop index may overshoot by one step
-#define TB_QUANT_LAUNCH(H, IDX)                                                                                        \
-  quant_mxfp4_kernel<T, H, IDX><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                                    \
-      static_cast<const T*>(x), xs, static_cast<unsigned char*>(codes), cs, static_cast<unsigned char*>(scales), ss,   \
-      static_cast<unsigned char*>(atoms), k_atoms, rows, bpr)
-  if (hadamard) {
-    if (small) TB_QUANT_LAUNCH(true, unsigned);
-    else TB_QUANT_LAUNCH(true, long long);
-  } else {
-    if (small) TB_QUANT_LAUNCH(false, unsigned);
-    else TB_QUANT_LAUNCH(false, long long);
-  }
-#undef TB_QUANT_LAUNCH
+  if (hadamard)
+    quant_mxfp4_kernel<T, true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        static_cast<const T*>(x), xs, static_cast<unsigned char*>(codes), cs, static_cast<unsigned char*>(scales), ss,
+        static_cast<unsigned char*>(atoms), k_atoms, rows, bpr);
+  else
+    quant_mxfp4_kernel<T, false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        static_cast<const T*>(x), xs, static_cast<unsigned char*>(codes), cs, static_cast<unsigned char*>(scales), ss,
+        static_cast<unsigned char*>(atoms), k_atoms, rows, bpr);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "quant_mxfp4_kernel launch");
   g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -40,7 +40,7 @@ static int next_pow2(int v) {
 
 int smem_bytes_for(int block_n, int cta_pair, int stages, int n_halves) {
   const int stage = 128 * 128 + n_halves * (block_n / cta_pair) * 128;
-  return stages * stage + 16384 + (2 * stages + 8) * 8 + 64 + 1024;  // ring + epilogue staging + barriers + slots + slack
+  return stages * stage + 16384 + (2 * stages + 16) * 8 + 64 + 1024;  // ring + epilogue staging + barriers + tile queue + slots + slack
 }
 
 struct Candidate {

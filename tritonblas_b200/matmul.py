@@ -29,6 +29,19 @@ class _GlobalWorkspace:
         return self.epoch
 
 
+_global_tile_counters = {}
+
+
+def _tile_counter_for(device):
+    """Two zeroed words per device for dynamically scheduled launches that bring no MatmulConfig."""
+    key = (device.type, device.index)
+    buf = _global_tile_counters.get(key)
+    if buf is None:
+        buf = torch.zeros(64, device=device, dtype=torch.int32)
+        _global_tile_counters[key] = buf
+    return buf
+
+
 def _workspace_for(device, nbytes):
     key = (device.type, device.index)
     ws = _global_workspaces.get(key)
@@ -105,7 +118,7 @@ def _ptr(t):
 
 
 def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, streamk=False, sk_grid=None,
-          c_copies=None):
+          c_copies=None, work_stealing=False):
     assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
     if not (a.is_cuda and b.is_cuda and c.is_cuda):
         raise RuntimeError("tritonblas_b200 runs on CUDA tensors only (no CPU path)")
@@ -152,6 +165,10 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
     args.allow_tf32 = int(torch.backends.cuda.matmul.allow_tf32)
     args.streamk = int(bool(streamk))
     args.sk_grid = int(sk_grid) if sk_grid else 0
+    if work_stealing and not streamk:
+        # dynamic tile schedule: the kernel leaves the two counter words zeroed, so launches on one stream share them
+        counter = config.tile_counter if config is not None else _tile_counter_for(a.device)
+        args.tile_counter = _ptr(counter)
     if streamk:
         need = workspace_bytes(cfg, args.sk_grid)
         holder = config if (config is not None and config.workspace.numel() >= need) else _workspace_for(a.device, need)
@@ -165,10 +182,11 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
 
 def persistent_matmul_lt(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, quantized=False,
                          work_stealing=False, c_copies=None):
-    """Data-parallel persistent GEMM (reference: matmul.py:69-200). ``work_stealing`` is accepted; tiles are
-    scheduled statically. ``c_copies``: device addresses of further buffers laid out like ``c`` (peer GPUs) that the
+    """Data-parallel persistent GEMM (reference: matmul.py:69-200). ``work_stealing`` selects the dynamic tile schedule
+    (tiles taken from a device counter, matmul.py:112-159) instead of the static round-robin. ``c_copies``: device addresses of further buffers laid out like ``c`` (peer GPUs) that the
     epilogue also writes."""
-    return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=False, c_copies=c_copies)
+    return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=False, c_copies=c_copies,
+                 work_stealing=work_stealing)
 
 
 def streamk_matmul_lt(a, b, c, selector, config=None, bias=None, sk_grid=None, a_scale=None, b_scale=None,
