@@ -122,3 +122,20 @@ def test_peer_dispatch_plan_places_every_row_once_and_expert_major():
             d, row = int(p.pair_rank[f]), int(p.pair_row[f])
             assert token_tag[d][row] == r * 1000 + f // topk
             assert expert_tag[d][row] == int(ids[r].flatten()[f])
+
+
+def test_bench_matmul_csv_schema(tmp_path):
+    """The YAML/CSV benchmark tool writes the reference's column set (benchmarks/tritonblas_matmul.py:278-291)."""
+    from tritonblas_b200 import bench_matmul as bm
+    row = {name: 0 for name in bm.CSV_FIELDS}
+    row["active_cus"] = 148
+    out = tmp_path / "r.csv"
+    bm.write_csv(str(out), [row])
+    header = out.read_text().splitlines()[0].split(",")
+    assert header == ["active_cus", "m", "n", "k", "mnk", "macro_tile", "bytes", "flops", "tritonblas_gflops", "a_type",
+                      "b_type", "c_type", "d_type", "compute_type", "in_dtype", "out_dtype", "init_type", "transA",
+                      "transB", "us", "alpha", "beta", "mode"]
+    import yaml
+    cases = yaml.safe_load(open(bm.__file__.replace("bench_matmul.py", "shapes/baseline.yaml")))
+    assert all({"m", "n", "k", "in_dtype", "out_dtype", "transA", "transB"} <= set(c) for c in cases)
+    assert all(bm.str_to_dtype(c["in_dtype"]) is not None for c in cases)

@@ -113,6 +113,26 @@ int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uin
   return TB_OK;
 }
 
+// MN-major operand [k][mn] (mn contiguous, `k_stride_bytes` between K rows) as a 3-D tensor [mn / atom][k][atom], atom =
+// the elements of one 128-byte swizzle row: one box of `groups` atoms x box_k rows lands in shared memory atom after atom,
+// the layout the MN-major matrix descriptors expect, with a single TMA instruction per operand and stage instead of one
+// per atom. Needs mn to be a multiple of the atom; the driver may also refuse the stride order (the K stride, which is
+// the larger one, comes first), in which case the caller keeps the 2-D map and one copy per atom.
+int encode_mn3d(CUtensorMap* map, int dtype, const void* base, uint64_t mn, uint64_t k, uint64_t k_stride_bytes,
+                uint32_t atom, uint32_t box_k, uint32_t groups, int swizzle) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (k_stride_bytes & 15) != 0) return TB_ERR_ALIGNMENT;
+  if (mn % atom != 0 || groups == 0) return TB_ERR_UNSUPPORTED;
+  cuuint64_t dims[3] = {atom, k, mn / atom};
+  cuuint64_t strides[2] = {k_stride_bytes, 128};
+  cuuint32_t box[3] = {atom, box_k, groups};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(map, tmap_dtype(dtype), 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TB_OK : TB_ERR_UNSUPPORTED;
+}
+
 // Scale-factor atoms as a 3-D tensor of 32-bit words: [row groups][K atoms][128 words]; box = one group x two atoms.
 int encode_sf_atoms(CUtensorMap* map, const void* base, uint64_t k_atoms, uint64_t groups) {
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return TB_ERR_ALIGNMENT;
@@ -370,12 +390,27 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   const void* B = a.b;
   // swizzle: 1 = 128-byte rows of 16-byte chunks; 2 = 128-byte rows of 32-byte chunks (MN-major 32-bit operands)
   const int mn_swz = es == 4 ? 2 : 1;
-  if (!a_mn) rc = encode_2d(&ta, a.a_dtype, A, a.k, a.m, static_cast<uint64_t>(a.a_stride_m) * es, bk, 128, 1);
-  else rc = encode_2d(&ta, a.a_dtype, A, a.m, a.k, static_cast<uint64_t>(a.a_stride_k) * es, mn_atom, bk, mn_swz);
+  const bool no_mn3d = getenv("TB_DISABLE_MN3D") != nullptr;  // A/B measurements
+  if (!a_mn) {
+    rc = encode_2d(&ta, a.a_dtype, A, a.k, a.m, static_cast<uint64_t>(a.a_stride_m) * es, bk, 128, 1);
+  } else {
+    // one 3-D copy per stage when the driver takes the map, else one 2-D copy per 128-byte atom
+    if (!no_mn3d && encode_mn3d(&ta, a.a_dtype, A, a.m, a.k, static_cast<uint64_t>(a.a_stride_k) * es, mn_atom, bk,
+                                128 / mn_atom, mn_swz) == TB_OK)
+      p.a_mn3d = 1;
+    else
+      rc = encode_2d(&ta, a.a_dtype, A, a.m, a.k, static_cast<uint64_t>(a.a_stride_k) * es, mn_atom, bk, mn_swz);
+  }
   if (rc == TB_OK) {
     const uint64_t b_rows = grouped ? static_cast<uint64_t>(a.n) * a.num_groups : static_cast<uint64_t>(a.n);
-    if (!b_mn) rc = encode_2d(&tbm, a.b_dtype, B, a.k, b_rows, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, 1);
-    else rc = encode_2d(&tbm, a.b_dtype, B, a.n, a.k, static_cast<uint64_t>(a.b_stride_k) * es, mn_atom, bk, mn_swz);
+    if (!b_mn) {
+      rc = encode_2d(&tbm, a.b_dtype, B, a.k, b_rows, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, 1);
+    } else if (!no_mn3d && encode_mn3d(&tbm, a.b_dtype, B, a.n, a.k, static_cast<uint64_t>(a.b_stride_k) * es, mn_atom,
+                                       bk, (bn / pair) / mn_atom, mn_swz) == TB_OK) {
+      p.b_mn3d = 1;
+    } else {
+      rc = encode_2d(&tbm, a.b_dtype, B, a.n, a.k, static_cast<uint64_t>(a.b_stride_k) * es, mn_atom, bk, mn_swz);
+    }
   }
   if (rc == TB_ERR_ALIGNMENT && !grouped && !swapped) return gemm_generic_loader(a, cfg, stream, dev->status);
   if (rc != TB_OK) return rc;

@@ -52,6 +52,7 @@ struct GemmParams {
                      // tile of every stage; both TMEM accumulator stages then belong to one tile (no cross-tile overlap)
   int num_k_blocks;  // ceil(K / k elements per stage)
   int k_per_stage;   // K elements per stage
+  int a_mn3d, b_mn3d;  // MN-major operand described by a 3-D tensor map [mn / atom][k][atom]: one copy per stage
   int k_serpentine;  // 1: odd work items of a program load their K blocks in descending order
   int tiles_m, tiles_n, group_m;
   int stages;
@@ -553,6 +554,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               mbar_arrive_expect_tx(&full_bar[s], expect);
               if (!p.a_mn) {
                 tma_load_2d(sa, &tmap_a, &full_bar[s], k0, m0);
+              } else if (p.a_mn3d) {
+                tma_load_3d(sa, &tmap_a, &full_bar[s], 0, k0, m0 / a_atom);
               } else {
                 for (int j = 0; j < kTileM / a_atom; ++j)
                   tma_load_2d(sa + j * mn_box_bytes, &tmap_a, &full_bar[s], m0 + j * a_atom, k0);
@@ -564,6 +567,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 const int nh0 = n0 + h * p.block_n;
                 if (!p.b_mn) {
                   tma_load_2d(sbh, &tmap_b, &full_bar[s], k0, nh0);
+                } else if (p.b_mn3d) {
+                  tma_load_3d(sbh, &tmap_b, &full_bar[s], 0, k0, nh0 / a_atom);
                 } else {
                   for (int j = 0; j < bn_local / a_atom; ++j)
                     tma_load_2d(sbh + j * mn_box_bytes, &tmap_b, &full_bar[s], nh0 + j * a_atom, k0);
@@ -582,6 +587,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], expect);
               if (!p.a_mn) {
                 tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
+              } else if (p.a_mn3d) {
+                tma_load_3d_pair(sa, &tmap_a, bar, 0, k0, m0 / a_atom);
               } else {
                 for (int j = 0; j < kTileM / a_atom; ++j)
                   tma_load_2d_pair(sa + j * mn_box_bytes, &tmap_a, bar, m0 + j * a_atom, k0);
@@ -593,6 +600,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 const int nh0 = n0 + h * p.block_n;
                 if (!p.b_mn) {
                   tma_load_2d_pair(sbh, &tmap_b, bar, k0, nh0);
+                } else if (p.b_mn3d) {
+                  tma_load_3d_pair(sbh, &tmap_b, bar, 0, k0, nh0 / a_atom);
                 } else {
                   for (int j = 0; j < bn_local / a_atom; ++j)
                     tma_load_2d_pair(sbh + j * mn_box_bytes, &tmap_b, bar, nh0 + j * a_atom, k0);

@@ -112,7 +112,10 @@ int select_config(const tb_problem& p_in, const MachineModel& hw, tb_config* out
       const double fabric = std::min(hw.fabric_bytes_per_clk, hw.l2_bytes_per_clk / static_cast<double>(active_ctas));
       const double mma_clk = mma_clk_per_stage_per_bn * bn * halves;
       const double fill_clk = (128.0 + halves * bn_local) * 128.0 / fabric;
-      const double stage_clk = std::max(mma_clk, fill_clk);
+      // Measured: with narrow tiles every MN-major operand costs about 10-15 % (8192^2 x 4096 bf16: 1260 / 1155 / 1021
+      // TFLOP/s for 0 / 1 / 2 such operands), with wide tiles nothing (1272 / 1276 / 1257).
+      const double mn_penalty = halves == 1 ? 1.0 + 0.15 * ((p.a_mn_major ? 1 : 0) + (p.b_mn_major ? 1 : 0)) : 1.0;
+      const double stage_clk = std::max(mma_clk, fill_clk) * mn_penalty;
       const double ramp_clk = hw.tile_ramp_clk;  // first-stage latency + epilogue drain not hidden by the next tile
       const double clk_to_us = 1.0 / (hw.sm_mhz);
       // Draining one 128 x bn accumulator. Two accumulator stages hide it behind the next tile's main loop unless
