@@ -49,7 +49,7 @@ WORKLOADS = {
 TORCH_DTYPES = {"bf16": torch.bfloat16, "fp16": torch.float16}
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the workload's dominant kernel, from the ncu captures
 # summarised under profiles/ (same shapes; a capture is not repeated inside the bench)
-NCU_TRAFFIC_BYTES = {"bf16_8192": 1.153e9 + 0.128e9, "mxfp4_8192": 0.1229e9 + 0.1042e9, "mxfp4_quant": 0.1342e9 + 0.0093e9}
+NCU_TRAFFIC_BYTES = {"bf16_8192": 0.794e9 + 0.124e9, "mxfp4_8192": 0.1565e9 + 0.1132e9, "mxfp4_quant": 0.1343e9 + 0.0078e9}
 MOE = dict(experts=64, topk=8, tokens=16384, hidden=4096, ffn=1536)
 
 
