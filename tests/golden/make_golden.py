@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by running the REFERENCE's own code on the CPU.
 
-Run once, in a container that has the reference tree (default /root/reference, override with TRITONBLAS_REF):
-    python tests/golden/make_golden.py
+Run once, where the reference tree is available (its location is given in TRITONBLAS_REF):
+    TRITONBLAS_REF=<reference checkout> python tests/golden/make_golden.py
 Outputs (committed, small):
     decoders.npz        reference mxfp4_to_f32 on all 256 packed bytes, e8m0_to_f32 on all 256 scale bytes
     mxfp4_quant.npz     inputs and the codes/scales the reference Triton quantiser kernel produced for them
@@ -21,7 +21,9 @@ os.environ["TRITON_INTERPRET"] = "1"
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
-REF = os.environ.get("TRITONBLAS_REF", "/root/reference")
+REF = os.environ.get("TRITONBLAS_REF")
+if not REF or not os.path.isdir(REF):
+    sys.exit("set TRITONBLAS_REF to a checkout of the reference tree")
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 
