@@ -82,6 +82,8 @@ typedef struct tb_config {
 /* One dense GEMM: C = cast( (A . B) [* a_scale[:,None]] [* b_scale[None,:]] [+ bias[None,:]] ).
  * Replaces persistent_matmul_lt / streamk_matmul_lt and the Triton kernels they launch
  * (include/tritonblas/matmul.py:69-366, kernels/persistent_gemm.py:26-126, kernels/streamk_gemm.py:7-384). */
+enum { TB_EPILOGUE_NONE = 0, TB_EPILOGUE_SWIGLU = 1 };
+
 typedef struct tb_gemm_args {
   int32_t m, n, k;
   int32_t a_dtype, b_dtype, c_dtype;
@@ -117,6 +119,14 @@ typedef struct tb_gemm_args {
    * that follow each other on one stream share the buffer without a reset; after a failed launch the caller zeroes it.
    * Ignored by stream-K launches (as the reference's a8w8 path does, matmul.py:387-388). */
   void* tile_counter;
+  /* Fused activation of the epilogue. TB_EPILOGUE_NONE, or TB_EPILOGUE_SWIGLU: B has 2*n rows (per group), the first n the
+   * gate projection and the next n the up projection, and C (n columns) receives silu(a.gate_j) * (a.up_j) computed in fp32
+   * on the accumulators and cast once. For the MoE gate/up projection (no reference counterpart: the reference has no
+   * grouped kernel; its dense contract of fp32 accumulation and one cast is kept). Needs K-contiguous operands, a 16-bit
+   * row-major C with 16-byte aligned rows, n a multiple of 128, more than 128 rows, no scales or bias, the data-parallel
+   * schedule; the library then runs CTA pairs whose accumulators hold 128 gate and 128 up columns side by side, so the
+   * activation hides behind the next tile's main loop. TB_ERR_UNSUPPORTED otherwise. */
+  int32_t epilogue_op;
 } tb_gemm_args;
 
 /* Fill `cfg` for `p`. Stands in for origami.select_config + OrigamiMatmulSelector._compute_sk_grid

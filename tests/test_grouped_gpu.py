@@ -53,6 +53,24 @@ def test_grouped_wide_tiles(counts, n, k, pair):
     assert tb.device_status() == 0
 
 
+@pytest.mark.parametrize("counts", [[256, 0, 300, 1, 77], [5, 9, 1000, 130, 0, 0, 513], [128] * 8])
+@pytest.mark.parametrize("ffn,k", [(256, 256), (384, 512), (1536, 320), (128, 128)])
+def test_grouped_gate_up_with_fused_swiglu(counts, ffn, k):
+    """swiglu=True: w = [gate | up]; the epilogue applies silu(gate) * up to the fp32 accumulators. Reference: the same
+    product in fp32 on the CPU (oracle grouped GEMM on both halves), activation in fp32, one cast."""
+    x, w, offs = _case(counts, 2 * ffn, k, seed=ffn + k)
+    y = torch.full((x.shape[0], ffn), float("nan"), dtype=torch.bfloat16, device="cuda")
+    tb.grouped_matmul(x, w, offs, out=y, swiglu=True)
+    h = gemm_oracle.grouped_gemm_ref(x, w.transpose(1, 2), offs.cpu(), torch.float32)
+    ref = torch.nn.functional.silu(h[:, :ffn]) * h[:, ffn:]
+    got = y.float().cpu()
+    rms = ref.pow(2).mean().sqrt().item()
+    err = (got - ref).abs()
+    assert torch.isfinite(got).all()
+    assert not (err > 1e-2 * ref.abs() + 1e-2 * max(rms, 1e-30)).any(), f"max err {err.max().item():.4g} rms {rms:.4g}"
+    assert tb.device_status() == 0
+
+
 def test_grouped_moe_projection_shapes():
     """BASELINE config 5 at full size: 64 experts, top-8 of 16384 tokens (131072 rows), Zipf(1.1)-skewed counts, hidden
     4096, ffn 1536; gate/up (N = 3072) and down (N = 4096) projections, 48 sampled rows checked per projection."""

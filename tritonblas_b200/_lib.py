@@ -53,7 +53,7 @@ class GemmArgs(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64), ("epoch", ctypes.c_uint32),
         ("group_offsets", ctypes.c_void_p), ("num_groups", ctypes.c_int32),
         ("c_copies", ctypes.POINTER(ctypes.c_void_p)), ("num_c_copies", ctypes.c_int32),
-        ("tile_counter", ctypes.c_void_p),
+        ("tile_counter", ctypes.c_void_p), ("epilogue_op", ctypes.c_int32),
     ]
 
 

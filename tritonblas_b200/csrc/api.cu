@@ -250,7 +250,7 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
     rc = select_config(pr, machine_for(dev), &cfg);
     if (rc != TB_OK) return rc;
   }
-  if (cfg.swap_ab && !swapped && !grouped) {
+  if (cfg.swap_ab && !swapped && !grouped && a.epilogue_op == TB_EPILOGUE_NONE) {
     // C^T = B^T A^T: exchange the operands' roles and transpose the output view; the per-row and per-column epilogue
     // vectors trade places and the bias becomes a per-row vector.
     tb_gemm_args t = a;
@@ -265,6 +265,24 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
     // Operands TMA cannot address go to the CUDA-core kernel in their original orientation (its bias is per column).
     if (rc == TB_ERR_ALIGNMENT) return gemm_generic_loader(a, cfg, stream, dev->status);
     return rc;
+  }
+  const bool glu = a.epilogue_op == TB_EPILOGUE_SWIGLU;
+  if (a.epilogue_op != TB_EPILOGUE_NONE && !glu) return TB_ERR_INVALID;
+  if (glu) {
+    // gate and up columns side by side in every accumulator: whole tiles and the straight-line 16-bit drain only
+    if (a.streamk || swapped || a_mn || b_mn || a.a_scale != nullptr || a.b_scale != nullptr || a.bias != nullptr ||
+        a.num_c_copies != 0 || (a.c_dtype != TB_DTYPE_BF16 && a.c_dtype != TB_DTYPE_F16) ||
+        a.a_dtype == TB_DTYPE_F32 || a.a_dtype == TB_DTYPE_I8)
+      return TB_ERR_UNSUPPORTED;
+    if (a.c_stride_n != 1 || ((a.c_stride_m * 2) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.c) & 15) != 0)
+      return TB_ERR_ALIGNMENT;
+    if (cfg.swap_ab || (a.n % 128) != 0 || a.m <= 128) return TB_ERR_UNSUPPORTED;
+    // CTA pair, 256-column accumulators (128 gate + 128 up columns), narrow tiles: the drain and its exponentials hide
+    // behind the next tile's main loop
+    cfg.cta_pair = 2;
+    cfg.block_m = 256;
+    cfg.block_n = 256;
+    cfg.n_halves = 1;
   }
   const int pair = cfg.cta_pair == 2 ? 2 : 1;
   const int bn = cfg.block_n;
@@ -289,7 +307,8 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   p.k_per_stage = bk;
   p.num_k_blocks = (a.k + bk - 1) / bk;
   p.tiles_m = (a.m + 128 * pair - 1) / (128 * pair);
-  p.tiles_n = (a.n + bn * halves - 1) / (bn * halves);
+  p.glu = glu ? 1 : 0;
+  p.tiles_n = glu ? a.n / (bn / 2) : (a.n + bn * halves - 1) / (bn * halves);
   p.group_m = cfg.group_m > 0 ? cfg.group_m : 8;
   p.stages = stages;
   p.esize = es;
@@ -402,7 +421,7 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
       rc = encode_2d(&ta, a.a_dtype, A, a.m, a.k, static_cast<uint64_t>(a.a_stride_k) * es, mn_atom, bk, mn_swz);
   }
   if (rc == TB_OK) {
-    const uint64_t b_rows = grouped ? static_cast<uint64_t>(a.n) * a.num_groups : static_cast<uint64_t>(a.n);
+    const uint64_t b_rows = (grouped ? static_cast<uint64_t>(a.n) * a.num_groups : static_cast<uint64_t>(a.n)) * (glu ? 2 : 1);
     if (!b_mn) {
       rc = encode_2d(&tbm, a.b_dtype, B, a.k, b_rows, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, 1);
     } else if (!no_mn3d && encode_mn3d(&tbm, a.b_dtype, B, a.n, a.k, static_cast<uint64_t>(a.b_stride_k) * es, mn_atom,

@@ -52,6 +52,9 @@ struct GemmParams {
                      // tile of every stage; both TMEM accumulator stages then belong to one tile (no cross-tile overlap)
   int num_k_blocks;  // ceil(K / k elements per stage)
   int k_per_stage;   // K elements per stage
+  int glu;  // 1 (CTA pairs only): B's rows are [gate | up] halves of N rows each (per group). The even CTA stages
+            // block_n / 2 gate rows and the odd CTA the matching up rows, so every accumulator holds gate values in its
+            // first block_n / 2 columns and up values in the rest; C (N columns) receives silu(gate) * up
   int a_mn3d, b_mn3d;  // MN-major operand described by a 3-D tensor map [mn / atom][k][atom]: one copy per stage
   int k_serpentine;  // 1: odd work items of a program load their K blocks in descending order
   int tiles_m, tiles_n, group_m;
@@ -171,7 +174,7 @@ __device__ __forceinline__ TileGeom tile_geometry(const GemmParams& p, int tile,
     tile_coords(p, tile, tm, tn);
     g.m0 = tm * tile_m;
     g.row_end = p.M;
-    g.n0 = tn * p.block_n * p.n_halves;
+    g.n0 = tn * (p.glu ? p.block_n / 2 : p.block_n * p.n_halves);
     g.b_row0 = g.n0;
     return g;
   }
@@ -187,8 +190,8 @@ __device__ __forceinline__ TileGeom tile_geometry(const GemmParams& p, int tile,
   tile_coords_dims(tile - tile_prefix[lo], tiles_m, p.tiles_n, p.group_m, tm, tn);
   g.m0 = row0 + tm * tile_m;
   g.row_end = row1;
-  g.n0 = tn * p.block_n * p.n_halves;
-  g.b_row0 = lo * p.N + g.n0;
+  g.n0 = tn * (p.glu ? p.block_n / 2 : p.block_n * p.n_halves);
+  g.b_row0 = lo * (p.glu ? 2 * p.N : p.N) + g.n0;
   return g;
 }
 
@@ -353,6 +356,60 @@ __device__ __forceinline__ void fast_drain(const GemmParams& p, uint8_t* stg, ui
         }
       }
     }
+    __syncwarp();
+  }
+}
+
+// Drain of a gate/up accumulator: `nchunks` x 32 gate columns at t_gate, the matching up columns at t_up; C receives
+// silu(gate) * up (fp32 math, one cast), 16-bit row-major, whole 64-column runs. Same staging scheme as
+// fast_drain. `release` hands the accumulator back once the last columns sit in registers.
+template <bool kBf16, typename Release>
+__device__ __forceinline__ void glu_drain(const GemmParams& p, uint8_t* stg, uint32_t t_gate, uint32_t t_up, int nchunks,
+                                          int lane, int q, int m0, int n0, int row_end, Release&& release_accumulators) {
+  const int seg = lane & 7, sub = lane >> 3;
+  uint8_t* mine = stg + lane * kEpiRowPitch;
+  unsigned short* c_rows =
+      reinterpret_cast<unsigned short*>(p.C) + static_cast<long long>(m0 + q * 32 + sub) * p.ldc_m + n0 + seg * 8;
+  const int rows_left = row_end - (m0 + q * 32 + sub);
+  for (int c0 = 0; c0 < nchunks; c0 += 2) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t g[32], u[32];
+      tmem_ld_32x32(t_gate + (c0 + half) * 32, g);
+      tmem_ld_32x32(t_up + (c0 + half) * 32, u);
+      tmem_ld_wait(g);
+      tmem_ld_wait(u);
+      if (half == 1 && c0 + 2 >= nchunks) release_accumulators();
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+        const float v0 = g0 / (1.0f + __expf(-g0)) * __uint_as_float(u[2 * j]);
+        const float v1 = g1 / (1.0f + __expf(-g1)) * __uint_as_float(u[2 * j + 1]);
+        if constexpr (kBf16) {
+          __nv_bfloat162 t = __floats2bfloat162_rn(v0, v1);
+          w[j] = *reinterpret_cast<uint32_t*>(&t);
+        } else {
+          __half2 t = __floats2half2_rn(v0, v1);
+          w[j] = *reinterpret_cast<uint32_t*>(&t);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(mine + (((half * 4 + j) ^ (lane & 7)) << 4)) =
+            make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    }
+    __syncwarp();
+    uint4 val[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int row_l = it * 4 + sub;
+      val[it] = *reinterpret_cast<const uint4*>(stg + row_l * kEpiRowPitch + ((seg ^ (row_l & 7)) << 4));
+    }
+#pragma unroll
+    for (int it = 0; it < 8; ++it)
+      if (it * 4 < rows_left)
+        *reinterpret_cast<uint4*>(c_rows + static_cast<long long>(it * 4) * p.ldc_m + c0 * 32) = val[it];
     __syncwarp();
   }
 }
@@ -534,7 +591,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (WorkItem w = next_item(); w.valid && ok; w = next_item()) {
         const TileGeom tg = tile_geometry(p, w.tile, kPairTileM, tile_prefix);
         const int m0 = tg.m0 + static_cast<int>(cta_rank) * kTileM;
-        const int n0 = tg.b_row0 + static_cast<int>(cta_rank) * bn_local;  // row of the B map
+        // row of the B map; in gate/up mode the odd CTA's rows are the up projection's, N rows further down
+        const int n0 = tg.b_row0 + static_cast<int>(cta_rank) * (p.glu ? p.N : bn_local);
         const int sf_n0 = tg.n0;
         // Every other work item walks its K range backwards: the A and B slices the previous item touched last are the
         // ones most likely still in L2 (the accumulation order of those items is reversed with it).
@@ -867,7 +925,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           else mbar_arrive_remote(tmem_empty_remote + acc_i * 8);
         }
       };
-      if (complete && staged && (p.block_n & 63) == 0) {
+      if (p.glu) {
+        // gate values in the accumulator's first block_n / 2 columns, up values in the rest: one fused drain of
+        // block_n / 2 output columns (the host guarantees whole tiles of a data-parallel launch and a 16-bit row-major C)
+        if (p.c_dtype == TB_BF16)
+          glu_drain<true>(p, stg, t_row, t_row + p.block_n / 2, p.block_n / 64, lane, q, m0, tg.n0, row_end, release_accumulator);
+        else
+          glu_drain<false>(p, stg, t_row, t_row + p.block_n / 2, p.block_n / 64, lane, q, m0, tg.n0, row_end, release_accumulator);
+      } else if (complete && staged && (p.block_n & 63) == 0) {
         // Common case (whole tile, 16-bit row-major output, tile width a multiple of 64). Every taken branch inside
         // the drain loop costs an instruction refetch, and a handful of them per 64 columns is what made a drain
         // through the general path three to four times slower than its loads and stores take; so the loop below is

@@ -204,6 +204,16 @@ def swiglu(h: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def _gate_up_swiglu(grouped_fn, rows, w1, group_offsets):
+    """silu(rows @ gate.T) * (rows @ up.T) for w1 = [gate | up]: on the GPU with this library's grouped GEMM the activation
+    runs inside the GEMM's epilogue when the shape allows it (ffn a multiple of 128, more than 128 rows); otherwise GEMM,
+    then `swiglu`."""
+    from .matmul import grouped_matmul
+    if grouped_fn is grouped_matmul and rows.is_cuda and (w1.shape[1] // 2) % 128 == 0 and rows.shape[0] > 128:
+        return grouped_fn(rows, w1, group_offsets, swiglu=True)
+    return swiglu(grouped_fn(rows, w1, group_offsets))
+
+
 class ExpertParallelMoE:
     """Expert-parallel MoE feed-forward: gate/up projection, SwiGLU, down projection, with all-to-all token dispatch.
 
@@ -219,8 +229,7 @@ class ExpertParallelMoE:
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor):
         plan = plan_dispatch(topk_ids, self.num_experts, self.group)
         rows = dispatch(x, topk_ids.shape[1], plan, self.group)
-        h = self.grouped_fn(rows, self.w1, plan.group_offsets)
-        y = self.grouped_fn(swiglu(h), self.w2, plan.group_offsets)
+        y = self.grouped_fn(_gate_up_swiglu(self.grouped_fn, rows, self.w1, plan.group_offsets), self.w2, plan.group_offsets)
         return combine(y, topk_weights, plan, self.group), plan
 
 
@@ -317,8 +326,8 @@ class PeerMemoryMoE:
                                                 plan.src_token.numel(), self.hidden, code, stream)
         _lib.check(rc, "tb_moe_dispatch_peers")
         self.recv_h.barrier(channel=0)                      # every rank's rows have landed in every receive buffer
-        h = grouped_matmul(self.recv, self.w1, plan.group_offsets)
-        grouped_matmul(swiglu(h), self.w2, plan.group_offsets, out=self.y)
+        grouped_matmul(_gate_up_swiglu(grouped_matmul, self.recv, self.w1, plan.group_offsets), self.w2,
+                       plan.group_offsets, out=self.y)
         self.y_h.barrier(channel=0)                         # every rank's expert outputs are complete
         w = topk_weights.to(torch.float32).contiguous()
         out = x.new_empty(tokens, self.hidden)

@@ -288,7 +288,7 @@ def matmul_a8w8(a, b, a_scale, b_scale, c, enable_streamk=False, work_stealing=F
     return persistent_matmul_lt(a, b, c, selector, None, a_scale=a_scale, b_scale=b_scale, quantized=True)
 
 
-def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, selector=None):
+def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, selector=None, swiglu=False):
     """Grouped (MoE) GEMM: out[r] = x[r] @ w[g].T for every row r of group g, rows of group g being
     [group_offsets[g], group_offsets[g+1]).
 
@@ -296,12 +296,18 @@ def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, se
     group_offsets: int32 CUDA tensor of G + 1 ascending offsets (it stays on the device: no host synchronisation);
     out: (rows, N), allocated in x.dtype when omitted. The reference has no grouped kernel; per group this is its dense
     contract (fp32 accumulate, one cast). ``selector`` overrides the tile configuration (tuning and tests).
+
+    ``swiglu=True``: w holds [gate | up] projections, (G, 2*F, K); out is (rows, F) = silu(x @ gate.T) * (x @ up.T),
+    the activation applied to the fp32 accumulators inside the GEMM's epilogue (F a multiple of 128, more than 128 rows).
     """
     assert x.ndim == 2 and w.ndim == 3 and x.shape[1] == w.shape[2], "Incompatible Dimensions"
     if not (x.is_cuda and w.is_cuda and group_offsets.is_cuda):
         raise RuntimeError("tritonblas_b200 runs on CUDA tensors only (no CPU path)")
     rows, K = x.shape
     G, N, _ = w.shape
+    if swiglu:
+        assert N % 256 == 0 and a_scale is None, "swiglu needs F = N / 2 to be a multiple of 128 and no scales"
+        N //= 2
     assert group_offsets.dtype == torch.int32 and group_offsets.numel() == G + 1, "group_offsets must be int32[G + 1]"
     if out is None:
         out = x.new_empty(rows, N)
@@ -313,7 +319,7 @@ def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, se
     # tiles of all groups are pooled over the SMs, so the tile model sees the total row count
     if selector is None:
         # narrow tiles: with many short groups the wide tile's exposed drains outweigh its smaller operand traffic
-        selector = _make_matmul_selector(rows, N, K, x.dtype, w.dtype, out.dtype, x.device, max_halves=1)
+        selector = _make_matmul_selector(rows, 2 * N if swiglu else N, K, x.dtype, w.dtype, out.dtype, x.device, max_halves=1)
     cfg = selector.config_for(False, False)
     args = _lib.GemmArgs()
     args.m, args.n, args.k = rows, N, K
@@ -327,6 +333,7 @@ def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, se
         args.a_scale, args.b_scale = _ptr(a_scale), _ptr(b_scale)
     args.allow_tf32 = 1
     args.group_offsets, args.num_groups = _ptr(group_offsets), G
+    args.epilogue_op = 1 if swiglu else 0
     with torch.cuda.device(x.device):
         rc = _lib.lib.tb_grouped_gemm(ctypes.byref(args), ctypes.byref(cfg), _lib.current_stream_ptr(x.device))
     _lib.check(rc, "tb_grouped_gemm")
