@@ -71,6 +71,17 @@ def test_grouped_gate_up_with_fused_swiglu(counts, ffn, k):
     assert tb.device_status() == 0
 
 
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_grouped_dynamic_schedule_is_bit_identical(swiglu):
+    counts = [5, 9, 1000, 130, 0, 0, 513, 2048, 77]
+    x, w, offs = _case(counts, 512, 384, seed=5)
+    ref = tb.grouped_matmul(x, w, offs, swiglu=swiglu)
+    for _ in range(3):
+        got = tb.grouped_matmul(x, w, offs, swiglu=swiglu, work_stealing=True)
+        assert torch.equal(got, ref)
+    assert tb.device_status() == 0
+
+
 def test_grouped_moe_projection_shapes():
     """BASELINE config 5 at full size: 64 experts, top-8 of 16384 tokens (131072 rows), Zipf(1.1)-skewed counts, hidden
     4096, ffn 1536; gate/up (N = 3072) and down (N = 4096) projections, 48 sampled rows checked per projection."""

@@ -288,7 +288,8 @@ def matmul_a8w8(a, b, a_scale, b_scale, c, enable_streamk=False, work_stealing=F
     return persistent_matmul_lt(a, b, c, selector, None, a_scale=a_scale, b_scale=b_scale, quantized=True)
 
 
-def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, selector=None, swiglu=False):
+def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, selector=None, swiglu=False,
+                   work_stealing=False):
     """Grouped (MoE) GEMM: out[r] = x[r] @ w[g].T for every row r of group g, rows of group g being
     [group_offsets[g], group_offsets[g+1]).
 
@@ -299,6 +300,7 @@ def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, se
 
     ``swiglu=True``: w holds [gate | up] projections, (G, 2*F, K); out is (rows, F) = silu(x @ gate.T) * (x @ up.T),
     the activation applied to the fp32 accumulators inside the GEMM's epilogue (F a multiple of 128, more than 128 rows).
+    ``work_stealing=True`` selects the dynamic tile schedule.
     """
     assert x.ndim == 2 and w.ndim == 3 and x.shape[1] == w.shape[2], "Incompatible Dimensions"
     if not (x.is_cuda and w.is_cuda and group_offsets.is_cuda):
@@ -334,6 +336,8 @@ def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, se
     args.allow_tf32 = 1
     args.group_offsets, args.num_groups = _ptr(group_offsets), G
     args.epilogue_op = 1 if swiglu else 0
+    if work_stealing:  # tiles after each program's first come from a device counter (see persistent_matmul_lt)
+        args.tile_counter = _ptr(_tile_counter_for(x.device))
     with torch.cuda.device(x.device):
         rc = _lib.lib.tb_grouped_gemm(ctypes.byref(args), ctypes.byref(cfg), _lib.current_stream_ptr(x.device))
     _lib.check(rc, "tb_grouped_gemm")
