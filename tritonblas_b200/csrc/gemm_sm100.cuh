@@ -473,6 +473,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       mbar_init(&sched_empty[i], 5 * CTAS);
     }
     mbar_fence_init();
+    // Everything above touched only shared memory. From here on global memory is read, which has to wait for the
+    // previous kernel of the stream when this launch was allowed to start before that one finished.
+    griddep_launch_dependents();
+    griddep_wait();
     if (p.group_offsets != nullptr) {
       // tile_prefix[0 .. G] = tiles before each group, followed by a copy of the G + 1 row offsets
       int acc_tiles = 0;
