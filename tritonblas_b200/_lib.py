@@ -161,5 +161,18 @@ def raise_on_device_failure(device=None):
         raise TritonBlasError(f"device-side failure: {lib.tb_status_string(code).decode()} [code {code}]")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def current_stream_ptr(device=None):
+    """The current CUDA stream of `device` as a pointer (the raw-handle getter when torch has it: it skips building a
+    torch.cuda.Stream object on every launch)."""
+    if _raw_stream is not None:
+        if device is None:
+            index = torch.cuda.current_device()
+        elif isinstance(device, int):
+            index = device
+        else:
+            index = device.index if device.index is not None else torch.cuda.current_device()
+        return ctypes.c_void_p(_raw_stream(index))
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)

@@ -179,8 +179,17 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const Gemm
   if constexpr (KIND == 0) {
     if ((p.debug_flags & 2) && p.debug_out != nullptr) kernel = gemm_kernel<KIND, CTAS, true>;
   }
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
+  // The opt-in shared-memory size is set once per kernel instantiation and device (and again if a launch needs more).
+  static int configured[2][64] = {};
+  int dev_index = 0;
+  cudaGetDevice(&dev_index);
+  int& have = configured[kernel == gemm_kernel<KIND, CTAS, false> ? 0 : 1][dev_index & 63];
+  cudaError_t e = cudaSuccess;
+  if (smem_bytes > have) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
+    have = smem_bytes;
+  }
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(static_cast<unsigned>(programs * CTAS), 1, 1);
   lc.blockDim = dim3(gemm_threads<KIND>(), 1, 1);

@@ -174,9 +174,13 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
         holder = config if (config is not None and config.workspace.numel() >= need) else _workspace_for(a.device, need)
         args.workspace, args.workspace_bytes = _ptr(holder.workspace), holder.workspace.numel()
         args.epoch = holder.next_epoch()
-    with torch.cuda.device(a.device):
+    if a.device.index is None or a.device.index == torch.cuda.current_device():
         rc = _lib.lib.tb_gemm(ctypes.byref(args), ctypes.byref(cfg), _lib.current_stream_ptr(a.device))
-    _lib.check(rc, "tb_gemm")
+    else:
+        with torch.cuda.device(a.device):
+            rc = _lib.lib.tb_gemm(ctypes.byref(args), ctypes.byref(cfg), _lib.current_stream_ptr(a.device))
+    if rc:
+        _lib.check(rc, "tb_gemm")
     return c
 
 
@@ -211,11 +215,25 @@ def matmul_a8w8_lt(a, b, a_scale, b_scale, c, selector, config: Optional[MatmulC
                                 work_stealing=work_stealing)
 
 
+_selector_cache = {}
+
+
 def _selector_for(a, b, c_dtype, streamk):
+    """Selector for the convenience entry points (the reference re-runs its selector on every call, matmul.py:407; the
+    result only depends on the key below, so it is kept)."""
     M, K = a.shape
     _, N = b.shape
-    return _make_matmul_selector(M, N, K, a.dtype, b.dtype, c_dtype, a.device, streamk=bool(streamk),
-                                 a_mn_major=_is_mn_major(_unit_stride_2d(a), 1), b_mn_major=_is_mn_major(_unit_stride_2d(b), 0))
+    a_mn = _is_mn_major(_unit_stride_2d(a), 1)
+    b_mn = _is_mn_major(_unit_stride_2d(b), 0)
+    key = (M, N, K, a.dtype, b.dtype, c_dtype, a.device, bool(streamk), a_mn, b_mn)
+    sel = _selector_cache.get(key)
+    if sel is None:
+        if len(_selector_cache) >= 1024:
+            _selector_cache.clear()
+        sel = _make_matmul_selector(M, N, K, a.dtype, b.dtype, c_dtype, a.device, streamk=bool(streamk),
+                                    a_mn_major=a_mn, b_mn_major=b_mn)
+        _selector_cache[key] = sel
+    return sel
 
 
 # ---------------------------------------------------------------------------------------------- custom ops
