@@ -130,7 +130,15 @@ int select_config(const tb_problem& p_in, const MachineModel& hw, tb_config* out
       const long long waves = (tiles + programs - 1) / programs;
       const double tile_clk = halves == 2 ? nkb * stage_clk + 2.0 * drain_clk : std::max(nkb * stage_clk, drain_clk);
       double dp = (waves * tile_clk + ramp_clk + drain_clk) * clk_to_us;
-      dp = std::max(dp, hbm_floor(active_ctas)) + hw.launch_us;
+      // HBM floor per wave: the bytes of the full waves move with every program pulling, those of the ragged last wave
+      // with only its programs pulling (224 tiles on 148 programs: the last 76 tiles stream at 0.59 of the bandwidth).
+      {
+        const long long full = tiles / programs, rem = tiles % programs;
+        double floor_us = 0.0;
+        if (full > 0) floor_us += hbm_floor(static_cast<long long>(programs) * pair) * (static_cast<double>(full * programs) / tiles);
+        if (rem > 0) floor_us += hbm_floor(rem * pair) * (static_cast<double>(rem) / tiles);
+        dp = std::max(dp, floor_us) + hw.launch_us;
+      }
       // stream-K: stages per program, plus one partial tile written and read back through L2, plus the flag hop
       const int sk_grid = static_cast<int>(std::min<long long>(programs, tiles * nkb));
       const double per_prog = std::ceil(static_cast<double>(tiles) * nkb / sk_grid);
