@@ -1,0 +1,27 @@
+"""The YAML -> CSV benchmark driver runs end to end on the GPU and checks its own results."""
+import csv
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("flags", [[], ["--enable-streamk"], ["--work-stealing"], ["--cu-sweep", "148,64"]])
+def test_yaml_cases_produce_csv_rows(tmp_path, flags):
+    from tritonblas_b200 import bench_matmul as bm
+    cases = tmp_path / "cases.yaml"
+    cases.write_text(
+        "- {m: 512, n: 768, k: 256, in_dtype: bf16, out_dtype: bf16, transA: T, transB: N}\n"
+        "- {m: 300, n: 520, k: 512, in_dtype: fp16, out_dtype: fp16, transA: N, transB: T}\n"
+        "- {m: 256, n: 512, k: 512, in_dtype: fp8_e4m3, out_dtype: bf16, transA: T, transB: N}\n")
+    out = tmp_path / "out.csv"
+    rows = bm.main(["--input-yaml", str(cases), "--output-csv", str(out), "--checkcorrectness", "--warmup", "2",
+                    "--repeat", "3"] + flags)
+    sweeps = 2 if "--cu-sweep" in flags else 1
+    assert len(rows) == 3 * sweeps
+    with open(out) as f:
+        read = list(csv.DictReader(f))
+    assert len(read) == 3 * sweeps
+    assert all(float(r["tritonblas_gflops"]) > 0 and float(r["us"]) > 0 for r in read)
+    expected_mode = "streamk" if "--enable-streamk" in flags else "work_stealing" if "--work-stealing" in flags else "persistent"
+    assert {r["mode"] for r in read} == {expected_mode}
