@@ -364,7 +364,15 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   {
     const char* dbg = getenv("TB_DEBUG_FLAGS");
     p.debug_flags = dbg != nullptr ? atoi(dbg) : 0;
-    p.debug_out = (p.debug_flags & 2) ? reinterpret_cast<long long*>(a.workspace) : nullptr;
+    // role cycle counters (148 x 16 words): the start of the workspace for data-parallel launches, its last 19 KB for
+    // stream-K launches whose caller over-allocated by that much
+    constexpr long long kDebugBytes = 148 * 16 * 8;
+    p.debug_out = nullptr;
+    if ((p.debug_flags & 2) && a.workspace != nullptr) {
+      if (!a.streamk) p.debug_out = reinterpret_cast<long long*>(a.workspace);
+      else if (a.workspace_bytes >= tb_gemm_workspace_bytes(&cfg, a.sk_grid) + kDebugBytes)
+        p.debug_out = reinterpret_cast<long long*>(static_cast<char*>(a.workspace) + ((a.workspace_bytes - kDebugBytes) & ~7ll));
+    }
     // Dense data-parallel launches: odd items walk K backwards (L2 reuse between consecutive tiles; +0.5-1 % sustained on
     // 8192^3). Not for grouped launches, where it measured 6 % slower on Zipf-sized groups.
     // Bit 3 of the debug flags turns it off for A/B measurements.

@@ -314,9 +314,12 @@ __device__ __forceinline__ void pack_chunk(const GemmParams& p, const uint32_t (
 // Drain of one whole 128 x block_n accumulator to a 16-bit row-major C (block_n a multiple of 64), straight-line per
 // 64-column run: two TMEM loads in flight, pack into the warp's staging rows, read back as 128-byte row runs, store.
 // `release` hands the accumulator back to the MMA issuer; it is called once the last columns sit in registers.
-template <int KIND, bool kBf16, bool kMath, bool kExtra, typename Release>
+// kFix (stream-K tile owners): the fp32 partial tiles of `fix_count` peers, `fix_stride` floats apart starting at
+// fix_src (already offset to this thread's row), are added in that order before scale, bias and cast.
+template <int KIND, bool kBf16, bool kMath, bool kExtra, bool kFix, typename Release>
 __device__ __forceinline__ void fast_drain(const GemmParams& p, uint8_t* stg, uint32_t t_row, int nchunks, int lane, int q,
-                                           int m0, int n0, int row, int row_end, float a_s, Release&& release_accumulator) {
+                                           int m0, int n0, int row, int row_end, float a_s, Release&& release_accumulator,
+                                           const float* fix_src = nullptr, size_t fix_stride = 0, int fix_count = 0) {
 
   const int seg = lane & 7, sub = lane >> 3;
   uint8_t* mine = stg + lane * kEpiRowPitch;
@@ -331,8 +334,31 @@ __device__ __forceinline__ void fast_drain(const GemmParams& p, uint8_t* stg, ui
     tmem_ld_wait(r0);
     tmem_ld_wait(r1);
     if (c0 + 2 >= nchunks) release_accumulator();  // the last columns sit in registers
-    pack_chunk<KIND, kBf16, kMath>(p, r0, mine, lane, n0 + c0 * 32, 0, a_s, row, row_end);
-    pack_chunk<KIND, kBf16, kMath>(p, r1, mine, lane, n0 + c0 * 32 + 32, 4, a_s, row, row_end);
+    if constexpr (kFix) {
+      float f0[32], f1[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        f0[j] = (KIND == 4) ? __int2float_rn(static_cast<int>(r0[j])) : __uint_as_float(r0[j]);
+        f1[j] = (KIND == 4) ? __int2float_rn(static_cast<int>(r1[j])) : __uint_as_float(r1[j]);
+      }
+      for (int pp = 0; pp < fix_count; ++pp) {
+        const float* src = fix_src + pp * fix_stride + static_cast<size_t>(c0 * 32) * kTileM;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f0[j] += __ldcg(src + j * kTileM);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f1[j] += __ldcg(src + (32 + j) * kTileM);
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        r0[j] = __float_as_uint(f0[j]);
+        r1[j] = __float_as_uint(f1[j]);
+      }
+      pack_chunk<0, kBf16, kMath>(p, r0, mine, lane, n0 + c0 * 32, 0, a_s, row, row_end);
+      pack_chunk<0, kBf16, kMath>(p, r1, mine, lane, n0 + c0 * 32 + 32, 4, a_s, row, row_end);
+    } else {
+      pack_chunk<KIND, kBf16, kMath>(p, r0, mine, lane, n0 + c0 * 32, 0, a_s, row, row_end);
+      pack_chunk<KIND, kBf16, kMath>(p, r1, mine, lane, n0 + c0 * 32 + 32, 4, a_s, row, row_end);
+    }
     __syncwarp();
     uint4 val[8];
 #pragma unroll
@@ -936,28 +962,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           glu_drain<true>(p, stg, t_row, t_row + p.block_n / 2, p.block_n / 64, lane, q, m0, tg.n0, row_end, release_accumulator);
         else
           glu_drain<false>(p, stg, t_row, t_row + p.block_n / 2, p.block_n / 64, lane, q, m0, tg.n0, row_end, release_accumulator);
-      } else if (complete && staged && (p.block_n & 63) == 0) {
-        // Common case (whole tile, 16-bit row-major output, tile width a multiple of 64). Every taken branch inside
-        // the drain loop costs an instruction refetch, and a handful of them per 64 columns is what made a drain
-        // through the general path three to four times slower than its loads and stores take; so the loop below is
-        // straight-line, and the choices (output type, scales or bias, extra destinations) are made once per tile
-        // by picking one of its instantiations.
+      } else if (owner && staged && (p.block_n & 63) == 0 && (complete || p.num_c_extra == 0)) {
+        // Common case (whole tile or a stream-K owner's fix-up, 16-bit row-major output, tile width a multiple of 64).
+        // Every taken branch inside the drain loop costs an instruction refetch, and a handful of them per 64 columns is
+        // what made a drain through the general path three to four times slower than its loads and stores take; so the
+        // loop is straight-line, and the choices (output type, scales or bias, extra destinations, partial tiles to add)
+        // are made once per tile by picking one of its instantiations.
         const bool has_math = p.a_scale != nullptr || p.b_scale != nullptr || p.bias != nullptr;
         const long long q0 = prof ? clock64() : 0;
-#define TB_FAST_DRAIN(BF, MATH, EXTRA) \
-  fast_drain<KIND, BF, MATH, EXTRA>(p, stg, t_row, nchunks, lane, q, m0, n0, row, row_end, a_s, release_accumulator)
-        if (p.num_c_extra > 0) {
-          if (p.c_dtype == TB_BF16) { if (has_math) TB_FAST_DRAIN(true, true, true); else TB_FAST_DRAIN(true, false, true); }
-          else { if (has_math) TB_FAST_DRAIN(false, true, true); else TB_FAST_DRAIN(false, false, true); }
+        const float* fix_src =
+            complete ? nullptr
+                     : p.partials + static_cast<size_t>((pid + 1) * CTAS + static_cast<int>(cta_rank)) * slot_elems + row_in_tile;
+#define TB_FAST_DRAIN(BF, MATH, EXTRA, FIX)                                                                      \
+  fast_drain<KIND, BF, MATH, EXTRA, FIX>(p, stg, t_row, nchunks, lane, q, m0, n0, row, row_end, a_s, release_accumulator, \
+                                         fix_src, static_cast<size_t>(CTAS) * slot_elems, peer_end - pid - 1)
+        if (!complete) {
+          if (p.c_dtype == TB_BF16) { if (has_math) TB_FAST_DRAIN(true, true, false, true); else TB_FAST_DRAIN(true, false, false, true); }
+          else { if (has_math) TB_FAST_DRAIN(false, true, false, true); else TB_FAST_DRAIN(false, false, false, true); }
+        } else if (p.num_c_extra > 0) {
+          if (p.c_dtype == TB_BF16) { if (has_math) TB_FAST_DRAIN(true, true, true, false); else TB_FAST_DRAIN(true, false, true, false); }
+          else { if (has_math) TB_FAST_DRAIN(false, true, true, false); else TB_FAST_DRAIN(false, false, true, false); }
         } else if (p.c_dtype == TB_BF16) {
-          if (has_math) TB_FAST_DRAIN(true, true, false); else TB_FAST_DRAIN(true, false, false);
+          if (has_math) TB_FAST_DRAIN(true, true, false, false); else TB_FAST_DRAIN(true, false, false, false);
         } else {
-          if (has_math) TB_FAST_DRAIN(false, true, false); else TB_FAST_DRAIN(false, false, false);
+          if (has_math) TB_FAST_DRAIN(false, true, false, false); else TB_FAST_DRAIN(false, false, false, false);
         }
 #undef TB_FAST_DRAIN
         if (prof) prof_drain += clock64() - q0;
+      } else if (!owner) {
+        // Partial tile of a stream-K launch: raw fp32 accumulators to this program's slot, column-major so that a warp
+        // writes 128 contiguous bytes per column. The tile's owner is waiting for it, so this loop is kept straight-line.
+        float* dst0 = p.partials + slot * slot_elems + row_in_tile;
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait(r);
+          if (c + 1 == nchunks) release_accumulator();
+          float* dst = dst0 + static_cast<size_t>(c * 32) * kTileM;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            dst[j * kTileM] = (KIND == 4) ? __int2float_rn(static_cast<int>(r[j])) : __uint_as_float(r[j]);
+        }
       } else {
-        // General path: partial tiles of a stream-K launch, their fix-up, and every other output type and layout.
+        // General path: fix-ups and whole tiles with any other output type or layout.
         for (int c = 0; c < nchunks; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
