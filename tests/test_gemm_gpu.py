@@ -301,3 +301,28 @@ def test_decode_shape_a8w8_scales_swap_with_operands():
     c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
     tb.matmul_a8w8(a8, b8, a_s, b_s, c)
     assert_close_to_oracle(c, a8, b8, a_scale=a_s, b_scale=b_s, what="decode a8w8")
+
+
+def test_stream_order_is_kept_with_early_kernel_launch():
+    """GEMM launches may be scheduled before the previous kernel of the stream has finished (programmatic dependent
+    launch); they must still see everything enqueued before them: chained GEMMs, async host copies, torch kernels."""
+    m = n = k = 512
+    g = torch.Generator().manual_seed(77)
+    b1 = (torch.randn(k, n, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    b2 = (torch.randn(n, n, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    a_dev = torch.empty(m, k, dtype=torch.bfloat16, device="cuda")
+    hosts = [(torch.randn(m, k, generator=g)).to(torch.bfloat16).pin_memory() for _ in range(12)]
+    outs = []
+    for h in hosts:
+        a_dev.copy_(h, non_blocking=True)          # copy -> GEMM -> GEMM -> torch kernel -> GEMM, all on one stream
+        c1 = tb.matmul(a_dev, b1)
+        c2 = tb.matmul(c1, b2)
+        c3 = tb.matmul(torch.relu(c2), b2)
+        outs.append(c3)
+    torch.cuda.synchronize()
+    for h, c3 in zip(hosts, outs):
+        r1 = (h.float() @ b1.float().cpu()).to(torch.bfloat16)
+        r2 = (r1.float() @ b2.float().cpu()).to(torch.bfloat16)
+        r3 = torch.relu(r2).float() @ b2.float().cpu()
+        err = (c3.float().cpu() - r3).abs().max().item()
+        assert err <= 3e-2 * r3.abs().max().item() + 1e-3, err
