@@ -343,6 +343,10 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
                 (reinterpret_cast<uintptr_t>(a.c) & 15) == 0;
     for (int x = 0; x < a.num_c_copies; ++x) ok16 = ok16 && (reinterpret_cast<uintptr_t>(a.c_copies[x]) & 15) == 0;
     p.staged_store = ok16 ? 1 : 0;
+    p.staged_f32 = (a.c_dtype == TB_DTYPE_F32 && a.c_stride_n == 1 && ((a.c_stride_m * 4) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(a.c) & 15) == 0 && a.num_c_copies == 0)
+                       ? 1
+                       : 0;
   }
   p.a_scale = a.a_scale; p.b_scale = a.b_scale;
   p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;

@@ -74,6 +74,7 @@ struct GemmParams {
   const void* bias;      // (N,) or null
   long long bias_stride;
   int bias_dtype;
+  int staged_f32;        // 1: fp32 output, unit column stride, 16-byte aligned rows, no extra destinations
   int staged_store;      // 1: 16-bit output, unit column stride, 16-byte aligned rows in every destination
   int bias_along_m;      // 1: bias indexed by row (set when the problem was transposed to C^T = B^T A^T)
   // schedule
@@ -382,6 +383,61 @@ __device__ __forceinline__ void fast_drain(const GemmParams& p, uint8_t* stg, ui
         }
       }
     }
+    __syncwarp();
+  }
+}
+
+// The same for a row-major fp32 C (16-byte aligned rows, whole tiles): per 32 columns the lane's 128-byte row passes
+// through the staging rows and leaves as full 128-byte runs.
+template <int KIND, bool kMath, typename Release>
+__device__ __forceinline__ void fast_drain_f32(const GemmParams& p, uint8_t* stg, uint32_t t_row, int nchunks, int lane, int q,
+                                               int m0, int n0, int row, int row_end, float a_s, Release&& release_accumulator) {
+  const int seg = lane & 7, sub = lane >> 3;
+  uint8_t* mine = stg + lane * kEpiRowPitch;
+  float* c_rows = reinterpret_cast<float*>(p.C) + static_cast<long long>(m0 + q * 32 + sub) * p.ldc_m + n0 + seg * 4;
+  const int rows_left = row_end - (m0 + q * 32 + sub);
+  for (int c = 0; c < nchunks; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_row + c * 32, r);
+    tmem_ld_wait(r);
+    if (c + 1 == nchunks) release_accumulator();
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = (KIND == 4) ? __int2float_rn(static_cast<int>(r[j])) : __uint_as_float(r[j]);
+    if constexpr (kMath) {
+      const int col0 = n0 + c * 32;
+      if (p.a_scale != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= a_s;
+      }
+      if (p.b_scale != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= p.b_scale[col0 + j];
+      }
+      if (p.bias != nullptr) {
+        if (p.bias_along_m) {
+          const float bv = row < row_end ? load_as_float(p.bias, row * p.bias_stride, p.bias_dtype) : 0.0f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += bv;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += load_as_float(p.bias, (col0 + j) * p.bias_stride, p.bias_dtype);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<float4*>(mine + ((j ^ (lane & 7)) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    __syncwarp();
+    float4 val[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int row_l = it * 4 + sub;
+      val[it] = *reinterpret_cast<const float4*>(stg + row_l * kEpiRowPitch + ((seg ^ (row_l & 7)) << 4));
+    }
+#pragma unroll
+    for (int it = 0; it < 8; ++it)
+      if (it * 4 < rows_left) *reinterpret_cast<float4*>(c_rows + static_cast<long long>(it * 4) * p.ldc_m + c * 32) = val[it];
     __syncwarp();
   }
 }
@@ -989,6 +1045,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
 #undef TB_FAST_DRAIN
         if (prof) prof_drain += clock64() - q0;
+      } else if (complete && p.staged_f32 && n0 + p.block_n <= p.N) {
+        if (p.a_scale != nullptr || p.b_scale != nullptr || p.bias != nullptr)
+          fast_drain_f32<KIND, true>(p, stg, t_row, nchunks, lane, q, m0, n0, row, row_end, a_s, release_accumulator);
+        else
+          fast_drain_f32<KIND, false>(p, stg, t_row, nchunks, lane, q, m0, n0, row, row_end, a_s, release_accumulator);
       } else if (!owner) {
         // Partial tile of a stream-K launch: raw fp32 accumulators to this program's slot, column-major so that a warp
         // writes 128 contiguous bytes per column. The tile's owner is waiting for it, so this loop is kept straight-line.
