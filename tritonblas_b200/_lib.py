@@ -155,9 +155,14 @@ def device_status(device=None):
     return out.value
 
 
+_failure_hooks = []  # callables run when a device-side failure is reported (e.g. to zero shared launch state)
+
+
 def raise_on_device_failure(device=None):
     code = device_status(device)
     if code != 0:
+        for hook in _failure_hooks:
+            hook()
         raise TritonBlasError(f"device-side failure: {lib.tb_status_string(code).decode()} [code {code}]")
 
 

@@ -42,6 +42,15 @@ def _tile_counter_for(device):
     return buf
 
 
+def _reset_tile_counters():
+    """A launch that gave up mid-way leaves its counter words non-zero; zero them before the next dynamic launch."""
+    for buf in _global_tile_counters.values():
+        buf.zero_()
+
+
+_lib._failure_hooks.append(_reset_tile_counters)
+
+
 def _workspace_for(device, nbytes):
     key = (device.type, device.index)
     ws = _global_workspaces.get(key)
