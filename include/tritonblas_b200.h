@@ -171,6 +171,10 @@ int tb_swiglu(const void* h, int64_t h_row_stride, void* out, int64_t out_row_st
               int32_t dtype, void* stream);
 int tb_moe_combine(const void* y, int64_t y_row_stride, const int64_t* pos, const float* weights, void* out,
                    int64_t out_row_stride, int32_t tokens, int32_t topk, int32_t hidden, int32_t dtype, void* stream);
+/*   tb_moe_gather_rows: out[i, :] = x[src_row[i], :] for i < n (token rows into expert-major order on one GPU); int64
+ *                       indices, 16-byte aligned rows, hidden a multiple of 8 elements of 2 bytes. */
+int tb_moe_gather_rows(const void* x, int64_t x_row_stride, const int64_t* src_row, void* out, int64_t out_row_stride,
+                       int64_t n, int32_t hidden, void* stream);
 
 /* Expert-parallel dispatch and combine over peer-mapped memory (each rank's receive / output buffer mapped into every
  * process, e.g. by CUDA IPC or torch symmetric memory), in place of all-to-all collectives. Ordinary loads and stores.

@@ -127,3 +127,15 @@ def test_swiglu_and_combine_kernels_match_fp32_formulas():
     ref = x.float().cpu() * w.sum(1, keepdim=True).cpu()     # every copy is the token itself
     assert torch.allclose(out, ref, rtol=1e-2, atol=1e-2)
     assert tb.device_status() == 0
+
+
+def test_row_gather_kernel_matches_index_select():
+    from tritonblas_b200 import distributed as tbd
+    g = torch.Generator().manual_seed(9)
+    for rows, hidden in ((1, 8), (333, 520), (4096, 4096)):
+        x = torch.randn(rows, hidden, generator=g).to(torch.bfloat16).cuda()
+        idx = torch.randint(0, rows, (3 * rows + 5,), generator=g).cuda()
+        assert torch.equal(tbd._gather_rows(x, idx), x.index_select(0, idx))
+        view = x[:, : hidden - (hidden % 16 or 8)] if hidden > 8 else x          # a row-strided view keeps the kernel path
+        assert torch.equal(tbd._gather_rows(view, idx), view.index_select(0, idx))
+    assert tb.device_status() == 0

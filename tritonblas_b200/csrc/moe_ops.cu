@@ -250,6 +250,39 @@ extern "C" int tb_moe_dispatch_peers(const void* x, int64_t x_row_stride, const 
   return TB_OK;
 }
 
+namespace tb {
+namespace {
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ x, long long x_stride_vec,
+                                                            const long long* __restrict__ src_row, uint4* __restrict__ out,
+                                                            long long out_stride_vec, long long n, int vec_per_row) {
+  // one warp per output row; rows are streamed once
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; r < n; r += warps) {
+    const uint4* src = x + src_row[r] * x_stride_vec;
+    uint4* dst = out + r * out_stride_vec;
+    for (int v = lane; v < vec_per_row; v += 32) __stcs(dst + v, __ldg(src + v));
+  }
+}
+}  // namespace
+}  // namespace tb
+
+extern "C" int tb_moe_gather_rows(const void* x, int64_t x_row_stride, const int64_t* src_row, void* out,
+                                  int64_t out_row_stride, int64_t n, int32_t hidden, void* stream) {
+  if (x == nullptr || src_row == nullptr || out == nullptr || n < 0 || hidden <= 0 || (hidden % 8) != 0) return TB_ERR_INVALID;
+  if (n == 0) return TB_OK;
+  if (!tb::aligned16(x, x_row_stride) || !tb::aligned16(out, out_row_stride)) return TB_ERR_ALIGNMENT;
+  long long blocks = (n + 7) / 8;
+  if (blocks > 148LL * 8 * 4) blocks = 148LL * 8 * 4;
+  tb::gather_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), x_row_stride / 8, reinterpret_cast<const long long*>(src_row), static_cast<uint4*>(out),
+      out_row_stride / 8, n, hidden / 8);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return tb::cuda_fail(e, "gather_rows_kernel launch");
+  tb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return TB_OK;
+}
+
 extern "C" int tb_moe_combine_peers(void* const* y_peers, int32_t num_peers, int64_t y_row_stride, const int32_t* pair_rank,
                                     const int64_t* pair_row, const float* weights, void* out, int64_t out_row_stride,
                                     int32_t tokens, int32_t topk, int32_t hidden, int32_t dtype, void* stream) {

@@ -146,10 +146,27 @@ def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None) -> Dispa
                         regroup_inv, pos)
 
 
+def _gather_rows(x: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """x[index] for 2-D x: this library's row-gather kernel for 16-bit CUDA rows of 16-byte multiples, torch otherwise."""
+    if not (x.is_cuda and x.element_size() == 2 and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0):
+        return x.index_select(0, index)
+    import ctypes
+    from . import _lib
+    index = index.to(torch.int64).contiguous()
+    out = x.new_empty(index.numel(), x.shape[1])
+    with torch.cuda.device(x.device):
+        rc = _lib.lib.tb_moe_gather_rows(ctypes.c_void_p(x.data_ptr()), x.stride(0), ctypes.c_void_p(index.data_ptr()),
+                                         ctypes.c_void_p(out.data_ptr()), out.stride(0), index.numel(), x.shape[1],
+                                         _lib.current_stream_ptr(x.device))
+    _lib.check(rc, "tb_moe_gather_rows")
+    return out
+
+
 def dispatch(x: torch.Tensor, topk: int, plan: DispatchPlan, group=None) -> torch.Tensor:
     """Rows of x (T, H), replicated topk times and ordered by expert, sent to the experts' owners. Returns the rows this
     rank's experts must process, expert-major (aligned with plan.group_offsets)."""
-    rows = x.index_select(0, plan.sort_idx // topk)
+    rows = _gather_rows(x, plan.sort_idx // topk)
     if plan.regroup_idx is None:
         return rows
     recv = rows.new_empty(int(sum(plan.recv_splits)), x.shape[1])
