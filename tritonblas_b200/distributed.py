@@ -171,7 +171,7 @@ def dispatch(x: torch.Tensor, topk: int, plan: DispatchPlan, group=None) -> torc
         return rows
     recv = rows.new_empty(int(sum(plan.recv_splits)), x.shape[1])
     dist.all_to_all_single(recv, rows, plan.recv_splits, plan.send_splits, group=group)
-    return recv.index_select(0, plan.regroup_idx)
+    return _gather_rows(recv, plan.regroup_idx)
 
 
 def combine(y: torch.Tensor, topk_weights: torch.Tensor, plan: DispatchPlan, group=None) -> torch.Tensor:
@@ -179,7 +179,7 @@ def combine(y: torch.Tensor, topk_weights: torch.Tensor, plan: DispatchPlan, gro
     (fp32 accumulate in k order, one cast)."""
     tokens, topk = topk_weights.shape
     if plan.regroup_idx is not None:
-        src_major = y.index_select(0, plan.regroup_inv)          # a gather; the scatter form is several times slower
+        src_major = _gather_rows(y, plan.regroup_inv)            # a gather; the scatter form is several times slower
         back = y.new_empty(int(sum(plan.send_splits)), y.shape[1])
         dist.all_to_all_single(back, src_major, plan.send_splits, plan.recv_splits, group=group)
     else:
