@@ -103,7 +103,8 @@ typedef struct tb_gemm_args {
                             the workspace must be zero-filled once when it is created) */
   /* Grouped (MoE) GEMM, tb_grouped_gemm only: group g multiplies rows [group_offsets[g], group_offsets[g+1]) of A
    * (m = total rows) by its own B_g, stored as rows [g*n, (g+1)*n) of a (num_groups*n, k) K-contiguous matrix, into the
-   * same rows of C. group_offsets is a DEVICE array of num_groups + 1 ascending int32. */
+   * same rows of C. group_offsets is a DEVICE array of num_groups + 1 ascending int32; the kernel clamps the offsets to
+   * [0, m], so offsets that describe more than m rows lose their tail instead of reaching past A and C. */
   const int32_t* group_offsets;
   int32_t num_groups;
   /* Fused output fan-out (tb_gemm only): up to 7 further destinations with c's dtype, shape and strides — typically the
@@ -127,6 +128,15 @@ typedef struct tb_gemm_args {
    * schedule; the library then runs CTA pairs whose accumulators hold 128 gate and 128 up columns side by side, so the
    * activation hides behind the next tile's main loop. TB_ERR_UNSUPPORTED otherwise. */
   int32_t epilogue_op;
+  /* Bound of every device-side wait of this launch in milliseconds; 0 = the default of 2 s. A wait that runs out makes
+   * the kernel record a TB_DEV_* code (tb_device_status) and return; nothing spins for ever (the reference's waits are
+   * unbounded, kernels/streamk_gemm.py:295-300). */
+  int32_t wait_timeout_ms;
+  /* Measurement and test switches, 0 in production. Bit 1 (value 2): per-role cycle counters are written to the start of
+   * `workspace` (148 x 16 int64). Bit 2 (value 4): stream-K programs never publish their partial tile, so the owners'
+   * bounded waits run out (RESULTS ARE WRONG; the failure-path test uses it). Bit 3 (value 8): every work item walks K
+   * forwards. */
+  int32_t debug_flags;
 } tb_gemm_args;
 
 /* Fill `cfg` for `p`. Stands in for origami.select_config + OrigamiMatmulSelector._compute_sk_grid
@@ -181,7 +191,8 @@ int tb_moe_gather_rows(const void* x, int64_t x_row_stride, const int64_t* src_r
  *   tb_moe_dispatch_peers: for i < n, row src_token[i] of x is copied to row dest_row[i] of peer_bufs[dest_rank[i]];
  *                          rows outside [0, capacity_rows) are dropped and counted in *overflow_count (device int, may
  *                          be NULL).
- *   tb_moe_combine_peers:  out[t, :] = sum_k weights[t,k] * y_peers[pair_rank[t,k]][pair_row[t,k], :] (fp32, k order).
+ *   tb_moe_combine_peers:  out[t, :] = sum_k weights[t,k] * y_peers[pair_rank[t,k]][pair_row[t,k], :] (fp32, k order);
+ *                          pairs whose row lies outside [0, capacity_rows), i.e. rows the dispatch dropped, add nothing.
  * peer_bufs / y_peers are HOST arrays of up to 8 device pointers; index arrays are device memory. The caller orders the
  * phases across ranks (barrier after dispatch, barrier before combine). No reference counterpart. */
 int tb_moe_dispatch_peers(const void* x, int64_t x_row_stride, const int64_t* src_token, const int32_t* dest_rank,
@@ -190,7 +201,7 @@ int tb_moe_dispatch_peers(const void* x, int64_t x_row_stride, const int64_t* sr
                           void* stream);
 int tb_moe_combine_peers(void* const* y_peers, int32_t num_peers, int64_t y_row_stride, const int32_t* pair_rank,
                          const int64_t* pair_row, const float* weights, void* out, int64_t out_row_stride, int32_t tokens,
-                         int32_t topk, int32_t hidden, int32_t dtype, void* stream);
+                         int32_t topk, int32_t hidden, int32_t dtype, int64_t capacity_rows, void* stream);
 
 /* MXFP4 GEMM: C (m, n) = sum over 32-element K blocks of (A_e2m1 * 2^(sa-127)) . (B_e2m1 * 2^(sb-127)), fp32
  * accumulate, one cast. A is (m, k/2) bytes and B is (n, k/2) bytes, two e2m1 codes per byte (even element in the low

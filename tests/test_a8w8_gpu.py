@@ -102,13 +102,19 @@ def test_int8_output_saturates():
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rows,k", [(1, 8), (37, 264), (256, 8192), (1000, 1536)])
-def test_fp8_row_quantiser_is_bit_exact_against_the_fixture(rows, k, dtype):
+def test_fp8_row_quantiser_is_bit_exact_against_the_oracle(rows, k, dtype):
+    """The CUDA quantiser against the CPU oracle's restatement of the reference fixture (utils.py:340-377), and the
+    package's torch fixture against the same oracle, so all three agree bit for bit."""
     g = torch.Generator().manual_seed(rows + k)
     x = (torch.randn(rows, k, generator=g) * 3).to(dtype).cuda()
     x[0, 0] = 0.0
     if rows > 2:
         x[2] = 0.0                                    # all-zero row: scale clamps at 1e-8 / 448
     q, s = utils.quantize_fp8_rows(x)
-    q_ref, s_ref = utils.quantize_tensor_per_channel(x, FP8, axis=1)
-    assert torch.equal(s, s_ref)
-    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+    from oracle import gemm_oracle
+    q_ref, s_ref = gemm_oracle.quantize_per_channel_ref(x, FP8, axis=1)
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+    q_fix, s_fix = utils.quantize_tensor_per_channel(x, FP8, axis=1)
+    assert torch.equal(s_fix.cpu().reshape(-1), s_ref)
+    assert torch.equal(q_fix.cpu().view(torch.uint8), q_ref.view(torch.uint8))

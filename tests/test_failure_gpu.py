@@ -1,9 +1,7 @@
 """Failure path of the device-side bounded waits, without faulting or hanging the GPU: a stream-K launch in which the
-programs that hold the tail of a tile's K range never raise their "partial published" flag (a test knob of the library).
+programs that hold the tail of a tile's K range never raise their "partial published" flag (a test switch of the library, set on the caller's MatmulConfig).
 The tile owners' wait runs out after the configured bound, the kernel records a status code and returns normally, the
 host reads the code, and the context stays usable for the next launch."""
-import os
-
 import pytest
 import torch
 
@@ -21,25 +19,21 @@ def test_owner_wait_times_out_cleanly_and_context_survives():
     cfg = tb.matmul_preamble(sel)
     c = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
     assert tb.device_status() == 0
-    os.environ["TB_DEBUG_FLAGS"] = "4"          # peers never publish
-    os.environ["TB_WAIT_TIMEOUT_MS"] = "150"
+    cfg.debug_flags, cfg.wait_timeout_ms = 4, 150     # peers never publish; waits give up after 150 ms
     try:
         tb.streamk_matmul_lt(a, b, c, sel, cfg, sk_grid=4)
         torch.cuda.synchronize()                # the launch itself completes: waits are bounded
     finally:
-        del os.environ["TB_DEBUG_FLAGS"]
-        del os.environ["TB_WAIT_TIMEOUT_MS"]
+        cfg.debug_flags, cfg.wait_timeout_ms = 0, 0
     code = tb.device_status()
     assert code == 105, code                    # stream-K owner timed out waiting for a peer's partial tile
     assert tb.device_status() == 0              # reading clears it
     with pytest.raises(tb.TritonBlasError, match="device-side failure"):
-        os.environ["TB_DEBUG_FLAGS"] = "4"
-        os.environ["TB_WAIT_TIMEOUT_MS"] = "150"
+        cfg.debug_flags, cfg.wait_timeout_ms = 4, 150
         try:
             tb.streamk_matmul_lt(a, b, c, sel, cfg, sk_grid=4)
         finally:
-            del os.environ["TB_DEBUG_FLAGS"]
-            del os.environ["TB_WAIT_TIMEOUT_MS"]
+            cfg.debug_flags, cfg.wait_timeout_ms = 0, 0
         tb.raise_on_device_failure()
     # the same workspace and context keep working
     tb.streamk_matmul_lt(a, b, c, sel, cfg, sk_grid=4)

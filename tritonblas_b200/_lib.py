@@ -54,6 +54,7 @@ class GemmArgs(ctypes.Structure):
         ("group_offsets", ctypes.c_void_p), ("num_groups", ctypes.c_int32),
         ("c_copies", ctypes.POINTER(ctypes.c_void_p)), ("num_c_copies", ctypes.c_int32),
         ("tile_counter", ctypes.c_void_p), ("epilogue_op", ctypes.c_int32),
+        ("wait_timeout_ms", ctypes.c_int32), ("debug_flags", ctypes.c_int32),
     ]
 
 
@@ -101,7 +102,7 @@ def _load():
     lib.tb_moe_dispatch_peers.restype = ctypes.c_int
     lib.tb_moe_combine_peers.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p,
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
-                                         ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+                                         ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p]
     lib.tb_moe_combine_peers.restype = ctypes.c_int
     lib.tb_gemm_mxfp4.argtypes = [ctypes.POINTER(Mxfp4Args), ctypes.c_void_p]
     lib.tb_gemm_mxfp4.restype = ctypes.c_int

@@ -19,6 +19,7 @@ import torch
 
 import tritonblas_b200 as tb
 from tritonblas_b200 import utils
+from tritonblas_b200.bench import do_bench
 
 _DTYPES = {"fp16": torch.float16, "float16": torch.float16, "bf16": torch.bfloat16, "bfloat16": torch.bfloat16,
            "fp32": torch.float32, "float32": torch.float32, "fp8": torch.float8_e4m3fn, "fp8e4m3": torch.float8_e4m3fn,
@@ -34,34 +35,6 @@ def str_to_dtype(name):
     if key not in _DTYPES:
         raise ValueError(f"unknown dtype {name!r}")
     return _DTYPES[key]
-
-
-_flush_buffer = {}
-
-
-def do_bench(fn, reset_fn=None, n_warmup=20, n_repeat=100, flush_l2=True):
-    """Median milliseconds of ``fn`` over ``n_repeat`` launches, each timed by its own pair of CUDA events."""
-    dev = torch.cuda.current_device()
-    if flush_l2 and dev not in _flush_buffer:
-        _flush_buffer[dev] = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")  # 2 x the 126 MB L2
-    for _ in range(n_warmup):
-        if reset_fn is not None:
-            reset_fn()
-        fn()
-    torch.cuda.synchronize()
-    times = []
-    for _ in range(n_repeat):
-        if reset_fn is not None:
-            reset_fn()
-        if flush_l2:
-            _flush_buffer[dev].zero_()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        fn()
-        stop.record()
-        stop.synchronize()
-        times.append(start.elapsed_time(stop))
-    return statistics.median(times)
 
 
 def bench_case(case, init_type="randn", enable_streamk=False, work_stealing=False, active_cus=None, check=False,
@@ -80,7 +53,7 @@ def bench_case(case, init_type="randn", enable_streamk=False, work_stealing=Fals
     else:
         def launch():
             tb.matmul_lt(inputs.A, inputs.B, inputs.C, selector, cfg, enable_streamk, work_stealing=work_stealing)
-    ms = do_bench(launch, n_warmup=n_warmup, n_repeat=n_repeat)
+    ms = do_bench(launch, n_warmup=n_warmup, n_repeat=n_repeat, return_mode="median")
     tb.raise_on_device_failure()
     if check:
         a32, b32 = inputs.A.float(), inputs.B.float()

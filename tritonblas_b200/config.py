@@ -30,6 +30,10 @@ class MatmulConfig:
         self.mask = mask
         self.sk_iter_counter = torch.zeros(COUNTER_STRIDE, device=device, dtype=torch.int32)
         self.sk_locks = self.sk_done = self.sk_P = None
+        # Launches made with this config: bound of every device-side wait in milliseconds (0 = the library's 2 s) and the
+        # library's measurement / test switches (tb_gemm_args.debug_flags; 0 in production).
+        self.wait_timeout_ms = 0
+        self.debug_flags = 0
 
     def next_epoch(self):
         self.epoch = (self.epoch % 0xFFFFFFF0) + 1

@@ -10,7 +10,7 @@
 
 #include "../../include/tritonblas_b200.h"
 #include "common_host.h"
-#include "gemm_sm100.cuh"
+#include "gemm_launch.cuh"
 #include "selector.h"
 
 namespace tb {
@@ -32,11 +32,31 @@ struct DeviceState {
   bool ready = false;
   int num_sms = 0;
   int smem_optin = 0;
-  int* status = nullptr;  // device word kernels write a failure code into
+  int* status = nullptr;  // device address of g_status_word on this device
 };
 static DeviceState g_dev[64];
-static std::mutex g_mu;
+static std::mutex g_mu;  // guards g_dev and g_encode
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+// The word kernels write a failure code into. Part of the library image (one instance per GPU that loads it), so the
+// library never calls an allocator; its device address is looked up once per device.
+static __device__ int g_status_word;
+
+// Makes `device` current for the lifetime of the object and puts the caller's device back on every exit path.
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t err = cudaSuccess;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    if (prev != device) {
+      err = cudaSetDevice(device);
+      switched = err == cudaSuccess;
+    }
+  }
+  ~DeviceGuard() {
+    if (switched && prev >= 0) cudaSetDevice(prev);
+  }
+};
 
 int device_state(int device, DeviceState** out) {
   if (device < 0 || device >= 64) return TB_ERR_INVALID;
@@ -49,13 +69,14 @@ int device_state(int device, DeviceState** out) {
       cudaGetLastError();
       return TB_ERR_NO_DEVICE;
     }
-    int cur = 0;
-    cudaGetDevice(&cur);
-    if ((e = cudaSetDevice(device)) != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err, "cudaSetDevice");
     cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, device);
     cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
-    if ((e = cudaMalloc(&d.status, 256)) != cudaSuccess) return cuda_fail(e, "cudaMalloc(status)");
-    if ((e = cudaMemset(d.status, 0, 256)) != cudaSuccess) return cuda_fail(e, "cudaMemset(status)");
+    // In host code the symbol's name is not a device address: ask for it, with this device current.
+    void* word = nullptr;
+    if ((e = cudaGetSymbolAddress(&word, g_status_word)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status)");
+    d.status = static_cast<int*>(word);
     if (g_encode == nullptr) {
       void* fn = nullptr;
       cudaDriverEntryPointQueryResult qres;
@@ -63,7 +84,6 @@ int device_state(int device, DeviceState** out) {
       if (e != cudaSuccess || fn == nullptr) return cuda_fail(e, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
       g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
     }
-    cudaSetDevice(cur);
     d.ready = true;
   }
   *out = &d;
@@ -166,63 +186,52 @@ MachineModel machine_for(const DeviceState* d) {
     hw.num_sms = d->num_sms;
     hw.smem_optin = d->smem_optin;
   }
-  const char* env = getenv("TB_DISABLE_CTA_PAIR");
-  if (env != nullptr && env[0] == '1') hw.allow_pair = false;
+  // measurement knob, read once: TB_DISABLE_CTA_PAIR=1 keeps the model to single-CTA tiles
+  static const bool no_pair = getenv("TB_DISABLE_CTA_PAIR") != nullptr && getenv("TB_DISABLE_CTA_PAIR")[0] == '1';
+  if (no_pair) hw.allow_pair = false;
   return hw;
 }
 
-template <int KIND, int CTAS>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const GemmParams& p, int programs, int smem_bytes,
-                       cudaStream_t stream, const CUtensorMap* tsfa = nullptr, const CUtensorMap* tsfb = nullptr) {
-  auto kernel = gemm_kernel<KIND, CTAS, false>;
-  // The instantiation with per-role cycle counters exists for 16-bit operands only (measurement runs).
-  if constexpr (KIND == 0) {
-    if ((p.debug_flags & 2) && p.debug_out != nullptr) kernel = gemm_kernel<KIND, CTAS, true>;
+bool pdl_enabled() {
+  static const bool on = getenv("TB_PDL") == nullptr || atoi(getenv("TB_PDL")) != 0;
+  return on;
+}
+
+// ---------------------------------------------------------------- built-in stream-K scratch (tb_gemm_streamk_builtin)
+// Flags (4 KB) followed by the fp32 partial tiles, in a device array that is part of the library image: every GPU that
+// loads the library holds these bytes until the process exits. In host code the array's name only stands for the
+// symbol; the address a kernel can use is asked for once per device, with that device current.
+constexpr size_t kBuiltinFlagBytes = 4096;
+constexpr size_t kBuiltinPartialBytes = 10u * 1024u * 1024u;
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinFlagBytes + kBuiltinPartialBytes];
+static unsigned char* g_builtin_addr[64] = {};
+static std::mutex g_builtin_mu;
+
+static int builtin_scratch(unsigned char** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return TB_ERR_NO_DEVICE;
   }
-  // The opt-in shared-memory size is set once per kernel instantiation and device (and again if a launch needs more).
-  static int configured[2][64] = {};
-  int dev_index = 0;
-  cudaGetDevice(&dev_index);
-  int& have = configured[kernel == gemm_kernel<KIND, CTAS, false> ? 0 : 1][dev_index & 63];
-  cudaError_t e = cudaSuccess;
-  if (smem_bytes > have) {
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
-    have = smem_bytes;
+  if (dev < 0 || dev >= 64) return TB_ERR_INVALID;
+  std::lock_guard<std::mutex> lk(g_builtin_mu);
+  if (g_builtin_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if ((e = cudaGetSymbolAddress(&p, g_builtin_scratch)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(scratch)");
+    g_builtin_addr[dev] = static_cast<unsigned char*>(p);
   }
-  cudaLaunchConfig_t lc = {};
-  lc.gridDim = dim3(static_cast<unsigned>(programs * CTAS), 1, 1);
-  lc.blockDim = dim3(gemm_threads<KIND>(), 1, 1);
-  lc.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
-  lc.stream = stream;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = CTAS;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  lc.attrs = attr;
-  lc.numAttrs = 1;
-  // Programmatic dependent launch: this kernel's CTAs may be scheduled, and run their shared-memory prologue, while the
-  // previous kernel of the stream drains; they wait for it (griddepcontrol.wait) before they touch global memory.
-  // (TB_PDL=0 in the environment turns it off.) Measured: 2 us off an 85 us decode GEMM, 5 us off back-to-back small GEMMs.
-  static const bool pdl = getenv("TB_PDL") == nullptr || atoi(getenv("TB_PDL")) != 0;
-  if (pdl) {
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    lc.numAttrs = 2;
-  }
-  // Kinds without block scales never touch the scale maps; they get copies of the operand maps as placeholders.
-  e = cudaLaunchKernelEx(&lc, kernel, ta, tb_, tsfa != nullptr ? *tsfa : ta, tsfb != nullptr ? *tsfb : tb_, p);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemm)");
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  *out = g_builtin_addr[dev];
   return TB_OK;
 }
 
 int gemm_fp32_exact(const tb_gemm_args& a, cudaStream_t stream);                 // simt_gemm.cu
 int gemm_generic_loader(const tb_gemm_args& a, const tb_config& cfg, cudaStream_t stream, int* status);  // unaligned operands
 
+// `builtin`: the stream-K flags and partial tiles of this launch live in the library's own scratch array (the launch
+// takes no workspace from the caller).
 static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaStream_t stream, bool grouped = false,
-                     bool swapped = false) {
+                     bool swapped = false, bool builtin = false) {
   const tb_gemm_args& a = a_in;
   if (a.m < 0 || a.n < 0 || a.k < 0) return TB_ERR_INVALID;
   if (grouped && (a.group_offsets == nullptr || a.num_groups <= 0 || a.num_groups > 4096 || a.streamk)) return TB_ERR_INVALID;
@@ -279,7 +288,7 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
     t.a_scale = a.b_scale; t.b_scale = a.a_scale;
     tb_config c2 = cfg;
     c2.swap_ab = 0;
-    rc = gemm_impl(t, &c2, stream, false, true);
+    rc = gemm_impl(t, &c2, stream, false, true, builtin);
     // Operands TMA cannot address go to the CUDA-core kernel in their original orientation (its bias is per column).
     if (rc == TB_ERR_ALIGNMENT) return gemm_generic_loader(a, cfg, stream, dev->status);
     return rc;
@@ -352,11 +361,8 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
   p.bias_along_m = swapped ? 1 : 0;
   p.status = dev->status;
-  p.timeout_ns = 2000000000ull;
-  {
-    const char* tmo = getenv("TB_WAIT_TIMEOUT_MS");  // bound of every device-side wait (default 2 s)
-    if (tmo != nullptr && atoi(tmo) > 0) p.timeout_ns = static_cast<unsigned long long>(atoi(tmo)) * 1000000ull;
-  }
+  // bound of every device-side wait: 2 s unless the caller asks for another one
+  p.timeout_ns = a.wait_timeout_ms > 0 ? static_cast<unsigned long long>(a.wait_timeout_ms) * 1000000ull : 2000000000ull;
   if (grouped) {
     p.group_offsets = a.group_offsets;
     p.num_groups = a.num_groups;
@@ -366,8 +372,7 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
     p.tile_counter = static_cast<unsigned*>(a.tile_counter);
   }
   {
-    const char* dbg = getenv("TB_DEBUG_FLAGS");
-    p.debug_flags = dbg != nullptr ? atoi(dbg) : 0;
+    p.debug_flags = a.debug_flags;
     // role cycle counters (148 x 16 words): the start of the workspace for data-parallel launches, its last 19 KB for
     // stream-K launches whose caller over-allocated by that much
     constexpr long long kDebugBytes = 148 * 16 * 8;
@@ -412,7 +417,26 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
     if (programs > total_iters) programs = static_cast<int>(total_iters);
     p.sk_tiles = static_cast<int>(tiles % programs);
     p.dp_tiles = static_cast<int>(tiles - p.sk_tiles);
-    if (p.sk_tiles > 0) {
+    if (p.sk_tiles > 0 && builtin) {
+      // one fp32 partial tile of 128 x block_n per CTA; launches without a split tile need none and are never refused
+      const size_t need = static_cast<size_t>(programs) * pair * 128 * static_cast<size_t>(bn) * 4;
+      if (need > kBuiltinPartialBytes || static_cast<size_t>(programs) * pair * 4 > kBuiltinFlagBytes) {
+        snprintf(g_cuda_err, sizeof(g_cuda_err),
+                 "built-in stream-K scratch holds %zu bytes of partial tiles, this launch needs %zu (%d programs x %d x 128 x %d "
+                 "fp32); pass a smaller sk_grid or use tb_gemm with a caller workspace",
+                 kBuiltinPartialBytes, need, programs, pair, bn);
+        return TB_ERR_WORKSPACE;
+      }
+      unsigned char* scratch = nullptr;
+      if ((rc = builtin_scratch(&scratch)) != TB_OK) return rc;
+      p.flags = reinterpret_cast<unsigned*>(scratch);
+      p.partials = reinterpret_cast<float*>(scratch + kBuiltinFlagBytes);
+      p.epoch = 1;
+      // The array keeps the previous call's contents: the flags must start at zero (partial tiles are written before
+      // they are read).
+      cudaError_t me = cudaMemsetAsync(scratch, 0, kBuiltinFlagBytes, stream);
+      if (me != cudaSuccess) return cuda_fail(me, "cudaMemsetAsync(flags)");
+    } else if (p.sk_tiles > 0) {
       const int64_t need = tb_gemm_workspace_bytes(&cfg, programs);
       if (a.workspace == nullptr || a.workspace_bytes < need) return TB_ERR_WORKSPACE;
       if (a.epoch == 0) return TB_ERR_INVALID;
@@ -439,7 +463,7 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   const void* B = a.b;
   // swizzle: 1 = 128-byte rows of 16-byte chunks; 2 = 128-byte rows of 32-byte chunks (MN-major 32-bit operands)
   const int mn_swz = es == 4 ? 2 : 1;
-  const bool no_mn3d = getenv("TB_DISABLE_MN3D") != nullptr;  // A/B measurements
+  static const bool no_mn3d = getenv("TB_DISABLE_MN3D") != nullptr;  // measurement knob, read once
   if (!a_mn) {
     rc = encode_2d(&ta, a.a_dtype, A, a.k, a.m, static_cast<uint64_t>(a.a_stride_m) * es, bk, 128, 1);
   } else {
@@ -557,169 +581,34 @@ static int gemm_mxfp4_impl(const tb_mxfp4_args& a, cudaStream_t stream) {
   return launch_gemm<3, 2>(ta, tbm, p, programs, smem_bytes, stream, &tsfa, &tsfb);
 }
 
-// ---------------------------------------------------------------- stream-K GEMM on built-in scratch (allocates nothing)
-// Flags (4 KB) followed by the fp32 partial tiles, in a device array that is part of the library image: every GPU that
-// loads the library holds these bytes until the process exits.
-constexpr size_t kBuiltinFlagBytes = 4096;
-constexpr size_t kBuiltinPartialBytes = 10u * 1024u * 1024u;
-static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinFlagBytes + kBuiltinPartialBytes];
-static __device__ int g_builtin_status;
-
-struct BuiltinState {
-  bool ready = false;
-  unsigned char* scratch = nullptr;  // device address of g_builtin_scratch on this device
-  int* status = nullptr;             // device address of g_builtin_status on this device
-  int num_sms = 0;
-  int smem_optin = 0;
-};
-static BuiltinState g_builtin[64];
-static std::mutex g_builtin_mu;
-
-// Once per device, with that device current. In host code the array's name only stands for the symbol; the address a
-// kernel can use has to be asked for.
-static int builtin_state(BuiltinState** out) {
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    return TB_ERR_NO_DEVICE;
-  }
-  if (dev < 0 || dev >= 64) return TB_ERR_INVALID;
-  std::lock_guard<std::mutex> lk(g_builtin_mu);
-  BuiltinState& st = g_builtin[dev];
-  if (!st.ready) {
-    void* p = nullptr;
-    if ((e = cudaGetSymbolAddress(&p, g_builtin_scratch)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(scratch)");
-    st.scratch = static_cast<unsigned char*>(p);
-    if ((e = cudaGetSymbolAddress(&p, g_builtin_status)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status)");
-    st.status = static_cast<int*>(p);
-    cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaDeviceGetAttribute(&st.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-    if (g_encode == nullptr) {
-      void* fn = nullptr;
-      cudaDriverEntryPointQueryResult qres;
-      e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
-      if (e != cudaSuccess || fn == nullptr) return cuda_fail(e, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
-      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
-    }
-    st.ready = true;
-  }
-  *out = &st;
-  return TB_OK;
-}
-
+// Stream-K launch on the built-in scratch: the regular launch path with the library's own flags and partial tiles.
 static int gemm_streamk_builtin_impl(const tb_gemm_args& in, const tb_config* user_cfg, cudaStream_t stream,
                                      int32_t* prev_status) {
   if (in.m <= 0 || in.n <= 0 || in.k <= 0) return TB_ERR_INVALID;
   if (in.a == nullptr || in.b == nullptr || in.c == nullptr) return TB_ERR_INVALID;
-  if (in.a_dtype != in.b_dtype) return TB_ERR_UNSUPPORTED;
-  if (in.a_dtype != TB_DTYPE_F16 && in.a_dtype != TB_DTYPE_BF16 && in.a_dtype != TB_DTYPE_E4M3) return TB_ERR_UNSUPPORTED;
-  if (in.c_dtype != TB_DTYPE_F16 && in.c_dtype != TB_DTYPE_BF16 && in.c_dtype != TB_DTYPE_F32) return TB_ERR_UNSUPPORTED;
-  // K-contiguous operands only (the layout decode weights are kept in)
-  if ((in.a_stride_k != 1 && in.k != 1) || (in.b_stride_k != 1 && in.k != 1)) return TB_ERR_UNSUPPORTED;
-  BuiltinState* st = nullptr;
-  int rc = builtin_state(&st);
+  // what the regular entry point would route elsewhere or fan out is not offered here
+  if (in.epilogue_op != TB_EPILOGUE_NONE || in.group_offsets != nullptr || in.num_groups != 0 || in.num_c_copies != 0)
+    return TB_ERR_UNSUPPORTED;
+  DeviceState* dev = nullptr;
+  int device = 0;
+  int rc = current_device_state(&dev, &device);
   if (rc != TB_OK) return rc;
   if (prev_status != nullptr) {
     // Outcome of the work enqueued before this call (waits for `stream`), then cleared.
     int v = 0;
     cudaError_t e = cudaStreamSynchronize(stream);
-    if (e == cudaSuccess) e = cudaMemcpy(&v, st->status, sizeof(int), cudaMemcpyDeviceToHost);
-    if (e == cudaSuccess && v != 0) e = cudaMemset(st->status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpy(&v, dev->status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && v != 0) e = cudaMemset(dev->status, 0, sizeof(int));
     if (e != cudaSuccess) return cuda_fail(e, "tb_gemm_streamk_builtin(status read)");
     *prev_status = v;
   }
-  const int es = in.a_dtype == TB_DTYPE_E4M3 ? 1 : 2;
-  MachineModel hw;
-  hw.num_sms = st->num_sms;
-  hw.smem_optin = st->smem_optin;
-  tb_config cfg;
-  if (user_cfg != nullptr) {
-    cfg = *user_cfg;
-  } else {
-    tb_problem pr = {};
-    pr.m = in.m; pr.n = in.n; pr.k = in.k;
-    pr.a_dtype = in.a_dtype; pr.b_dtype = in.b_dtype; pr.c_dtype = in.c_dtype;
-    pr.streamk = 1;
-    rc = select_config(pr, hw, &cfg);
-    if (rc != TB_OK) return rc;
-  }
   tb_gemm_args a = in;
-  const bool swapped = cfg.swap_ab != 0;
-  if (swapped) {  // C^T = B^T A^T, as in the regular entry point
-    a.m = in.n; a.n = in.m;
-    a.a = in.b; a.a_stride_m = in.b_stride_n; a.a_stride_k = in.b_stride_k;
-    a.b = in.a; a.b_stride_k = in.a_stride_k; a.b_stride_n = in.a_stride_m;
-    a.c_stride_m = in.c_stride_n; a.c_stride_n = in.c_stride_m;
-    a.a_scale = in.b_scale; a.b_scale = in.a_scale;
-  }
-  const int pair = cfg.cta_pair == 2 ? 2 : 1;
-  const int bn = cfg.block_n;
-  if (bn < 32 || bn > 256 || (bn % 32) != 0 || ((bn / pair) % 16) != 0 || cfg.block_m != 128 * pair) return TB_ERR_INVALID;
-  const int bk = 128 / es;
-  int stages = cfg.stages < 2 ? 2 : cfg.stages;
-  while (stages > 2 && smem_bytes_for(bn, pair, stages) > st->smem_optin) --stages;
-  const int smem_bytes = smem_bytes_for(bn, pair, stages);
-  if (smem_bytes > st->smem_optin) return TB_ERR_INVALID;
-
-  GemmParams p = {};
-  p.M = a.m; p.N = a.n; p.K = a.k;
-  p.block_n = bn;
-  p.n_halves = 1;
-  p.k_per_stage = bk;
-  p.num_k_blocks = (a.k + bk - 1) / bk;
-  p.tiles_m = (a.m + 128 * pair - 1) / (128 * pair);
-  p.tiles_n = (a.n + bn - 1) / bn;
-  p.group_m = cfg.group_m > 0 ? cfg.group_m : 8;
-  p.stages = stages;
-  p.esize = es;
-  int tc = 32;
-  while (tc < 2 * bn) tc <<= 1;
-  p.tmem_cols = static_cast<uint32_t>(tc);
-  p.C = a.c; p.ldc_m = a.c_stride_m; p.ldc_n = a.c_stride_n; p.c_dtype = a.c_dtype;
-  p.a_scale = a.a_scale; p.b_scale = a.b_scale;
-  p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
-  p.bias_along_m = swapped ? 1 : 0;
-  p.staged_store = ((a.c_dtype == TB_DTYPE_BF16 || a.c_dtype == TB_DTYPE_F16) && a.c_stride_n == 1 &&
-                    ((a.c_stride_m * 2) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.c) & 15) == 0) ? 1 : 0;
-  p.status = st->status;
-  p.timeout_ns = 2000000000ull;
-  const uint32_t fmt = in.a_dtype == TB_DTYPE_BF16 ? 1u : 0u;  // f16 = 0, bf16 = 1, e4m3 = 0
-  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
-            (static_cast<uint32_t>((128 * pair) >> 4) << 24);
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
-  const int max_programs = st->num_sms / pair;
-  int programs = in.sk_grid > 0 ? in.sk_grid : cfg.sk_grid;
-  if (programs <= 0 || programs > max_programs) programs = max_programs;
-  if (programs > tiles * p.num_k_blocks) programs = static_cast<int>(tiles * p.num_k_blocks);
-  if (programs < 1) programs = 1;
-  p.sk_tiles = static_cast<int>(tiles % programs);
-  p.dp_tiles = static_cast<int>(tiles - p.sk_tiles);
-  const size_t need = static_cast<size_t>(programs) * pair * 128 * static_cast<size_t>(bn) * 4;
-  if (need > kBuiltinPartialBytes) {
-    snprintf(g_cuda_err, sizeof(g_cuda_err),
-             "built-in stream-K scratch holds %zu bytes of partial tiles, this launch needs %zu (%d programs x %d x 128 x %d "
-             "fp32); pass a smaller sk_grid or use tb_gemm with a caller workspace",
-             kBuiltinPartialBytes, need, programs, pair, bn);
-    return TB_ERR_WORKSPACE;
-  }
-  p.flags = reinterpret_cast<unsigned*>(st->scratch);
-  p.partials = reinterpret_cast<float*>(st->scratch + kBuiltinFlagBytes);
-  p.epoch = 1;
-  // The array keeps the previous call's contents: the flags must start at zero (the partial tiles are overwritten
-  // before they are read).
-  cudaError_t e = cudaMemsetAsync(st->scratch, 0, kBuiltinFlagBytes, stream);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(flags)");
-
-  CUtensorMap ta, tbm;
-  rc = encode_2d(&ta, a.a_dtype, a.a, a.k, a.m, static_cast<uint64_t>(a.a_stride_m) * es, bk, 128, 1);
-  if (rc == TB_OK) rc = encode_2d(&tbm, a.b_dtype, a.b, a.k, a.n, static_cast<uint64_t>(a.b_stride_n) * es, bk, bn / pair, 1);
-  if (rc != TB_OK) return rc;
-  const int kind = in.a_dtype == TB_DTYPE_E4M3 ? 2 : 0;
-  if (pair == 1) return kind == 0 ? launch_gemm<0, 1>(ta, tbm, p, programs, smem_bytes, stream)
-                                  : launch_gemm<2, 1>(ta, tbm, p, programs, smem_bytes, stream);
-  return kind == 0 ? launch_gemm<0, 2>(ta, tbm, p, programs, smem_bytes, stream)
-                   : launch_gemm<2, 2>(ta, tbm, p, programs, smem_bytes, stream);
+  a.streamk = 1;
+  a.workspace = nullptr;
+  a.workspace_bytes = 0;
+  a.epoch = 0;
+  a.tile_counter = nullptr;
+  return gemm_impl(a, user_cfg, stream, false, false, true);
 }
 
 }  // namespace tb
@@ -767,14 +656,12 @@ int tb_device_status(int32_t device, int32_t* status_out) {
   tb::DeviceState* d = nullptr;
   int rc = tb::device_state(device, &d);
   if (rc != TB_OK) return rc;
-  int cur = 0;
-  cudaGetDevice(&cur);
-  cudaSetDevice(device);
+  tb::DeviceGuard guard(device);
+  if (guard.err != cudaSuccess) return tb::cuda_fail(guard.err, "cudaSetDevice");
   int v = 0;
   cudaError_t e = cudaDeviceSynchronize();
   if (e == cudaSuccess) e = cudaMemcpy(&v, d->status, sizeof(int), cudaMemcpyDeviceToHost);
   if (e == cudaSuccess && v != 0) e = cudaMemset(d->status, 0, sizeof(int));
-  cudaSetDevice(cur);
   if (e != cudaSuccess) return tb::cuda_fail(e, "tb_device_status");
   if (status_out) *status_out = v;
   return TB_OK;
@@ -805,6 +692,7 @@ const char* tb_status_string(int code) {
     case tb::TB_DEV_TIMEOUT_PEER_FLAG: return "device: stream-K owner timed out waiting for a peer's partial tile";
     case tb::TB_DEV_TIMEOUT_SCALE: return "device: timed out waiting for block scales";
     case tb::TB_DEV_TIMEOUT_STORE: return "device: timed out publishing a partial tile";
+    case tb::TB_DEV_TIMEOUT_TILE_QUEUE: return "device: a role timed out waiting for the next tile of the dynamic schedule";
     default: return "unknown status";
   }
 }

@@ -10,7 +10,10 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB = os.path.join(PKG, "libtritonblas_b200.so")
-SOURCES = ["api.cu", "simt_gemm.cu", "quant_mxfp4.cu", "quant_fp8.cu", "moe_ops.cu", "selector.cpp"]
+# the gemm_inst_* files hold the kernel instantiations (one MMA kind each) and dominate the build: they go first so that
+# the parallel compile below starts them before the small files
+SOURCES = ["gemm_inst_f16.cu", "gemm_inst_f8.cu", "gemm_inst_mxf4.cu", "gemm_inst_tf32.cu", "gemm_inst_i8.cu", "api.cu",
+           "simt_gemm.cu", "quant_mxfp4.cu", "quant_fp8.cu", "moe_ops.cu", "selector.cpp"]
 HEADERS_DIRS = [HERE, os.path.join(os.path.dirname(PKG), "include")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -47,15 +50,19 @@ def build(force=False, verbose=False):
     """Compile every source into one shared library; returns its path."""
     if not force and not needs_build():
         return LIB
-    objs = []
-    for src in SOURCES:
+    from concurrent.futures import ThreadPoolExecutor
+
+    def compile_one(src):
         obj = os.path.join(HERE, os.path.splitext(src)[0] + ".o")
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(HERE, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
-        objs.append(obj)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(compile_one, SOURCES))
     cmd = [_nvcc(), "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     if verbose:
         print(" ".join(cmd), flush=True)

@@ -560,14 +560,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     griddep_launch_dependents();
     griddep_wait();
     if (p.group_offsets != nullptr) {
-      // tile_prefix[0 .. G] = tiles before each group, followed by a copy of the G + 1 row offsets
+      // tile_prefix[0 .. G] = tiles before each group, followed by a copy of the G + 1 row offsets. The copy is clamped to
+      // [0, M] and made non-decreasing: offsets that describe more rows than A and C hold (a receive buffer sized below
+      // the worst case) then lose their tail instead of sending loads and stores past the end of the buffers.
       int acc_tiles = 0;
       int* offs = tile_prefix + p.num_groups + 1;
       tile_prefix[0] = 0;
-      int row0 = p.group_offsets[0];
+      int row0 = min(max(p.group_offsets[0], 0), p.M);
       offs[0] = row0;
       for (int g = 0; g < p.num_groups; ++g) {
-        const int row1 = p.group_offsets[g + 1];
+        const int row1 = min(max(p.group_offsets[g + 1], row0), p.M);
         offs[g + 1] = row1;
         acc_tiles += ((row1 - row0 + kTileM * CTAS - 1) / (kTileM * CTAS)) * p.tiles_n;
         tile_prefix[g + 1] = acc_tiles;

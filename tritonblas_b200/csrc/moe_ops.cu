@@ -201,7 +201,8 @@ __global__ void __launch_bounds__(256) combine_peers_kernel(PeerPtrs y_peers, lo
                                                               const int* __restrict__ pair_rank,
                                                               const long long* __restrict__ pair_row,
                                                               const float* __restrict__ w, T* __restrict__ out,
-                                                              long long out_stride, int tokens, int topk, int hidden) {
+                                                              long long out_stride, int tokens, int topk, int hidden,
+                                                              long long capacity_rows) {
   const int vec_per_row = hidden / 8;
   const long long total = static_cast<long long>(tokens) * vec_per_row;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -211,10 +212,13 @@ __global__ void __launch_bounds__(256) combine_peers_kernel(PeerPtrs y_peers, lo
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int k = 0; k < topk; ++k) {
       const long long f = static_cast<long long>(t) * topk + k;
+      const long long prow = pair_row[f];
+      // a pair whose row the dispatch dropped (beyond the owner's capacity) contributes nothing
+      if (prow < 0 || prow >= capacity_rows) continue;
       const T* y = static_cast<const T*>(y_peers.p[pair_rank[f]]);
       const float wk = w[f];
       float v[8];
-      Vec8<T>::load(y + pair_row[f] * y_stride + c, v);
+      Vec8<T>::load(y + prow * y_stride + c, v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = fmaf(v[j], wk, acc[j]);
     }
@@ -285,9 +289,10 @@ extern "C" int tb_moe_gather_rows(const void* x, int64_t x_row_stride, const int
 
 extern "C" int tb_moe_combine_peers(void* const* y_peers, int32_t num_peers, int64_t y_row_stride, const int32_t* pair_rank,
                                     const int64_t* pair_row, const float* weights, void* out, int64_t out_row_stride,
-                                    int32_t tokens, int32_t topk, int32_t hidden, int32_t dtype, void* stream) {
+                                    int32_t tokens, int32_t topk, int32_t hidden, int32_t dtype, int64_t capacity_rows,
+                                    void* stream) {
   if (y_peers == nullptr || pair_rank == nullptr || pair_row == nullptr || weights == nullptr || out == nullptr) return TB_ERR_INVALID;
-  if (num_peers < 1 || num_peers > 8 || tokens < 0 || topk <= 0 || hidden <= 0 || (hidden % 8) != 0) return TB_ERR_INVALID;
+  if (num_peers < 1 || num_peers > 8 || tokens < 0 || topk <= 0 || hidden <= 0 || (hidden % 8) != 0 || capacity_rows < 0) return TB_ERR_INVALID;
   if (tokens == 0) return TB_OK;
   if (((y_row_stride * 2) & 15) != 0 || !tb::aligned16(out, out_row_stride)) return TB_ERR_ALIGNMENT;
   tb::PeerPtrs peers = {};
@@ -300,11 +305,13 @@ extern "C" int tb_moe_combine_peers(void* const* y_peers, int32_t num_peers, int
   if (dtype == TB_DTYPE_BF16)
     tb::combine_peers_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(peers, y_row_stride, pair_rank,
                                                                  reinterpret_cast<const long long*>(pair_row), weights,
-                                                                 static_cast<__nv_bfloat16*>(out), out_row_stride, tokens, topk, hidden);
+                                                                 static_cast<__nv_bfloat16*>(out), out_row_stride, tokens, topk, hidden,
+                                                                 capacity_rows);
   else if (dtype == TB_DTYPE_F16)
     tb::combine_peers_kernel<__half><<<grid, 256, 0, st>>>(peers, y_row_stride, pair_rank,
                                                           reinterpret_cast<const long long*>(pair_row), weights,
-                                                          static_cast<__half*>(out), out_row_stride, tokens, topk, hidden);
+                                                          static_cast<__half*>(out), out_row_stride, tokens, topk, hidden,
+                                                          capacity_rows);
   else
     return TB_ERR_UNSUPPORTED;
   cudaError_t e = cudaGetLastError();

@@ -9,6 +9,8 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <type_traits>
+
 #include "common_host.h"
 
 namespace tb {
@@ -22,6 +24,7 @@ struct SimtParams {
   const void* A; long long a_sm, a_sk; int a_dtype;
   const void* B; long long b_sk, b_sn; int b_dtype;
   void* C; long long c_sm, c_sn; int c_dtype;
+  void* c_extra[7]; int num_c_extra;  // further destinations laid out like C (the tensor-core path's fan-out)
   const float* a_scale; const float* b_scale;
   const void* bias; long long bias_stride; int bias_dtype;
 };
@@ -59,17 +62,19 @@ __device__ __forceinline__ void st_elem(void* p, long long i, int dtype, float v
   }
 }
 
+// Acc = float, or int for 8-bit integer operands (exact int32 sums, as the tensor-core integer kind produces).
+template <typename Acc>
 __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
-  __shared__ float As[BK][BM + 4];
-  __shared__ float Bs[BK][BN + 4];
+  __shared__ Acc As[BK][BM + 4];
+  __shared__ Acc Bs[BK][BN + 4];
   const int tid = threadIdx.x;
   const int tx = tid % 16, ty = tid / 16;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  float acc[TM][TN];
+  Acc acc[TM][TN];
 #pragma unroll
   for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < TN; ++j) acc[i][j] = Acc(0);
 
   // Loader mapping follows the contiguous axis of each operand so global reads coalesce for either layout.
   const bool a_kc = (p.a_sk == 1);
@@ -81,7 +86,7 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
       const int kk = a_kc ? idx % BK : idx / BM;
       const int mm = a_kc ? idx / BK : idx % BM;
       const int gm = m0 + mm, gk = k0 + kk;
-      As[kk][mm] = (gm < p.M && gk < p.K) ? ld_elem(p.A, gm * p.a_sm + gk * p.a_sk, p.a_dtype) : 0.f;
+      As[kk][mm] = (gm < p.M && gk < p.K) ? static_cast<Acc>(ld_elem(p.A, gm * p.a_sm + gk * p.a_sk, p.a_dtype)) : Acc(0);
     }
 #pragma unroll
     for (int i = 0; i < (BN * BK) / 256; ++i) {
@@ -89,12 +94,12 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
       const int kk = b_nc ? idx / BN : idx % BK;
       const int nn = b_nc ? idx % BN : idx / BK;
       const int gn = n0 + nn, gk = k0 + kk;
-      Bs[kk][nn] = (gn < p.N && gk < p.K) ? ld_elem(p.B, gk * p.b_sk + gn * p.b_sn, p.b_dtype) : 0.f;
+      Bs[kk][nn] = (gn < p.N && gk < p.K) ? static_cast<Acc>(ld_elem(p.B, gk * p.b_sk + gn * p.b_sn, p.b_dtype)) : Acc(0);
     }
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
-      float a[TM], b[TN];
+      Acc a[TM], b[TN];
 #pragma unroll
       for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
 #pragma unroll
@@ -102,7 +107,10 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) {
+          if constexpr (std::is_same<Acc, float>::value) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          else acc[i][j] += a[i] * b[j];
+        }
     }
     __syncthreads();
   }
@@ -115,25 +123,32 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
     for (int j = 0; j < TN; ++j) {
       const int gn = n0 + tx * TN + j;
       if (gn >= p.N) continue;
-      float v = acc[i][j];
+      float v = static_cast<float>(acc[i][j]);
       if (p.a_scale) v *= as;
       if (p.b_scale) v *= p.b_scale[gn];
       if (p.bias) v += ld_elem(p.bias, gn * p.bias_stride, p.bias_dtype);
       st_elem(p.C, gm * p.c_sm + gn * p.c_sn, p.c_dtype, v);
+      for (int x = 0; x < p.num_c_extra; ++x) st_elem(p.c_extra[x], gm * p.c_sm + gn * p.c_sn, p.c_dtype, v);
     }
   }
 }
 
 int launch_simt(const tb_gemm_args& a, cudaStream_t stream) {
+  // The fused activation exists on the tensor-core path only; the output fan-out is honoured here as well.
+  if (a.epilogue_op != TB_EPILOGUE_NONE) return TB_ERR_UNSUPPORTED;
+  if (a.num_c_copies < 0 || a.num_c_copies > 7 || (a.num_c_copies > 0 && a.c_copies == nullptr)) return TB_ERR_INVALID;
   SimtParams p;
   p.M = a.m; p.N = a.n; p.K = a.k;
   p.A = a.a; p.a_sm = a.a_stride_m; p.a_sk = a.a_stride_k; p.a_dtype = a.a_dtype;
   p.B = a.b; p.b_sk = a.b_stride_k; p.b_sn = a.b_stride_n; p.b_dtype = a.b_dtype;
   p.C = a.c; p.c_sm = a.c_stride_m; p.c_sn = a.c_stride_n; p.c_dtype = a.c_dtype;
+  p.num_c_extra = a.num_c_copies;
+  for (int x = 0; x < 7; ++x) p.c_extra[x] = x < a.num_c_copies ? a.c_copies[x] : nullptr;
   p.a_scale = a.a_scale; p.b_scale = a.b_scale;
   p.bias = a.bias; p.bias_stride = a.bias_stride; p.bias_dtype = a.bias_dtype;
   dim3 grid((a.n + BN - 1) / BN, (a.m + BM - 1) / BM, 1);
-  simt_gemm_kernel<<<grid, 256, 0, stream>>>(p);
+  if (a.a_dtype == TB_DTYPE_I8 && a.b_dtype == TB_DTYPE_I8) simt_gemm_kernel<int><<<grid, 256, 0, stream>>>(p);
+  else simt_gemm_kernel<float><<<grid, 256, 0, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "simt_gemm_kernel launch");
   g_launches.fetch_add(1, std::memory_order_relaxed);

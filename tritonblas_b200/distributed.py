@@ -264,8 +264,13 @@ class PeerDispatchPlan:
     group_offsets: torch.Tensor  # int32 (experts_per_rank + 1,) row offsets of this rank's experts in its receive buffer
 
 
-def plan_peer_dispatch(topk_ids: torch.Tensor, counts_all: torch.Tensor, rank: int) -> PeerDispatchPlan:
+def plan_peer_dispatch(topk_ids: torch.Tensor, counts_all: torch.Tensor, rank: int,
+                       capacity: Optional[int] = None) -> PeerDispatchPlan:
     """Pure index arithmetic on the device (no host synchronisation).
+
+    ``capacity``: rows of every rank's receive buffer. Rows routed beyond it are dropped by the dispatch kernel (and
+    counted); the group offsets returned here are clamped to it, so the grouped GEMMs and the combine step never reach
+    past the buffers either.
 
     counts_all: int64 (world, num_experts), counts_all[r, e] = pairs of rank r routed to expert e (every rank holds the
     same matrix after an all-gather of its own bincount). Expert e lives on rank e // experts_per_rank; inside that
@@ -292,7 +297,10 @@ def plan_peer_dispatch(topk_ids: torch.Tensor, counts_all: torch.Tensor, rank: i
     pair_rank = torch.empty_like(dest_rank)
     pair_rank[sort_idx] = dest_rank
     group_offsets = torch.zeros(epr + 1, dtype=torch.int32, device=flat.device)
-    group_offsets[1:] = per_owner[rank].cumsum(0).to(torch.int32)
+    ends = per_owner[rank].cumsum(0)
+    if capacity is not None:
+        ends = ends.clamp(max=int(capacity))
+    group_offsets[1:] = ends.to(torch.int32)
     topk = topk_ids.shape[1]
     return PeerDispatchPlan(sort_idx // topk, dest_rank, dest_row, pair_rank, pair_row, group_offsets)
 
@@ -332,7 +340,7 @@ class PeerMemoryMoE:
         mine = torch.bincount(topk_ids.reshape(-1).to(torch.int64), minlength=self.num_experts)
         counts_all = torch.empty(self.world, self.num_experts, dtype=mine.dtype, device=mine.device)
         dist.all_gather_into_tensor(counts_all.view(-1), mine, group=self.group)
-        plan = plan_peer_dispatch(topk_ids, counts_all, self.rank)
+        plan = plan_peer_dispatch(topk_ids, counts_all, self.rank, self.capacity)
         stream = _lib.current_stream_ptr(x.device)
         code = _lib.DTYPE_CODE[x.dtype]
         x = x if x.stride(1) == 1 else x.contiguous()
@@ -355,6 +363,6 @@ class PeerMemoryMoE:
                                                ctypes.c_void_p(plan.pair_rank.data_ptr()),
                                                ctypes.c_void_p(plan.pair_row.data_ptr()), ctypes.c_void_p(w.data_ptr()),
                                                ctypes.c_void_p(out.data_ptr()), out.stride(0), tokens, topk, self.hidden,
-                                               code, stream)
+                                               code, self.capacity, stream)
         _lib.check(rc, "tb_moe_combine_peers")
         return out, plan

@@ -172,6 +172,8 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
         ptrs = (ctypes.c_void_p * len(c_copies))(*[int(p) for p in c_copies])
         args.c_copies, args.num_c_copies = ptrs, len(c_copies)
     args.allow_tf32 = int(torch.backends.cuda.matmul.allow_tf32)
+    if config is not None:
+        args.wait_timeout_ms, args.debug_flags = int(config.wait_timeout_ms), int(config.debug_flags)
     args.streamk = int(bool(streamk))
     args.sk_grid = int(sk_grid) if sk_grid else 0
     if work_stealing and not streamk:
