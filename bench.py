@@ -9,19 +9,32 @@ Prints ONE JSON line (rank 0):
   e2e          the same metric through the public API with HOST (pinned) operands: H2D of the inputs and D2H of the result
                inside the timed region, every step
   roofline     the dominant kernel against the measured cuBLAS bf16 throughput / HBM copy bandwidth (MEASURED_PEAKS.json)
+  parity_check a fixed sample of the result of one more step, on every rank, against the CPU oracle (outside the timed
+               region): rows x columns of C including columns every other rank computed
   cpu_baseline the reference semantics (fp32-accumulate torch.matmul) on the host cores, on a bounded sample
+With the default workload the line also carries (each measured after the headline, outside `value`):
+  moe / moe_nccl  the expert-parallel MoE step (64 experts, top-8 of 16384 tokens, hidden 4096, ffn 1536, Zipf routing) at
+               this GPU count: whole-job TFLOP/s, ms per step, rows per rank, its own parity_check. On several GPUs `moe`
+               exchanges tokens through peer-mapped memory, `moe_nccl` through NCCL all-to-all.
+  cublas_same_run, sustained, workloads   (1 GPU) torch.matmul on the same operands in the same run; a >= 1.5 s
+               back-to-back block with clocks; kernel-level roofline lines of the FP8, MXFP4, quantiser and decode shapes.
 With --gpus N > 1 (under torchrun) the default workload is N-sharded: rank r computes C[:, r*N/P:(r+1)*N/P] from the full A
-and its column block of B, then the ranks all-gather C over NCCL (total work fixed: "strong" scaling). `--workload moe`
-runs the expert-parallel MoE projections with NCCL all-to-all dispatch/combine instead.
+and its column block of B and the GEMM epilogue pushes every tile into all ranks' gathered C over NVLink (total work
+fixed: "strong" scaling); `--nccl-gather` gathers with NCCL instead. `--workload moe` runs only the MoE step.
 `--impl reference` times the reference's CPU implementation of the path (its matmul semantics via torch.matmul).
 """
 import argparse
+import gc
 import json
 import os
 import subprocess
 import sys
 import threading
 import time
+
+# A rank of a multi-GPU run must never be bound to an NVLink multicast object (a rank that dies while bound raises
+# faults on its peers); this library only uses ordinary peer loads and stores.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 import torch
 
@@ -46,6 +59,8 @@ WORKLOADS = {
     "mxfp4_quant": dict(M=8192, N=8192, K=8192, dtype="mxfp4", streamk=False, bound="hbm"),
     "moe": dict(M=16384 * 8, N=0, K=0, dtype="bf16", streamk=False, bound="tensor"),
 }
+# kernel-level lines added to the default 1-GPU run
+EXTRA_WORKLOADS = ["fp8_m4096", "mxfp4_8192", "mxfp4_quant", "bf16_skinny_m16", "bf16_skinny_m128", "fp8_m16"]
 TORCH_DTYPES = {"bf16": torch.bfloat16, "fp16": torch.float16}
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the workload's dominant kernel, from the ncu captures
 # summarised under profiles/ (same shapes; a capture is not repeated inside the bench)
@@ -170,6 +185,21 @@ def run_reference(args, wl, rank):
     print(json.dumps(line), flush=True)
 
 
+def _parity(got, ref, rtol):
+    """(ok, max error relative to rtol * (|ref| + rms)) of a sample against the oracle's fp32 values."""
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
+    rms = max(ref.pow(2).mean().sqrt().item(), 1e-30)
+    err = (got - ref).abs()
+    ok = bool(torch.isfinite(got).all()) and bool((err <= rtol * ref.abs() + rtol * rms).all())
+    return ok, float(err.max().item()), rms
+
+
+def _b_shard_host(rank, set_index, n_local, K):
+    """Rank `rank`'s block of B for operand set `set_index` (bf16, (n_local, K)): every rank can rebuild any block."""
+    g = torch.Generator().manual_seed(99 + rank + 7 * set_index)
+    return (torch.randn(n_local, K, generator=g) * 0.02).to(torch.bfloat16)
+
+
 # ------------------------------------------------------------------------------------------ workloads (our arm)
 class DenseWorkload:
     """bf16 / fp16 / fp8 GEMM, optionally N-sharded over the ranks with an all-gather of C."""
@@ -177,7 +207,7 @@ class DenseWorkload:
     def __init__(self, args, wl, dev, rank, world):
         import tritonblas_b200 as tb
         from tritonblas_b200 import utils
-        self.tb, self.wl, self.dev, self.world = tb, wl, dev, world
+        self.tb, self.wl, self.dev, self.world, self.rank = tb, wl, dev, world, rank
         M, N, K = wl["M"], wl["N"], wl["K"]
         self.M, self.K = M, K
         self.n_local = N // world
@@ -196,7 +226,7 @@ class DenseWorkload:
         self.A_host, self.B_host, self.a_s, self.b_s = [], [], [], []
         for i in range(nsets):
             a = (torch.randn(M, K, generator=g) * (1.0 if self.fp8 else 0.02)).to(torch.bfloat16)
-            b = (torch.randn(self.n_local, K, generator=torch.Generator().manual_seed(99 + rank + 7 * i)) * 0.02).to(torch.bfloat16)
+            b = _b_shard_host(rank, i, self.n_local, K)
             if self.fp8:
                 a8, a_s = utils.quantize_tensor_per_channel(a, FP8, axis=1)
                 b8, b_s = utils.quantize_tensor_per_channel(b, FP8, axis=1)   # rows of (N, K) = output channels
@@ -260,11 +290,17 @@ class DenseWorkload:
     def step(self, i, dist):
         if self.layers is not None:
             # two gathered buffers alternate, so the opening barrier is not needed (see forward_fused)
-            self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets], pre_barrier=self.nsets < 2)
-            return
+            return self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets], pre_barrier=self.nsets < 2)
         c = self.gemm(i)
         if self.world > 1:
             dist.all_gather_into_tensor(self.Cg, c)
+            return self.Cg.view(self.world, self.M, self.n_local)
+        return c
+
+    def cublas_step(self, i):
+        """torch.matmul (cuBLAS) on the same operands, for the same-run comparison; not part of `value`."""
+        s = i % self.nsets
+        torch.matmul(self.A[s], self.Bt[s].T, out=self.C[i % len(self.C)])
 
     def e2e_step(self, i, dist):
         """Host operands in, host result out, through the public API. H2D of step i+1 and D2H of step i-1 run on their own
@@ -281,11 +317,15 @@ class DenseWorkload:
         if self.ev_out[j] is not None:
             main.wait_event(self.ev_out[j])                 # the previous result in this buffer has left for the host
         c = self.c_dev[j]
-        if self.fp8:
+        if self.layers is not None:
+            # the same fused path as `value`: this rank's block goes to every rank's gathered buffer from the epilogue
+            gathered = self.layers[j].forward_fused(self.a_dev[j], pre_barrier=self.nsets < 2, b_shard_t=self.b_dev[j])
+            c = gathered[self.rank]
+        elif self.fp8:
             self.tb.matmul_a8w8(self.a_dev[j], self.b_dev[j].T, self.a_s[s], self.b_s[s], c, enable_streamk=self.streamk)
         else:
             self.tb.matmul(self.a_dev[j], self.b_dev[j].T, out=c, enable_streamk=self.streamk)
-        if self.world > 1:
+        if self.world > 1 and self.layers is None:
             dist.all_gather_into_tensor(self.Cg, c)
         self.ev_c[j] = main.record_event()
         with torch.cuda.stream(self.s_out):
@@ -298,6 +338,34 @@ class DenseWorkload:
         for ev in self.ev_out:
             if ev is not None:
                 main.wait_event(ev)
+
+    def parity_check(self, dist):
+        """One more step on operand set 0; 64 rows x 256 columns of the (gathered) C, the columns spread evenly over
+        every rank's block, against the CPU oracle."""
+        from oracle import gemm_oracle
+        out = self.step(0, dist)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        g = torch.Generator().manual_seed(2024)
+        rows = torch.unique(torch.cat([torch.randint(0, self.M, (60,), generator=g),
+                                       torch.tensor([0, min(127, self.M - 1), min(128, self.M - 1), self.M - 1])]))
+        per = max(256 // self.world, 8)
+        ok, worst = True, 0.0
+        for r in range(self.world):
+            cols = torch.unique(torch.cat([torch.randint(0, self.n_local, (per - 2,), generator=g),
+                                           torch.tensor([0, self.n_local - 1])]))
+            block = out[r] if self.world > 1 else out
+            got = block[rows.to(self.dev)][:, cols.to(self.dev)]
+            if self.fp8:      # single GPU only: the quantised operands and their scales are at hand
+                ref = gemm_oracle.gemm_ref_f32(self.A[0][rows.to(self.dev)], self.Bt[0][cols.to(self.dev)].T,
+                                               self.a_s[0][rows.to(self.dev)], self.b_s[0][cols.to(self.dev)])
+            else:
+                b_blk = _b_shard_host(r, 0, self.n_local, self.K).to(self.in_dtype)
+                ref = gemm_oracle.gemm_ref_f32(self.A_host[0][rows], b_blk[cols].T)
+            k, e, _ = _parity(got, ref, 1e-2)
+            ok, worst = ok and k, max(worst, e)
+        return ok, worst
 
 
 class Mxfp4Workload:
@@ -330,13 +398,13 @@ class Mxfp4Workload:
                           f"bf16 N(0,1); activations pre-quantised by the fused Hadamard+quantise kernel (timed apart in e2e)")
         self.h2d, self.d2h = M * K * 2, (M * K // 2 + M * K // 32 if quant_only else 2 * M * N)
         self.extra = {"parallelism": "single GPU"}
+        self.qout = utils.hadamard_mxfp4_quant(self.X[0], scale_atoms=True) if quant_only else None
 
     def step(self, i, dist):
         s = i % self.nsets
         if self.quant_only:
-            self.utils.hadamard_mxfp4_quant(self.X[s], scale_atoms=True)
-        else:
-            self.tb.matmul_fp4(self.q[s][0], self.qb, self.C, self.q[s][1], self.sb)
+            return self.utils.hadamard_mxfp4_quant(self.X[s], scale_atoms=True, out=self.qout)
+        return self.tb.matmul_fp4(self.q[s][0], self.qb, self.C, self.q[s][1], self.sb)
 
     def e2e_step(self, i, dist):
         x = self.X_host[i % self.nsets].to(self.dev, non_blocking=True)
@@ -347,14 +415,51 @@ class Mxfp4Workload:
         self.tb.matmul_fp4(qa, self.qb, self.C, sa, self.sb)
         self.C_host.copy_(self.C, non_blocking=True)
 
+    def parity_check(self, dist):
+        """Sampled rows: quantiser codes and scales bit-exact against the oracle; GEMM rows against the dequantised fp32
+        product (rtol 1e-2 + 1e-2 rms)."""
+        import numpy as np
+        from oracle import mxfp4_oracle
+        rows = [0, 1, 127, 128, 4095, self.M - 1] + torch.randint(0, self.M, (26,), generator=torch.Generator().manual_seed(3)).tolist()
+        idx = torch.tensor(rows, device=self.dev)
+        if self.quant_only:
+            qa, sa = self.utils.hadamard_mxfp4_quant(self.X[0][idx].contiguous())
+            ra = mxfp4_oracle.hadamard_quantize_mxfp4(self.X[0][idx].float().cpu().numpy())
+            ok = bool(np.array_equal(qa.cpu().numpy(), ra[0]) and np.array_equal(sa.cpu().numpy(), ra[1]))
+            return ok, 0.0 if ok else 1.0
+        qa, sa = self.utils.hadamard_mxfp4_quant(self.X[0][idx].contiguous())
+        qb, sb = self.utils.hadamard_mxfp4_quant(self._weights_again())
+        c = torch.empty(len(rows), self.N, dtype=torch.bfloat16, device=self.dev)
+        self.tb.matmul_fp4(qa, qb, c, sa, sb)
+        ref = mxfp4_oracle.mxfp4_gemm_ref(qa.cpu().numpy(), sa.cpu().numpy(), qb.cpu().numpy(), sb.cpu().numpy())
+        ok, e, _ = _parity(c, torch.from_numpy(np.asarray(ref, dtype=np.float32)), 1e-2)
+        # and the timed launch's own output on the same rows (full-size operands, scale atoms from the quantiser)
+        self.step(0, dist)
+        ok2, e2, _ = _parity(self.C[idx], torch.from_numpy(np.asarray(ref, dtype=np.float32)), 1e-2)
+        return ok and ok2, max(e, e2)
+
+    def _weights_again(self):
+        g = torch.Generator().manual_seed(4321)
+        for _ in range(self.nsets):
+            torch.randn(self.M, self.K, generator=g)
+        return torch.randn(self.N, self.K, generator=g).to(torch.bfloat16).to(self.dev)
+
+
+def _expert_weights(e, H, F, dev):
+    """Expert e's [gate | up] (2F, H) and down (H, F) projections, bf16 N(0, 0.02): any rank can rebuild any expert."""
+    g = torch.Generator(device=dev).manual_seed(5000 + e)
+    w1 = (torch.randn(2 * F, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(H, F, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    return w1, w2
+
 
 class MoeWorkload:
     """Expert-parallel MoE projections: 64 experts, top-8 of 16384 tokens, hidden 4096, ffn 1536, Zipf(1.1) routing."""
 
-    def __init__(self, args, wl, dev, rank, world):
+    def __init__(self, args, wl, dev, rank, world, nccl=False):
         import tritonblas_b200 as tb
         from tritonblas_b200 import distributed as tbd
-        self.tb, self.tbd, self.dev, self.world = tb, tbd, dev, world
+        self.tb, self.tbd, self.dev, self.world, self.rank = tb, tbd, dev, world, rank
         E, topk, T, H, F = MOE["experts"], MOE["topk"], MOE["tokens"], MOE["hidden"], MOE["ffn"]
         self.t_local = T // world
         epr = E // world
@@ -363,39 +468,183 @@ class MoeWorkload:
         p = (p / p.sum())[torch.randperm(E, generator=g)]
         ids_all = torch.multinomial(p.expand(T, E), topk, replacement=False, generator=g)
         self.ids_host = ids_all[rank * self.t_local:(rank + 1) * self.t_local].contiguous().pin_memory()
-        self.wts = torch.full((self.t_local, topk), 1.0 / topk, device=dev, dtype=torch.float32)
+        gw = torch.Generator().manual_seed(78 + rank)
+        self.wts = (torch.rand(self.t_local, topk, generator=gw) * 0.2 + 0.025).to(dev)   # routing weights, fp32
         gl = torch.Generator().manual_seed(1000 + rank)
         self.x_host = torch.randn(self.t_local, H, generator=gl).to(torch.bfloat16).pin_memory()
         self.x, self.ids = self.x_host.to(dev), self.ids_host.to(dev)
-        w1 = (torch.randn(epr, 2 * F, H, generator=gl) * 0.02).to(torch.bfloat16).to(dev)
-        w2 = (torch.randn(epr, H, F, generator=gl) * 0.02).to(torch.bfloat16).to(dev)
-        if world > 1 and not args.nccl_moe:
+        mine = [_expert_weights(e, H, F, dev) for e in range(rank * epr, (rank + 1) * epr)]
+        w1 = torch.stack([m[0] for m in mine])
+        w2 = torch.stack([m[1] for m in mine])
+        del mine
+        if world > 1 and not nccl:
             # token exchange over peer-mapped memory (one dispatch kernel, one combine kernel, two barriers)
             self.moe = tbd.PeerMemoryMoE(w1, w2, E, capacity=T * topk)
         else:
             self.moe = tbd.ExpertParallelMoE(w1, w2, E, None)
-        self.peer_path = isinstance(self.moe, tbd.PeerMemoryMoE)
+        self.path = "local" if world == 1 else ("nccl" if nccl else "peer")
         self.out_host = torch.empty(self.t_local, H, dtype=torch.bfloat16).pin_memory()
         rows = T * topk
         self.flops = 2.0 * rows * (H * 2 * F + F * H)
         self.kernel_flops = self.flops / world
         self.kernel_bytes = 0
         self.h2d, self.d2h = self.t_local * H * 2 + self.t_local * topk * 8, self.t_local * H * 2
-        counts = torch.bincount(ids_all.flatten(), minlength=E).reshape(world, epr).sum(1).tolist()
+        self.rows_per_rank = torch.bincount(ids_all.flatten(), minlength=E).reshape(world, epr).sum(1).tolist()
         self.label = (f"grouped MoE GEMM bf16: {E} experts, top-{topk} of {T} tokens, hidden {H}, ffn {F}, gate/up + down "
-                      f"projections, Zipf(1.1) routing (seeded), SwiGLU between (torch elementwise, outside the FLOP count)")
+                      f"projections, Zipf(1.1) routing (seeded), SwiGLU between (fused into the gate/up epilogue, outside "
+                      f"the FLOP count)")
         self.extra = {"parallelism": (f"expert-parallel x{world}, " + ("dispatch/combine kernels over NVLink peer memory"
-                                      if self.peer_path else "NCCL all-to-all dispatch/combine")) if world > 1
-                      else "single GPU", "rows_per_rank": counts}
+                                      if self.path == "peer" else "NCCL all-to-all dispatch/combine")) if world > 1
+                      else "single GPU", "rows_per_rank": self.rows_per_rank}
 
     def step(self, i, dist):
-        self.moe.forward(self.x, self.ids, self.wts)
+        return self.moe.forward(self.x, self.ids, self.wts)[0]
 
     def e2e_step(self, i, dist):
         x = self.x_host.to(self.dev, non_blocking=True)
         ids = self.ids_host.to(self.dev, non_blocking=True)
         out, _ = self.moe.forward(x, ids, self.wts)
         self.out_host.copy_(out, non_blocking=True)
+
+    def parity_check(self, dist):
+        """64 of this rank's tokens (their eight experts live on any rank) against the CPU oracle; rtol 2e-2 + 2e-2 rms
+        (two chained bf16 GEMMs and a bf16 weighted sum)."""
+        from oracle import moe_oracle
+        out = self.step(0, dist)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        H, F = MOE["hidden"], MOE["ffn"]
+        toks = torch.unique(torch.cat([torch.randint(0, self.t_local, (62,), generator=torch.Generator().manual_seed(9 + self.rank)),
+                                       torch.tensor([0, self.t_local - 1])])).tolist()
+        cache = {}
+
+        def weights(e):
+            if e not in cache:
+                w1, w2 = _expert_weights(e, H, F, self.dev)
+                cache[e] = (w1.cpu(), w2.cpu())
+            return cache[e]
+
+        ref = moe_oracle.moe_ffn_ref(self.x_host, self.ids_host, self.wts, lambda e: weights(e)[0], lambda e: weights(e)[1], toks)
+        ok, e, _ = _parity(out[torch.tensor(toks, device=self.dev)], ref, 2e-2)
+        return ok, e
+
+
+def make_workload(name, args, dev, rank, world, **kw):
+    wl = WORKLOADS[name]
+    if name == "moe":
+        return MoeWorkload(args, wl, dev, rank, world, **kw)
+    if wl["dtype"] == "mxfp4":
+        return Mxfp4Workload(args, wl, dev, rank, world, quant_only=(name == "mxfp4_quant"))
+    return DenseWorkload(args, wl, dev, rank, world)
+
+
+class Runner:
+    """Timing of step functions with CUDA events on the launching stream, barrier + synchronize on both sides."""
+
+    def __init__(self, dev, rank, world, local_rank, dist):
+        self.dev, self.rank, self.world, self.local_rank, self.dist = dev, rank, world, local_rank, dist
+        self.stream = torch.cuda.current_stream()
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, *values):
+        if self.world == 1:
+            return list(values)
+        t = torch.tensor(values, device=self.dev, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def all_ok(self, ok, err):
+        if self.world == 1:
+            return bool(ok), float(err)
+        t = torch.tensor([0.0 if ok else 1.0, err], device=self.dev, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t[0].item() == 0.0, t[1].item()
+
+    def timed(self, step, n_warm, n_timed, clocks=True, first=0):
+        """(total ms, mean ms of one call, clocks, launches of this library) of n_timed calls of step(i)."""
+        from tritonblas_b200 import _lib
+        it = first
+        for _ in range(n_warm):
+            step(it)
+            it += 1
+        self.barrier()
+        launches0 = _lib.lib.tb_launch_count()
+        sampler = ClockSampler(self.local_rank) if (clocks and self.rank == 0) else None
+        if sampler:
+            sampler.start()
+        events = []
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        wall0 = time.time()
+        t0.record(self.stream)
+        for _ in range(n_timed):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.stream)
+            step(it)
+            e1.record(self.stream)
+            events.append((e0, e1))
+            it += 1
+        t1.record(self.stream)
+        self.barrier()
+        wall1 = time.time()
+        ck = sampler.stop(wall0, wall1) if sampler else None
+        launches = _lib.lib.tb_launch_count() - launches0
+        total = t0.elapsed_time(t1)
+        unit = sum(a.elapsed_time(b) for a, b in events) / len(events)
+        total, unit = self.max_over_ranks(total, unit)
+        if self.world > 1:
+            lt = torch.tensor([launches], device=self.dev, dtype=torch.int64)
+            self.dist.all_reduce(lt)
+            launches = int(lt.item())
+        return total, unit, ck, int(launches)
+
+
+def roofline_of(name, w, unit_ms, timed_s, peaks, world):
+    wl = WORKLOADS[name]
+    if wl["bound"] == "tensor":
+        achieved = w.kernel_flops / (unit_ms * 1e-3) / 1e12
+        nominal = NOMINAL_TFLOPS[wl["dtype"]]
+        if wl["dtype"] in ("bf16", "fp16"):
+            peak = peaks["bf16_tflops"] if timed_s < 1.0 else peaks["bf16_tflops_sustained"]
+            kind = ("burst" if timed_s < 1.0 else "sustained") + f" cuBLAS bf16 ({peaks['source']})"
+        else:
+            # no measured fp8 / fp4 tensor peak exists on this pool: the denominator is the nominal dense rate
+            peak, kind = nominal, f"nominal dense {wl['dtype']} (no measured peak for this type)"
+        return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES.get(name) if world == 1 else None, "peak_kind": kind, "kernel_ms": unit_ms,
+                "frac_of_nominal_dense": achieved / nominal}
+    achieved = w.kernel_bytes / (unit_ms * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+            "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_kind": f"copy ({peaks['source']})", "kernel_ms": unit_ms,
+            "algorithmic_bytes": w.kernel_bytes, "frac_of_nominal": achieved / 7700.0}
+
+
+def release():
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+def moe_block(args, run, nccl):
+    """The MoE step at this GPU count: whole-job TFLOP/s (GEMM FLOPs of both projections / max-over-ranks time)."""
+    w = MoeWorkload(args, WORKLOADS["moe"], run.dev, run.rank, run.world, nccl=nccl)
+    n = max(5, min(args.steps, 12))
+    total, unit, ck, launches = run.timed(lambda i: w.step(i, run.dist), 3, n, clocks=run.world == 1)
+    ok, err = run.all_ok(*w.parity_check(run.dist))
+    out = {"value": w.flops * n / (total * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": total / n, "steps": n,
+           "rows_per_rank": w.rows_per_rank, "path": w.path, "gpu_launches": launches,
+           "parity_check": {"ok": ok, "max_err": err, "ranks_checked": run.world, "tokens_per_rank": 64,
+                            "tolerance": "2e-2 * (|ref| + rms(ref)) against the CPU oracle"},
+           "frac_of_nominal_dense": w.flops * n / (total * 1e-3) / 1e12 / (NOMINAL_TFLOPS["bf16"] * run.world)}
+    if ck:
+        out["clocks"] = ck
+    del w
+    release()
+    return out
 
 
 def main():
@@ -408,6 +657,8 @@ def main():
     ap.add_argument("--gemms-per-step", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-operand leg (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="default workload: skip the MoE, sustained, cuBLAS and per-workload blocks (profiling runs)")
     ap.add_argument("--nccl-moe", action="store_true",
                     help="moe workload on several GPUs: NCCL all-to-all dispatch/combine instead of the peer-memory kernels")
     ap.add_argument("--nccl-gather", action="store_true",
@@ -425,7 +676,6 @@ def main():
         return
 
     import tritonblas_b200 as tb
-    from tritonblas_b200 import _lib
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -434,95 +684,38 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    run = Runner(dev, rank, world, local_rank, dist)
+    default_line = args.workload == "bf16_8192" and not args.no_extras
 
-    if args.workload == "moe":
-        w = MoeWorkload(args, wl, dev, rank, world)
-        gps = 1
-    elif wl["dtype"] == "mxfp4":
-        w = Mxfp4Workload(args, wl, dev, rank, world, quant_only=(args.workload == "mxfp4_quant"))
-        gps = args.gemms_per_step
-    else:
-        w = DenseWorkload(args, wl, dev, rank, world)
-        gps = args.gemms_per_step
-    stream = torch.cuda.current_stream()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    it = 0
-    for _ in range(args.warmup * gps):
-        w.step(it, dist)
-        it += 1
-    barrier()
-    launches0 = _lib.lib.tb_launch_count()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    events = []
-    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    wall0 = time.time()
-    t_start.record(stream)
-    for _ in range(args.steps * gps):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        w.step(it, dist)
-        e1.record(stream)
-        events.append((e0, e1))
-        it += 1
-    t_end.record(stream)
-    barrier()
-    wall1 = time.time()
-    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
-    launches = _lib.lib.tb_launch_count() - launches0
-    ms_total = t_start.elapsed_time(t_end)
-    unit_ms = sum(a.elapsed_time(b) for a, b in events) / len(events)   # one GEMM (plus its collective when sharded)
+    w = make_workload(args.workload, args, dev, rank, world, **({"nccl": args.nccl_moe} if args.workload == "moe" else {}))
+    gps = 1 if args.workload == "moe" else args.gemms_per_step
+    ms_total, unit_ms, clocks, launches = run.timed(lambda i: w.step(i, dist), args.warmup * gps, args.steps * gps)
     status = tb.device_status(local_rank)
 
     e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))
-    for i in range(2 if e2e_steps else 0):
-        w.e2e_step(i, dist)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(e2e_steps):
-        w.e2e_step(i, dist)
-    if hasattr(w, "e2e_finish"):
-        w.e2e_finish()          # the last results' device-to-host copies are inside the timed region
-    e1.record(stream)
-    barrier()
-    e2e_ms = max(e0.elapsed_time(e1), 1e-6)
+    e2e_ms = 1e-6
+    if e2e_steps:
+        for i in range(2):
+            w.e2e_step(i, dist)
+        run.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(run.stream)
+        for i in range(e2e_steps):
+            w.e2e_step(i, dist)
+        if hasattr(w, "e2e_finish"):
+            w.e2e_finish()          # the last results' device-to-host copies are inside the timed region
+        e1.record(run.stream)
+        run.barrier()
+        (e2e_ms,) = run.max_over_ranks(max(e0.elapsed_time(e1), 1e-6))
 
-    if world > 1:
-        t = torch.tensor([ms_total, e2e_ms, unit_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, e2e_ms, unit_ms = t.tolist()
-        lt = torch.tensor([launches], device=dev, dtype=torch.int64)
-        dist.all_reduce(lt)
-        launches = int(lt.item())
+    p_ok, p_err = run.all_ok(*w.parity_check(dist))
 
+    peaks = measured_peaks()
+    line = None
     if rank == 0:
-        peaks = measured_peaks()
         value = w.flops * args.steps * gps / (ms_total * 1e-3) / 1e12
         e2e_value = w.flops * e2e_steps / (e2e_ms * 1e-3) / 1e12 if e2e_steps else 0.0
-        if wl["bound"] == "tensor":
-            timed_s = ms_total * 1e-3
-            peak = peaks["bf16_tflops"] if timed_s < 1.0 else peaks["bf16_tflops_sustained"]
-            # the measured denominator is cuBLAS bf16; fp8 and fp4 kinds scale it by their nominal rate ratio
-            ratio = NOMINAL_TFLOPS[wl["dtype"]] / NOMINAL_TFLOPS["bf16"]
-            achieved = w.kernel_flops / (unit_ms * 1e-3) / 1e12
-            roof = {"bound": "tensor", "achieved": achieved, "peak": peak * ratio, "unit": "TFLOP/s",
-                    "frac": achieved / (peak * ratio), "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None,
-                    "peak_kind": ("burst" if timed_s < 1.0 else "sustained") + f" cuBLAS bf16 ({peaks['source']})"
-                                 + (f" x{ratio:g} nominal {wl['dtype']}/bf16 rate" if ratio != 1 else ""),
-                    "kernel_ms": unit_ms, "frac_of_nominal_dense": achieved / NOMINAL_TFLOPS[wl["dtype"]]}
-        else:
-            achieved = w.kernel_bytes / (unit_ms * 1e-3) / 1e9
-            roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_kind": f"copy ({peaks['source']})",
-                    "kernel_ms": unit_ms, "algorithmic_bytes": w.kernel_bytes}
+        roof = roofline_of(args.workload, w, unit_ms, ms_total * 1e-3, peaks, world)
         cfg = {"workload": f"{args.workload}: {w.label}", "gemms_per_step": gps,
                "l2_policy": "operand sets rotate; the rotated sets together exceed the 126 MB L2"}
         cfg.update(w.extra)
@@ -532,9 +725,63 @@ def main():
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
             "config": cfg, "roofline": roof,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h,
-                    "steps": e2e_steps},
+                    "steps": e2e_steps,
+                    "path": "fused epilogue push" if getattr(w, "layers", None) is not None else "public API"},
             "gpu_launches": int(launches), "clocks": clocks, "device_status": status,
         }
+    parity = {"ok": p_ok, "max_err": p_err, "ranks_checked": world,
+              "sample": "64 rows x 256 columns of the gathered C per rank, columns from every rank's block"
+                        if isinstance(w, DenseWorkload) else "sampled rows / tokens",
+              "tolerance": "1e-2 * (|ref| + rms(ref)) against the CPU oracle (2e-2 for the MoE step; quantiser bit-exact)"}
+    if line is not None:
+        line["parity_check"] = parity
+
+    if default_line and world == 1:
+        # ---- the same operands through torch.matmul (cuBLAS) in the same run, and a sustained block of both
+        n = args.steps * gps
+        c_total, c_unit, _, _ = run.timed(lambda i: w.cublas_step(i), args.warmup * gps, n, clocks=False)
+        line["cublas_same_run"] = {"tflops": w.kernel_flops / (c_unit * 1e-3) / 1e12, "ms": c_unit,
+                                   "ours_over_cublas": c_unit / unit_ms,
+                                   "how": "torch.matmul(A, B^T view, out=C) on the same rotating operand sets, same launch count"}
+        n_sus = int(1800.0 / unit_ms) + 1
+        s_total, s_unit, s_ck, _ = run.timed(lambda i: w.step(i, dist), 8, n_sus)
+        cs_total, cs_unit, cs_ck, _ = run.timed(lambda i: w.cublas_step(i), 8, n_sus)
+        line["sustained"] = {"value": w.flops * n_sus / (s_total * 1e-3) / 1e12, "unit": "TFLOP/s", "seconds": s_total * 1e-3,
+                             "launches": n_sus, "sm_mhz_median": s_ck["sm_mhz"], "power_w_max": s_ck.get("power_w_max"),
+                             "reasons": s_ck["reasons"], "clock_samples": s_ck.get("samples"),
+                             "frac_of_measured_sustained_cublas": w.flops * n_sus / (s_total * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                             "cublas_same_run": {"tflops": w.flops * n_sus / (cs_total * 1e-3) / 1e12,
+                                                 "sm_mhz_median": cs_ck["sm_mhz"], "power_w_max": cs_ck.get("power_w_max")}}
+    del w
+    release()
+
+    if default_line:
+        moe = moe_block(args, run, nccl=False)
+        moe_nccl = moe_block(args, run, nccl=True) if world > 1 else None
+        if line is not None:
+            line["moe"] = moe
+            if moe_nccl is not None:
+                line["moe_nccl"] = moe_nccl
+
+    if default_line and world == 1:
+        items = []
+        for name in EXTRA_WORKLOADS:
+            xw = make_workload(name, args, dev, rank, world)
+            # about a quarter of a second of launches, timed one by one
+            _, est, _, _ = run.timed(lambda i: xw.step(i, dist), 3, 5, clocks=False)
+            n = max(20, min(4000, int(250.0 / max(est, 1e-3))))
+            total, unit, ck, nl = run.timed(lambda i: xw.step(i, dist), 3, n)
+            ok, err = xw.parity_check(dist)
+            flops = xw.kernel_flops if name != "mxfp4_quant" else 0.0
+            items.append({"workload": f"{name}: {xw.label}", "value": (flops / (unit * 1e-3) / 1e12) if flops else None,
+                          "unit": "TFLOP/s", "kernel_ms": unit, "launches": n, "gpu_launches": nl,
+                          "roofline": roofline_of(name, xw, unit, total * 1e-3, peaks, 1), "clocks": ck,
+                          "parity_check": {"ok": ok, "max_err": err}})
+            del xw
+            release()
+        line["workloads"] = items
+
+    if line is not None:
         if not args.no_cpu_baseline and world == 1:
             if args.workload == "moe":
                 M, N, K = 2048, MOE["hidden"], 2 * MOE["ffn"]
@@ -546,6 +793,7 @@ def main():
                                               f"full {K}x{N} B, repeated for {dt:.1f} s in total"}
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -5,7 +5,7 @@
  *   - every entry point returns 0 on success or a positive TB_ERR_* code; tb_status_string() explains a code;
  *   - pointers are raw device pointers, sizes and strides are in ELEMENTS unless a name ends in _bytes;
  *   - `stream` is a cudaStream_t passed as void*; work is enqueued, never synchronised, unless stated;
- *   - the library neither allocates nor frees caller memory: outputs and workspaces are caller-owned;
+ *   - the library neither allocates nor frees device memory: outputs and workspaces are caller-owned;
  *   - citations name the reference interface (path inside the tritonBLAS tree : line) an entry point stands in for.
  */
 #ifndef TRITONBLAS_B200_H_
@@ -154,18 +154,21 @@ int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);
  * arena at start-up, or a latency path on which cudaMalloc (which synchronises the whole device) is not allowed, has no
  * way to size and own the partial-tile workspace tb_gemm asks for. This entry point takes no workspace: flags and fp32
  * partial tiles live in an array that is part of the library image (4 KB + 10 MB per GPU that loads the library, held
- * until the process exits), and the failure word its kernels write is built in as well. It calls no allocator (no
- * cudaMalloc / cudaFree, no torch). It has no counterpart in the reference.
- *   - Same arguments as tb_gemm with streamk = 1; args->workspace / workspace_bytes / epoch are ignored. Operands must be
- *     K-contiguous f16, bf16 or e4m3; output f16, bf16 or f32.
- *   - Limit: programs x 128 x block_n x 4 bytes (x2 for a CTA pair) of partial tiles must fit 10 MB; a launch that needs
- *     more returns TB_ERR_WORKSPACE and tb_last_cuda_error() says by how much (lower args->sk_grid, or use tb_gemm).
- *   - The first call on a device looks up the device addresses of the built-in arrays; make that first call before any
+ * until the process exits). It calls no allocator (no cudaMalloc / cudaFree, no torch); nothing else in the library does
+ * either. It has no counterpart in the reference.
+ *   - Same arguments and launch path as tb_gemm with streamk = 1; args->workspace / workspace_bytes / epoch /
+ *     tile_counter are ignored. epilogue_op, group_offsets / num_groups and c_copies are not offered here
+ *     (TB_ERR_UNSUPPORTED).
+ *   - Limit: a launch that splits a tile keeps one fp32 partial tile per CTA, programs x 128 x block_n x 4 bytes (x2 for a
+ *     CTA pair), which must fit 10 MB; a launch that needs more returns TB_ERR_WORKSPACE and tb_last_cuda_error() says by
+ *     how much (lower args->sk_grid, or use tb_gemm). A launch whose grid divides its tile count splits nothing and is
+ *     never refused.
+ *   - The first call on a device looks up the device address of the built-in array; make that first call before any
  *     stream capture begins.
  *   - All calls on a device share the one array, which keeps the previous call's contents (the flags are cleared at the
  *     start of every call, on `stream`): two calls whose kernels overlap on the GPU (different streams) race.
- *   - prev_status, when not NULL, receives and clears the failure code recorded by earlier calls on this device; reading
- *     it waits for `stream`. Pass NULL to stay asynchronous. */
+ *   - prev_status, when not NULL, receives and clears the device's failure code (the word tb_device_status reads)
+ *     recorded by earlier launches; reading it waits for `stream`. Pass NULL to stay asynchronous. */
 int tb_gemm_streamk_builtin(const tb_gemm_args* args, const tb_config* cfg, void* stream, int32_t* prev_status);
 
 /* Grouped GEMM over row groups of A (expert-parallel MoE projections). No reference counterpart: its semantics are the

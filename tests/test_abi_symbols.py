@@ -37,3 +37,17 @@ def test_struct_sizes_match_header_layout():
     from tritonblas_b200 import _lib
     assert ctypes.sizeof(_lib.Problem) == 13 * 4
     assert ctypes.sizeof(_lib.Config) == 15 * 4
+
+
+def test_library_sources_name_no_device_allocator():
+    """The library never allocates device memory (its status word and the built-in stream-K scratch are part of the
+    library image): no source file calls an allocating or freeing CUDA routine."""
+    import glob
+    import os
+    import re
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pat = re.compile(r"\b(cudaMalloc\w*|cudaFree\w*|cuMemAlloc\w*|cuMemFree\w*|cudaHostAlloc|cuMemCreate)\s*\(")
+    for path in glob.glob(os.path.join(here, "tritonblas_b200", "csrc", "*")):
+        if path.endswith((".cu", ".cuh", ".cpp", ".h")):
+            with open(path) as f:
+                assert not pat.search(f.read()), path

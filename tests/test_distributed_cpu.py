@@ -124,6 +124,30 @@ def test_peer_dispatch_plan_places_every_row_once_and_expert_major():
             assert expert_tag[d][row] == int(ids[r].flatten()[f])
 
 
+def test_peer_dispatch_plan_clamps_group_offsets_to_capacity():
+    """A receive buffer smaller than the routing needs: the dispatch kernel drops rows at or beyond `capacity`; the group
+    offsets handed to the grouped GEMM are clamped to it (never past the buffer, still ascending), and the pairs whose row
+    was dropped are exactly those the combine kernel skips (row >= capacity)."""
+    world, E, T, topk = 2, 8, 50, 2
+    g = torch.Generator().manual_seed(6)
+    ids = [torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)]) for _ in range(world)]
+    counts_all = torch.stack([torch.bincount(i.flatten(), minlength=E) for i in ids])
+    epr = E // world
+    for r in range(world):
+        need = int(counts_all[:, r * epr:(r + 1) * epr].sum())
+        cap = need - 17
+        full = tbd.plan_peer_dispatch(ids[r], counts_all, r)
+        clamped = tbd.plan_peer_dispatch(ids[r], counts_all, r, capacity=cap)
+        offs = clamped.group_offsets.tolist()
+        assert offs[0] == 0 and offs[-1] == cap and all(a <= b for a, b in zip(offs, offs[1:]))
+        assert offs == [min(o, cap) for o in full.group_offsets.tolist()]
+        assert torch.equal(clamped.dest_row, full.dest_row)           # rows keep their places; the kernels drop the tail
+    dropped = sum(int(((tbd.plan_peer_dispatch(ids[r], counts_all, r).dest_row >= int(counts_all[:, d * epr:(d + 1) * epr].sum()) - 17)
+                       & (tbd.plan_peer_dispatch(ids[r], counts_all, r).dest_rank == d)).sum())
+                  for r in range(world) for d in range(world))
+    assert dropped == 17 * world
+
+
 def test_bench_matmul_csv_schema(tmp_path):
     """The YAML/CSV benchmark tool writes the reference's column set (benchmarks/tritonblas_matmul.py:278-291)."""
     from tritonblas_b200 import bench_matmul as bm

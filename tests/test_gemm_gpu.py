@@ -138,6 +138,24 @@ def test_large_unaligned_operands_take_the_tensor_core_path(ta, tb_):
     assert_close_to_oracle(c, a, b, what=f"unaligned {ta}{tb_}")
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 200, 100), (512, 768, 256), (64, 96, 0)])
+def test_output_fan_out_to_further_buffers(m, n, k):
+    """c_copies: every tile also goes to further buffers laid out like C (on several GPUs: the peers' gathered C). Checked on
+    one GPU with local buffers, for operands TMA can address and for K % 8 != 0, which runs on the CUDA-core kernel; K = 0
+    leaves bias only."""
+    a, b = make_operands(m, n, max(k, 8), torch.bfloat16, "T", "T", seed=17)
+    a, b = a[:, :k].contiguous(), b[:k].T.contiguous().T          # K-contiguous with pitch K: unaligned when K % 8 != 0
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).cuda()
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    copies = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    sel = tb.OrigamiMatmulSelector(m, n, max(k, 1), torch.bfloat16, torch.bfloat16, torch.bfloat16, torch.device("cuda", 0),
+                                   max_halves=1)
+    tb.persistent_matmul_lt(a, b, c, sel, None, bias=bias, c_copies=[t.data_ptr() for t in copies])
+    assert_close_to_oracle(c, a, b, bias=bias, what=f"fan-out {(m, n, k)}")
+    for t in copies:
+        assert torch.equal(t, c)
+
+
 @pytest.mark.parametrize("pair", [1, 2])
 def test_strided_output_and_out_argument(pair):
     m, n, k = 300, 200, 256

@@ -57,6 +57,16 @@ for _ in range(2):
     out2, _ = peer.forward(xs[rank], ids[rank], wts[rank])
     assert torch.allclose(out2.float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item()), "peer-memory MoE"
 assert int(peer.overflow.item()) == 0
+# unaligned shard (K not a multiple of 8): the CUDA-core kernel must fan the tiles out to the peers as well
+K2 = 100
+a2 = (torch.randn(64, K2, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+b2 = (torch.randn(256, K2, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+lo2, hi2 = tbd.shard_range(256, world, rank)
+layer2 = tbd.ColumnShardedGemm(b2[lo2:hi2].contiguous())
+layer2.enable_fused_gather(64)
+c3 = tbd.ColumnShardedGemm.as_matrix(layer2.forward_fused(a2)).float()
+ref3 = a2.float() @ b2.float().T
+assert torch.allclose(c3, ref3, rtol=1e-2, atol=1e-2 * ref3.abs().max().item()), "fused push from the CUDA-core kernel"
 assert tb.device_status(rank) == 0
 dist.barrier()
 dist.destroy_process_group()
@@ -73,7 +83,7 @@ def test_two_rank_sharded_gemm_fused_push_and_moe():
     procs = []
     for rank in range(2):
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
-                   TB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+                   TB_ROOT=ROOT, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
         procs.append(subprocess.Popen([sys.executable, "-c", WORKER], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))
     outs = []

@@ -238,7 +238,6 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   if (a.m == 0 || a.n == 0) return TB_OK;
   if (a.a == nullptr || a.b == nullptr || a.c == nullptr) return TB_ERR_INVALID;
   if (a.a_dtype != a.b_dtype) return TB_ERR_UNSUPPORTED;
-  if (a.k == 0) return TB_ERR_UNSUPPORTED;
   const int es = esize_of(a.a_dtype);
   if (es == 0 || a.a_dtype == TB_DTYPE_U8) return TB_ERR_UNSUPPORTED;
   if (a.c_dtype != TB_DTYPE_F16 && a.c_dtype != TB_DTYPE_BF16 && a.c_dtype != TB_DTYPE_F32 && a.c_dtype != TB_DTYPE_E4M3 &&
@@ -250,7 +249,8 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   int rc = current_device_state(&dev, &device);
   if (rc != TB_OK) return rc;
 
-  if (a.a_dtype == TB_DTYPE_F32 && !a.allow_tf32) return grouped ? TB_ERR_UNSUPPORTED : gemm_fp32_exact(a, stream);
+  // An empty K range leaves the epilogue alone (zero, scaled, plus bias): the CUDA-core kernel's loop simply does not run.
+  if ((a.a_dtype == TB_DTYPE_F32 && !a.allow_tf32) || a.k == 0) return grouped ? TB_ERR_UNSUPPORTED : gemm_fp32_exact(a, stream);
 
   // operand majors from strides
   int a_mn, b_mn;

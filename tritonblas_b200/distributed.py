@@ -71,7 +71,7 @@ class ColumnShardedGemm:
                                                      self.b_shard_t.dtype, dtype, self.b_shard_t.device, max_halves=1)
         return self._gathered
 
-    def forward_fused(self, a: torch.Tensor, pre_barrier: bool = True) -> torch.Tensor:
+    def forward_fused(self, a: torch.Tensor, pre_barrier: bool = True, b_shard_t: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One kernel computes this rank's block of C and pushes it into every rank's gathered buffer; a symmetric-memory
         barrier then orders the ranks. Returns this rank's (world, M, n_local) buffer.
 
@@ -79,11 +79,12 @@ class ColumnShardedGemm:
         overwrites them. It can be dropped (one barrier less per call) when calls alternate between two or more
         gathered buffers and each buffer is read on this stream before the next call is enqueued: a rank can then only
         start overwriting a buffer after every rank has passed the closing barrier of the call in between, which on each
-        rank's stream comes after its reads."""
+        rank's stream comes after its reads. ``b_shard_t`` replaces this rank's block of B for one call (same shape)."""
         from .matmul import persistent_matmul_lt
         if pre_barrier:
             self._handle.barrier(channel=0)      # nobody is still reading the previous contents
-        persistent_matmul_lt(a, self.b_shard_t.T, self._gathered[self.rank], self._fused_selector, None,
+        b_t = self.b_shard_t if b_shard_t is None else b_shard_t
+        persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None,
                              c_copies=self._peer_slots)
         self._handle.barrier(channel=1)          # every rank's pushes have landed
         return self._gathered

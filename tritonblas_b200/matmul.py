@@ -137,11 +137,6 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
         raise RuntimeError(f"output has shape {tuple(c.shape)}, expected {(M, N)}")
     if M == 0 or N == 0:
         return c
-    if K == 0:
-        c.zero_()
-        if bias is not None:
-            c.add_(bias.to(c.dtype))
-        return c
     a = _unit_stride_2d(a)
     b = _unit_stride_2d(b)
     if M * N * K >= _REPITCH_MIN_MACS and a.dtype != torch.float32:

@@ -163,7 +163,7 @@ def quantize_fp8_rows(x: torch.Tensor):
     return q, scale
 
 
-def _mxfp4_quant(x, hadamard, scale_atoms=False):
+def _mxfp4_quant(x, hadamard, scale_atoms=False, out=None):
     assert x.ndim == 2, "Input must be 2D tensor"
     M, N = x.shape
     assert N % 32 == 0, f"N ({N}) must be divisible by 32"
@@ -174,17 +174,30 @@ def _mxfp4_quant(x, hadamard, scale_atoms=False):
     es = x.element_size()
     if x.stride(1) != 1 or (x.stride(0) * es) % 16 != 0 or x.data_ptr() % 16 != 0:
         x = x.contiguous()
-    codes = torch.empty((M, N // 2), dtype=torch.uint8, device=x.device)
-    scales = torch.empty((M, N // 32), dtype=torch.uint8, device=x.device)
-    atoms = None
-    if scale_atoms:
-        atoms = torch.full((max(int(_lib.lib.tb_mxfp4_atoms_bytes(M, N)), 16),), 127, dtype=torch.uint8, device=x.device)
+    atoms = scales = None
+    if out is not None:
+        # the (codes, scales) pair of an earlier call with the same shape and flags: nothing is allocated or filled
+        codes, second = out
+        assert tuple(codes.shape) == (M, N // 2) and codes.dtype == torch.uint8 and codes.device == x.device
+        if scale_atoms:
+            assert isinstance(second, Mxfp4ScaleAtoms) and (second.rows, second.k) == (M, N)
+            atoms = second.data
+        else:
+            assert tuple(second.shape) == (M, N // 32)
+            scales = second
+    else:
+        codes = torch.empty((M, N // 2), dtype=torch.uint8, device=x.device)
+        if scale_atoms:   # padding rows and blocks of the atom layout hold 127 (scale 1.0); the kernel writes the rest
+            atoms = torch.full((max(int(_lib.lib.tb_mxfp4_atoms_bytes(M, N)), 16),), 127, dtype=torch.uint8, device=x.device)
+        else:
+            scales = torch.empty((M, N // 32), dtype=torch.uint8, device=x.device)
     if M == 0 or N == 0:
         return (codes, Mxfp4ScaleAtoms(atoms, M, N)) if scale_atoms else (codes, scales)
     with torch.cuda.device(x.device):
         rc = _lib.lib.tb_mxfp4_quant_atoms(ctypes.c_void_p(x.data_ptr()), _lib.DTYPE_CODE[x.dtype], M, N, x.stride(0),
                                            ctypes.c_void_p(codes.data_ptr()), codes.stride(0),
-                                           ctypes.c_void_p(scales.data_ptr()), scales.stride(0),
+                                           ctypes.c_void_p(scales.data_ptr() if scales is not None else 0),
+                                           scales.stride(0) if scales is not None else N // 32,
                                            ctypes.c_void_p(atoms.data_ptr()) if scale_atoms else ctypes.c_void_p(0),
                                            int(hadamard), _lib.current_stream_ptr(x.device))
     _lib.check(rc, "tb_mxfp4_quant")
@@ -193,17 +206,20 @@ def _mxfp4_quant(x, hadamard, scale_atoms=False):
     return codes, scales
 
 
-def dynamic_mxfp4_quant(x: torch.Tensor, scale_atoms: bool = False):
+def dynamic_mxfp4_quant(x: torch.Tensor, scale_atoms: bool = False, out=None):
     """x (M, N) -> packed e2m1 codes (M, N/2) uint8 and e8m0 scales (M, N/32) uint8, one scale per 32 contiguous
     elements; bit-identical to the reference quantiser (utils.py:742-789). With ``scale_atoms`` the scales come back as
-    :class:`Mxfp4ScaleAtoms`, ready for matmul_fp4 without a re-arrangement pass."""
-    return _mxfp4_quant(x, False, scale_atoms)
+    :class:`Mxfp4ScaleAtoms`, ready for matmul_fp4 without a re-arrangement pass. ``out``: the pair an earlier call with
+    the same shape and flags returned; it is overwritten and returned (no allocation, no fill: a steady-state step is
+    then one kernel)."""
+    return _mxfp4_quant(x, False, scale_atoms, out)
 
 
-def hadamard_mxfp4_quant(x: torch.Tensor, scale_atoms: bool = False):
+def hadamard_mxfp4_quant(x: torch.Tensor, scale_atoms: bool = False, out=None):
     """Fused activation transform: rotate every 32-element block by H32/sqrt(32), then quantise to MXFP4.
-    Apply it to both operands' K blocks: (A H)(B H)^T = A B^T because H is orthonormal and symmetric."""
-    return _mxfp4_quant(x, True, scale_atoms)
+    Apply it to both operands' K blocks: (A H)(B H)^T = A B^T because H is orthonormal and symmetric. ``out`` as in
+    :func:`dynamic_mxfp4_quant`."""
+    return _mxfp4_quant(x, True, scale_atoms, out)
 
 
 _E2M1_TABLE = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
