@@ -36,14 +36,18 @@ def gemm_ref_f32(a, b, a_scale=None, b_scale=None, bias=None):
 
 def quantize_per_channel_ref(x, dtype, axis):
     """Per-row (axis=1) or per-column (axis=0) symmetric quantisation to fp8/int8 as the reference fixture does
-    (include/tritonblas/utils.py:340-377): scale = clamp(amax, 1e-8) / dtype_max, q = (x * (1/scale)).to(dtype)."""
+    (include/tritonblas/utils.py:340-377): scale = clamp(amax, 1e-8) / dtype_max, q = (x * (1/scale)).to(dtype).
+
+    The fixture runs where its input lives, which in the reference's tests is the GPU, and there torch divides a tensor
+    by a Python scalar as a multiplication by the scalar's fp32 reciprocal; this restatement does the same so that it
+    reproduces the reference's scales bit for bit (a true division differs by one ulp for some rows)."""
     xf = x.detach().cpu().to(torch.float32)
     if dtype.is_floating_point:
         qmax = torch.finfo(dtype).max
     else:
         qmax = torch.iinfo(dtype).max
     amax = xf.abs().amax(dim=axis, keepdim=True).clamp(min=1e-8)
-    scale = amax / qmax
+    scale = amax * (torch.tensor(1.0, dtype=torch.float32) / torch.tensor(float(qmax), dtype=torch.float32))
     q = xf * (1.0 / scale)
     if not dtype.is_floating_point:
         q = q.round().clamp(-qmax, qmax)
