@@ -477,11 +477,12 @@ class MoeWorkload:
         w1 = torch.stack([m[0] for m in mine])
         w2 = torch.stack([m[1] for m in mine])
         del mine
-        if world > 1 and not nccl:
-            # token exchange over peer-mapped memory (one dispatch kernel, one combine kernel, two barriers)
-            self.moe = tbd.PeerMemoryMoE(w1, w2, E, capacity=T * topk)
-        else:
+        if nccl:
             self.moe = tbd.ExpertParallelMoE(w1, w2, E, None)
+        else:
+            # device-side plan, one dispatch and one combine kernel; on several GPUs the rows travel over peer-mapped
+            # memory (two barriers), on one GPU the same kernels run on local buffers
+            self.moe = tbd.PeerMemoryMoE(w1, w2, E, capacity=T * topk)
         self.path = "local" if world == 1 else ("nccl" if nccl else "peer")
         self.out_host = torch.empty(self.t_local, H, dtype=torch.bfloat16).pin_memory()
         rows = T * topk

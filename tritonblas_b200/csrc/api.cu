@@ -236,7 +236,7 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   if (a.m < 0 || a.n < 0 || a.k < 0) return TB_ERR_INVALID;
   if (grouped && (a.group_offsets == nullptr || a.num_groups <= 0 || a.num_groups > 4096 || a.streamk)) return TB_ERR_INVALID;
   if (a.m == 0 || a.n == 0) return TB_OK;
-  if (a.a == nullptr || a.b == nullptr || a.c == nullptr) return TB_ERR_INVALID;
+  if (a.c == nullptr || ((a.a == nullptr || a.b == nullptr) && a.k != 0)) return TB_ERR_INVALID;  // empty operands have no address
   if (a.a_dtype != a.b_dtype) return TB_ERR_UNSUPPORTED;
   const int es = esize_of(a.a_dtype);
   if (es == 0 || a.a_dtype == TB_DTYPE_U8) return TB_ERR_UNSUPPORTED;

@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restri
                                                              const int* __restrict__ dest_rank,
                                                              const long long* __restrict__ dest_row, PeerPtrs peers,
                                                              long long dest_stride_vec, long long n, int vec_per_row,
-                                                             long long capacity_rows, int* __restrict__ overflow) {
+                                                             long long capacity_rows, int* __restrict__ overflow, int topk) {
   // one warp per row
   const int lane = threadIdx.x & 31;
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -190,7 +190,9 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restri
       if (lane == 0 && overflow != nullptr) atomicAdd(overflow, 1);
       continue;
     }
-    const uint4* src = x + src_token[r] * x_stride_vec;
+    // without a source list the i-th entry is the flattened (token, k) pair i: token i / topk
+    const long long token = src_token != nullptr ? src_token[r] : r / topk;
+    const uint4* src = x + token * x_stride_vec;
     uint4* dst = reinterpret_cast<uint4*>(peers.p[dest_rank[r]]) + row * dest_stride_vec;
     for (int v = lane; v < vec_per_row; v += 32) dst[v] = src[v];
   }
@@ -232,8 +234,9 @@ __global__ void __launch_bounds__(256) combine_peers_kernel(PeerPtrs y_peers, lo
 extern "C" int tb_moe_dispatch_peers(const void* x, int64_t x_row_stride, const int64_t* src_token, const int32_t* dest_rank,
                                      const int64_t* dest_row, void* const* peer_bufs, int32_t num_peers,
                                      int64_t dest_row_stride, int64_t capacity_rows, int32_t* overflow_count, int64_t n,
-                                     int32_t hidden, int32_t dtype, void* stream) {
-  if (x == nullptr || src_token == nullptr || dest_rank == nullptr || dest_row == nullptr || peer_bufs == nullptr) return TB_ERR_INVALID;
+                                     int32_t hidden, int32_t dtype, int32_t topk, void* stream) {
+  if (x == nullptr || dest_rank == nullptr || dest_row == nullptr || peer_bufs == nullptr) return TB_ERR_INVALID;
+  if (src_token == nullptr && topk < 1) return TB_ERR_INVALID;
   if (num_peers < 1 || num_peers > 8 || n < 0 || hidden <= 0 || (hidden % 8) != 0) return TB_ERR_INVALID;
   if (dtype != TB_DTYPE_BF16 && dtype != TB_DTYPE_F16) return TB_ERR_UNSUPPORTED;
   if (n == 0) return TB_OK;
@@ -247,7 +250,8 @@ extern "C" int tb_moe_dispatch_peers(const void* x, int64_t x_row_stride, const 
   if (blocks > 148LL * 8 * 4) blocks = 148LL * 8 * 4;
   tb::moe_dispatch_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), x_row_stride / 8, reinterpret_cast<const long long*>(src_token), dest_rank,
-      reinterpret_cast<const long long*>(dest_row), peers, dest_row_stride / 8, n, hidden / 8, capacity_rows, overflow_count);
+      reinterpret_cast<const long long*>(dest_row), peers, dest_row_stride / 8, n, hidden / 8, capacity_rows, overflow_count,
+      topk < 1 ? 1 : topk);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return tb::cuda_fail(e, "moe_dispatch_kernel launch");
   tb::g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -316,6 +320,158 @@ extern "C" int tb_moe_combine_peers(void* const* y_peers, int32_t num_peers, int
     return TB_ERR_UNSUPPORTED;
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return tb::cuda_fail(e, "combine_peers_kernel launch");
+  tb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return TB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Dispatch plan on the device: where every routed (token, k) pair goes. Two small kernels replace a sort, a histogram and
+// a dozen index operations:
+//   count: counts[e] = pairs of this rank routed to expert e (shared-memory histogram per block, one global add per
+//          expert and block);
+//   plan:  given the counts of every rank (counts_all[r][e], after the ranks exchanged them), expert e lives on rank
+//          e / experts_per_rank; inside its owner's receive buffer the experts follow each other and inside an expert the
+//          source ranks follow each other. A pair of this rank routed to e gets row
+//              owner_off[e] + sum_{r < rank} counts_all[r][e] + (its position among this rank's pairs of e),
+//          the position taken from a per-expert cursor (block-aggregated, so the order inside an expert is arbitrary;
+//          every row is computed independently of its position and the combine step sums in k order, so the result
+//          does not depend on it).
+namespace tb {
+namespace {
+
+constexpr int kPlanThreads = 256;
+constexpr int kPlanItems = 4;       // pairs per thread
+constexpr int kPlanMaxExperts = 1024;
+
+__device__ __forceinline__ int expert_of(const void* ids, int is64, long long f) {
+  return is64 ? static_cast<int>(static_cast<const long long*>(ids)[f]) : static_cast<const int*>(ids)[f];
+}
+
+__global__ void __launch_bounds__(kPlanThreads) moe_count_kernel(const void* __restrict__ ids, int is64, long long n, int E,
+                                                                  int* __restrict__ counts) {
+  __shared__ int hist[kPlanMaxExperts];
+  for (int e = threadIdx.x; e < E; e += kPlanThreads) hist[e] = 0;
+  __syncthreads();
+  const long long base = static_cast<long long>(blockIdx.x) * kPlanThreads * kPlanItems;
+#pragma unroll
+  for (int i = 0; i < kPlanItems; ++i) {
+    const long long f = base + i * kPlanThreads + threadIdx.x;
+    if (f < n) {
+      const int e = expert_of(ids, is64, f);
+      if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += kPlanThreads)
+    if (hist[e] != 0) atomicAdd(&counts[e], hist[e]);
+}
+
+__global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const void* __restrict__ ids, int is64, long long n, int E,
+                                                                 int world, int rank, const int* __restrict__ counts_all,
+                                                                 int* __restrict__ cursor, long long capacity,
+                                                                 int* __restrict__ pair_rank, long long* __restrict__ pair_row,
+                                                                 int* __restrict__ group_offsets) {
+  __shared__ int total[kPlanMaxExperts];      // rows of expert e over all source ranks
+  __shared__ long long dest[kPlanMaxExperts]; // first row of this rank's pairs of expert e in the owner's buffer
+  __shared__ int hist[kPlanMaxExperts];
+  __shared__ int block_base[kPlanMaxExperts];
+  const int epr = E / world;
+  for (int e = threadIdx.x; e < E; e += kPlanThreads) {
+    int t = 0, lower = 0;
+    for (int r = 0; r < world; ++r) {
+      const int c = counts_all[r * E + e];
+      t += c;
+      if (r < rank) lower += c;
+    }
+    total[e] = t;
+    hist[e] = lower;        // parked here until the owner offsets are known
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += kPlanThreads) {
+    long long off = 0;
+    for (int j = (e / epr) * epr; j < e; ++j) off += total[j];
+    dest[e] = off + hist[e];
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    // row offsets of this rank's own experts, clamped to the receive buffer (rows beyond it are dropped by the dispatch)
+    for (int j = threadIdx.x; j <= epr; j += kPlanThreads) {
+      long long off = 0;
+      for (int i = 0; i < j; ++i) off += total[rank * epr + i];
+      group_offsets[j] = static_cast<int>(off < capacity ? off : capacity);
+    }
+  }
+  for (int e = threadIdx.x; e < E; e += kPlanThreads) hist[e] = 0;
+  __syncthreads();
+  const long long base = static_cast<long long>(blockIdx.x) * kPlanThreads * kPlanItems;
+  int ex[kPlanItems], local[kPlanItems];
+#pragma unroll
+  for (int i = 0; i < kPlanItems; ++i) {
+    const long long f = base + i * kPlanThreads + threadIdx.x;
+    ex[i] = -1;
+    local[i] = 0;
+    if (f < n) {
+      const int e = expert_of(ids, is64, f);
+      if (e >= 0 && e < E) {
+        ex[i] = e;
+        local[i] = atomicAdd(&hist[e], 1);
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += kPlanThreads) block_base[e] = hist[e] != 0 ? atomicAdd(&cursor[e], hist[e]) : 0;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < kPlanItems; ++i) {
+    const long long f = base + i * kPlanThreads + threadIdx.x;
+    if (f < n) {
+      const int e = ex[i];
+      // an expert id outside [0, E) routes nowhere: row -1 is dropped by the dispatch and skipped by the combine
+      pair_rank[f] = e >= 0 ? e / epr : 0;
+      pair_row[f] = e >= 0 ? dest[e] + block_base[e] + local[i] : -1;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace tb
+
+extern "C" int tb_moe_count(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts, int32_t* counts,
+                            void* stream) {
+  if (topk_ids == nullptr || counts == nullptr || n_pairs < 0 || num_experts < 1 || num_experts > tb::kPlanMaxExperts)
+    return TB_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int32_t) * num_experts, st);
+  if (e != cudaSuccess) return tb::cuda_fail(e, "cudaMemsetAsync(counts)");
+  if (n_pairs == 0) return TB_OK;
+  const long long per_block = tb::kPlanThreads * tb::kPlanItems;
+  const unsigned blocks = static_cast<unsigned>((n_pairs + per_block - 1) / per_block);
+  tb::moe_count_kernel<<<blocks, tb::kPlanThreads, 0, st>>>(topk_ids, ids_are_int64, n_pairs, num_experts, counts);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return tb::cuda_fail(e, "moe_count_kernel launch");
+  tb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return TB_OK;
+}
+
+extern "C" int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts, int32_t world,
+                           int32_t rank, const int32_t* counts_all, int32_t* cursor, int64_t capacity_rows,
+                           int32_t* pair_rank, int64_t* pair_row, int32_t* group_offsets, void* stream) {
+  if (topk_ids == nullptr || counts_all == nullptr || cursor == nullptr || pair_rank == nullptr || pair_row == nullptr ||
+      group_offsets == nullptr)
+    return TB_ERR_INVALID;
+  if (n_pairs < 0 || num_experts < 1 || num_experts > tb::kPlanMaxExperts || world < 1 || rank < 0 || rank >= world ||
+      (num_experts % world) != 0 || capacity_rows < 0)
+    return TB_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(cursor, 0, sizeof(int32_t) * num_experts, st);
+  if (e != cudaSuccess) return tb::cuda_fail(e, "cudaMemsetAsync(cursor)");
+  const long long per_block = tb::kPlanThreads * tb::kPlanItems;
+  const unsigned blocks = static_cast<unsigned>(n_pairs > 0 ? (n_pairs + per_block - 1) / per_block : 1);
+  tb::moe_plan_kernel<<<blocks, tb::kPlanThreads, 0, st>>>(topk_ids, ids_are_int64, n_pairs, num_experts, world, rank, counts_all,
+                                                          cursor, capacity_rows, pair_rank,
+                                                          reinterpret_cast<long long*>(pair_row), group_offsets);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return tb::cuda_fail(e, "moe_plan_kernel launch");
   tb::g_launches.fetch_add(1, std::memory_order_relaxed);
   return TB_OK;
 }

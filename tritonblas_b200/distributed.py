@@ -256,8 +256,12 @@ class ExpertParallelMoE:
 # ---------------------------------------------------------------------------------------------- peer-memory MoE path
 @dataclass
 class PeerDispatchPlan:
-    """Where every (token, k) pair of this rank goes when rows are written straight into the owners' receive buffers."""
-    src_token: torch.Tensor      # int64 (n,)  token of the i-th row in expert-sorted order
+    """Where every (token, k) pair of this rank goes when rows are written straight into the owners' receive buffers.
+
+    ``plan_peer_dispatch`` (torch index arithmetic, any device: the specification the CPU tests check) lists the rows in
+    expert-sorted order; ``PeerMemoryMoE.plan`` (two CUDA kernels) lists them in pair order with ``src_token`` None
+    (entry i is pair i, token i // topk) and leaves the order of the rows inside an expert unspecified."""
+    src_token: Optional[torch.Tensor]   # int64 (n,)  token of the i-th row; None: entry i is the flattened pair i
     dest_rank: torch.Tensor      # int32 (n,)  rank that owns the row's expert
     dest_row: torch.Tensor       # int64 (n,)  row in that rank's receive buffer
     pair_rank: torch.Tensor      # int32 (tokens*topk,)  the same, indexed by the flattened (token, k) pair
@@ -309,54 +313,100 @@ def plan_peer_dispatch(topk_ids: torch.Tensor, counts_all: torch.Tensor, rank: i
 class PeerMemoryMoE:
     """Expert-parallel MoE feed-forward whose token exchange runs over peer-mapped memory instead of collectives.
 
-    Every rank allocates a receive buffer and an output buffer of ``capacity`` rows in symmetric memory. dispatch is ONE
-    kernel that writes each routed row into its owner's receive buffer over NVLink, already in the order the grouped GEMM
-    wants; combine is ONE kernel that reads the experts' outputs from the owners' buffers and forms the top-k weighted
-    sum. Two symmetric-memory barriers per call order the phases; the only collective is an all-gather of the per-expert
-    counts (world x experts integers), and nothing synchronises with the host.
+    Every rank allocates a receive buffer and an output buffer of ``capacity`` rows in symmetric memory. The dispatch plan
+    is two small kernels (per-expert counts; row of every (token, k) pair in its owner's buffer), dispatch is ONE kernel
+    that writes each routed row into its owner's receive buffer over NVLink, already in the order the grouped GEMM wants;
+    combine is ONE kernel that reads the experts' outputs from the owners' buffers and forms the top-k weighted sum. Two
+    symmetric-memory barriers per call order the phases; the only collective is an all-gather of the per-expert counts
+    (world x experts integers), and nothing synchronises with the host. Rows routed beyond ``capacity`` are dropped and
+    counted in ``overflow``; the tokens they belong to lose that expert's contribution.
+
+    With one rank (no process group) the same kernels run on ordinary device buffers, without barriers or collectives.
     """
 
     def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, capacity: int, group=None):
-        import torch.distributed._symmetric_memory as symm_mem
+        import ctypes
         self.w1, self.w2, self.num_experts, self.group = w1, w2, num_experts, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        assert num_experts % self.world == 0, "experts must divide evenly over the ranks"
         hidden = w1.shape[2]
         self.capacity, self.hidden = int(capacity), hidden
-        pg = group if group is not None else dist.group.WORLD
-        self.recv = symm_mem.empty(self.capacity, hidden, dtype=w1.dtype, device=w1.device)
-        self.recv_h = symm_mem.rendezvous(self.recv, group=pg)
-        self.y = symm_mem.empty(self.capacity, hidden, dtype=w1.dtype, device=w1.device)
-        self.y_h = symm_mem.rendezvous(self.y, group=pg)
-        self.overflow = torch.zeros(1, dtype=torch.int32, device=w1.device)   # rows dropped because capacity was too small
+        dev = w1.device
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            pg = group if group is not None else dist.group.WORLD
+            self.recv = symm_mem.empty(self.capacity, hidden, dtype=w1.dtype, device=dev)
+            self.recv_h = symm_mem.rendezvous(self.recv, group=pg)
+            self.y = symm_mem.empty(self.capacity, hidden, dtype=w1.dtype, device=dev)
+            self.y_h = symm_mem.rendezvous(self.y, group=pg)
+            recv_ptrs, y_ptrs = self.recv_h.buffer_ptrs, self.y_h.buffer_ptrs
+        else:
+            self.recv = torch.empty(self.capacity, hidden, dtype=w1.dtype, device=dev)
+            self.y = torch.empty(self.capacity, hidden, dtype=w1.dtype, device=dev)
+            self.recv_h = self.y_h = None
+            recv_ptrs, y_ptrs = [self.recv.data_ptr()], [self.y.data_ptr()]
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)   # rows dropped because capacity was too small
+        self._recv_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in recv_ptrs])
+        self._y_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in y_ptrs])
+        # plan state: this rank's counts, every rank's counts, the per-expert cursor, row offsets of the local experts
+        self._counts = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self._counts_all = torch.zeros(self.world, num_experts, dtype=torch.int32, device=dev)
+        self._cursor = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self._pairs = {}       # n_pairs -> (pair_rank int32, pair_row int64)
+
+    def plan(self, topk_ids: torch.Tensor) -> PeerDispatchPlan:
+        """Device-side dispatch plan of ``topk_ids`` (tokens, topk): no sort, no host synchronisation."""
         import ctypes
-        self._recv_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.recv_h.buffer_ptrs])
-        self._y_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.y_h.buffer_ptrs])
+        from . import _lib
+        ids = topk_ids if topk_ids.is_contiguous() else topk_ids.contiguous()
+        assert ids.dtype in (torch.int32, torch.int64), "expert ids must be int32 or int64"
+        n = ids.numel()
+        if n not in self._pairs:
+            self._pairs[n] = (torch.empty(n, dtype=torch.int32, device=ids.device),
+                              torch.empty(n, dtype=torch.int64, device=ids.device))
+        pair_rank, pair_row = self._pairs[n]
+        group_offsets = torch.empty(self.num_experts // self.world + 1, dtype=torch.int32, device=ids.device)
+        stream = _lib.current_stream_ptr(ids.device)
+        is64 = int(ids.dtype == torch.int64)
+        with torch.cuda.device(ids.device):
+            rc = _lib.lib.tb_moe_count(ctypes.c_void_p(ids.data_ptr()), is64, n, self.num_experts,
+                                       ctypes.c_void_p(self._counts.data_ptr()), stream)
+            _lib.check(rc, "tb_moe_count")
+            if self.world > 1:
+                dist.all_gather_into_tensor(self._counts_all.view(-1), self._counts, group=self.group)
+                counts_all = self._counts_all
+            else:
+                counts_all = self._counts
+            rc = _lib.lib.tb_moe_plan(ctypes.c_void_p(ids.data_ptr()), is64, n, self.num_experts, self.world, self.rank,
+                                      ctypes.c_void_p(counts_all.data_ptr()), ctypes.c_void_p(self._cursor.data_ptr()),
+                                      self.capacity, ctypes.c_void_p(pair_rank.data_ptr()), ctypes.c_void_p(pair_row.data_ptr()),
+                                      ctypes.c_void_p(group_offsets.data_ptr()), stream)
+            _lib.check(rc, "tb_moe_plan")
+        return PeerDispatchPlan(None, pair_rank, pair_row, pair_rank, pair_row, group_offsets)
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor):
         import ctypes
         from . import _lib
         from .matmul import grouped_matmul
         tokens, topk = topk_ids.shape
-        mine = torch.bincount(topk_ids.reshape(-1).to(torch.int64), minlength=self.num_experts)
-        counts_all = torch.empty(self.world, self.num_experts, dtype=mine.dtype, device=mine.device)
-        dist.all_gather_into_tensor(counts_all.view(-1), mine, group=self.group)
-        plan = plan_peer_dispatch(topk_ids, counts_all, self.rank, self.capacity)
+        plan = self.plan(topk_ids)
         stream = _lib.current_stream_ptr(x.device)
         code = _lib.DTYPE_CODE[x.dtype]
         x = x if x.stride(1) == 1 else x.contiguous()
         with torch.cuda.device(x.device):
-            rc = _lib.lib.tb_moe_dispatch_peers(ctypes.c_void_p(x.data_ptr()), x.stride(0),
-                                                ctypes.c_void_p(plan.src_token.data_ptr()),
-                                                ctypes.c_void_p(plan.dest_rank.data_ptr()),
-                                                ctypes.c_void_p(plan.dest_row.data_ptr()), self._recv_ptrs, self.world,
+            rc = _lib.lib.tb_moe_dispatch_peers(ctypes.c_void_p(x.data_ptr()), x.stride(0), ctypes.c_void_p(0),
+                                                ctypes.c_void_p(plan.pair_rank.data_ptr()),
+                                                ctypes.c_void_p(plan.pair_row.data_ptr()), self._recv_ptrs, self.world,
                                                 self.recv.stride(0), self.capacity, ctypes.c_void_p(self.overflow.data_ptr()),
-                                                plan.src_token.numel(), self.hidden, code, stream)
+                                                tokens * topk, self.hidden, code, topk, stream)
         _lib.check(rc, "tb_moe_dispatch_peers")
-        self.recv_h.barrier(channel=0)                      # every rank's rows have landed in every receive buffer
+        if self.recv_h is not None:
+            self.recv_h.barrier(channel=0)                  # every rank's rows have landed in every receive buffer
         grouped_matmul(_gate_up_swiglu(grouped_matmul, self.recv, self.w1, plan.group_offsets), self.w2,
                        plan.group_offsets, out=self.y)
-        self.y_h.barrier(channel=0)                         # every rank's expert outputs are complete
+        if self.y_h is not None:
+            self.y_h.barrier(channel=0)                     # every rank's expert outputs are complete
         w = topk_weights.to(torch.float32).contiguous()
         out = x.new_empty(tokens, self.hidden)
         with torch.cuda.device(x.device):
