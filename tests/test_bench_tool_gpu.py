@@ -25,3 +25,20 @@ def test_yaml_cases_produce_csv_rows(tmp_path, flags):
     assert all(float(r["tritonblas_gflops"]) > 0 and float(r["us"]) > 0 for r in read)
     expected_mode = "streamk" if "--enable-streamk" in flags else "work_stealing" if "--work-stealing" in flags else "persistent"
     assert {r["mode"] for r in read} == {expected_mode}
+
+
+def test_selector_pick_is_close_to_the_best_configuration():
+    """The analytical selector against an exhaustive sweep of the launch space (tile width, CTA pair, wide tiles), launches
+    back to back: the picked configuration's time is within 10 % of the best one's on shapes of the headline families
+    (the committed sweep of the full-size shapes is summarised under profiles/; this test keeps the shapes small enough
+    to run in seconds)."""
+    from tritonblas_b200 import sweep
+    sweep._MODE["steady"] = True
+    try:
+        for m, n, k, dt, sk in [(4096, 4096, 4096, "bf16", False), (2048, 8192, 8192, "bf16", False),
+                                (2048, 7168, 4096, "fp8", False), (16, 28672, 8192, "bf16", True)]:
+            rows, eff = sweep.sweep_tiles(m, n, k, dt, sk, warmup=3, repeats=10)
+            assert len(rows) >= 2
+            assert eff >= 0.90, (m, n, k, dt, sk, eff, [(r["cta_pair"], r["block_n"], r["n_halves"], r["us"]) for r in rows])
+    finally:
+        sweep._MODE["steady"] = False
