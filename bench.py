@@ -473,16 +473,21 @@ class MoeWorkload:
         gl = torch.Generator().manual_seed(1000 + rank)
         self.x_host = torch.randn(self.t_local, H, generator=gl).to(torch.bfloat16).pin_memory()
         self.x, self.ids = self.x_host.to(dev), self.ids_host.to(dev)
-        mine = [_expert_weights(e, H, F, dev) for e in range(rank * epr, (rank + 1) * epr)]
+        # Expert placement: balanced over the ranks by the per-expert load of the routing table (greedy, equal number of
+        # experts per rank); with the contiguous layout one rank of eight holds twice the mean rows under this Zipf routing.
+        load = torch.bincount(ids_all.flatten(), minlength=E)
+        place = tbd.balanced_expert_placement(load, world) if (world > 1 and not args.contiguous_experts) else None
+        layout = torch.arange(E) if place is None else torch.argsort(place.long())     # layout position -> expert id
+        mine = [_expert_weights(int(e), H, F, dev) for e in layout[rank * epr:(rank + 1) * epr]]
         w1 = torch.stack([m[0] for m in mine])
         w2 = torch.stack([m[1] for m in mine])
         del mine
         if nccl:
-            self.moe = tbd.ExpertParallelMoE(w1, w2, E, None)
+            self.moe = tbd.ExpertParallelMoE(w1, w2, E, None, expert_place=None if place is None else place.to(dev))
         else:
             # device-side plan, one dispatch and one combine kernel; on several GPUs the rows travel over peer-mapped
             # memory (two barriers), on one GPU the same kernels run on local buffers
-            self.moe = tbd.PeerMemoryMoE(w1, w2, E, capacity=T * topk)
+            self.moe = tbd.PeerMemoryMoE(w1, w2, E, capacity=T * topk, expert_place=place)
         self.path = "local" if world == 1 else ("nccl" if nccl else "peer")
         self.out_host = torch.empty(self.t_local, H, dtype=torch.bfloat16).pin_memory()
         rows = T * topk
@@ -490,13 +495,14 @@ class MoeWorkload:
         self.kernel_flops = self.flops / world
         self.kernel_bytes = 0
         self.h2d, self.d2h = self.t_local * H * 2 + self.t_local * topk * 8, self.t_local * H * 2
-        self.rows_per_rank = torch.bincount(ids_all.flatten(), minlength=E).reshape(world, epr).sum(1).tolist()
+        self.rows_per_rank = load[layout].reshape(world, epr).sum(1).tolist()
+        self.placement = "contiguous" if place is None else "balanced by expert load (greedy, equal experts per rank)"
         self.label = (f"grouped MoE GEMM bf16: {E} experts, top-{topk} of {T} tokens, hidden {H}, ffn {F}, gate/up + down "
                       f"projections, Zipf(1.1) routing (seeded), SwiGLU between (fused into the gate/up epilogue, outside "
                       f"the FLOP count)")
         self.extra = {"parallelism": (f"expert-parallel x{world}, " + ("dispatch/combine kernels over NVLink peer memory"
                                       if self.path == "peer" else "NCCL all-to-all dispatch/combine")) if world > 1
-                      else "single GPU", "rows_per_rank": self.rows_per_rank}
+                      else "single GPU", "rows_per_rank": self.rows_per_rank, "expert_placement": self.placement}
 
     def step(self, i, dist):
         return self.moe.forward(self.x, self.ids, self.wts)[0]
@@ -641,7 +647,7 @@ def moe_block(args, run, nccl):
     total, unit, ck, launches = run.timed(lambda i: w.step(i, run.dist), 3, n, clocks=run.world == 1)
     ok, err = run.all_ok(*w.parity_check(run.dist))
     out = {"value": w.flops * n / (total * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": total / n, "steps": n,
-           "rows_per_rank": w.rows_per_rank, "path": w.path, "gpu_launches": launches,
+           "rows_per_rank": w.rows_per_rank, "expert_placement": w.placement, "path": w.path, "gpu_launches": launches,
            "parity_check": {"ok": ok, "max_err": err, "ranks_checked": run.world, "tokens_per_rank": 64,
                             "tolerance": "2e-2 * (|ref| + rms(ref)) + one bf16 ulp of max|ref| against the CPU oracle"},
            "frac_of_nominal_dense": w.flops * n / (total * 1e-3) / 1e12 / (NOMINAL_TFLOPS["bf16"] * run.world)}
@@ -666,6 +672,8 @@ def main():
                     help="default workload: skip the MoE, sustained, cuBLAS and per-workload blocks (profiling runs)")
     ap.add_argument("--nccl-moe", action="store_true",
                     help="moe workload on several GPUs: NCCL all-to-all dispatch/combine instead of the peer-memory kernels")
+    ap.add_argument("--contiguous-experts", action="store_true",
+                    help="MoE on several GPUs: experts laid out over the ranks in id order instead of balanced by load")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="multi-GPU default workload: gather C with NCCL after the GEMM instead of the fused epilogue push")
     args = ap.parse_args()

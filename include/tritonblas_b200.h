@@ -208,18 +208,22 @@ int tb_moe_combine_peers(void* const* y_peers, int32_t num_peers, int64_t y_row_
 
 /* Dispatch plan of the expert-parallel MoE step, computed on the device (no host synchronisation, no sort). No reference
  * counterpart. topk_ids: n_pairs expert ids of the flattened (token, k) pairs, int32 or int64 (ids_are_int64).
- *   tb_moe_count: counts[e] = pairs routed to expert e (counts, int32[num_experts], is cleared by the call).
+ * expert_place (device int32[num_experts], or NULL for the identity) gives every expert id its position q in the order
+ * the experts are laid out over the ranks: position q lives on rank q / (num_experts / world) as that rank's local expert
+ * q % (num_experts / world). A placement that spreads the popular experts evens out the rows per rank. Counts, offsets and
+ * rows below are all in placement order.
+ *   tb_moe_count: counts[q] = pairs routed to the expert at position q (counts, int32[num_experts], is cleared by the call).
  *   tb_moe_plan:  counts_all is int32[world][num_experts], every rank's counts (for one GPU: the counts themselves).
- *                 Expert e lives on rank e / (num_experts / world); in its owner's receive buffer the experts follow each
- *                 other and inside an expert the source ranks follow each other. Writes, for every pair f of this rank,
+ *                 In its owner's receive buffer the experts follow each other in placement order
+ *                 and inside an expert the source ranks follow each other. Writes, for every pair f of this rank,
  *                 pair_rank[f] (owner) and pair_row[f] (row in the owner's buffer; -1 for an id outside [0, num_experts)),
  *                 and group_offsets[num_experts / world + 1], the row offsets of this rank's own experts clamped to
  *                 capacity_rows. cursor is int32[num_experts] scratch (cleared by the call). The order of the rows inside
  *                 an expert is unspecified; num_experts <= 1024. */
-int tb_moe_count(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts, int32_t* counts,
-                 void* stream);
-int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts, int32_t world, int32_t rank,
-                const int32_t* counts_all, int32_t* cursor, int64_t capacity_rows, int32_t* pair_rank, int64_t* pair_row,
+int tb_moe_count(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts,
+                 const int32_t* expert_place, int32_t* counts, void* stream);
+int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts, const int32_t* expert_place,
+                int32_t world, int32_t rank, const int32_t* counts_all, int32_t* cursor, int64_t capacity_rows, int32_t* pair_rank, int64_t* pair_row,
                 int32_t* group_offsets, void* stream);
 
 /* MXFP4 GEMM: C (m, n) = sum over 32-element K blocks of (A_e2m1 * 2^(sa-127)) . (B_e2m1 * 2^(sb-127)), fp32

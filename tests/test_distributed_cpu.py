@@ -148,6 +148,29 @@ def test_peer_dispatch_plan_clamps_group_offsets_to_capacity():
     assert dropped == 17 * world
 
 
+def test_balanced_expert_placement_evens_out_the_rows_per_rank():
+    E, topk, T = 64, 8, 4096
+    g = torch.Generator().manual_seed(77)
+    p = torch.arange(1, E + 1, dtype=torch.float64) ** -1.1
+    p = (p / p.sum())[torch.randperm(E, generator=g)]
+    ids = torch.multinomial(p.expand(T, E), topk, replacement=False, generator=g)
+    load = torch.bincount(ids.flatten(), minlength=E)
+    for world in (2, 4, 8):
+        place = tbd.balanced_expert_placement(load, world)
+        epr = E // world
+        assert sorted(place.tolist()) == list(range(E))
+        per_rank = torch.zeros(world, dtype=torch.int64).index_add_(0, (place // epr).long(), load)
+        contiguous = load.reshape(world, epr).sum(1)
+        mean = load.sum().item() / world
+        assert per_rank.max().item() <= contiguous.max().item()
+        assert per_rank.max().item() / mean < 1.25
+    # the single-rank plan honours a placement: experts appear in layout order
+    place = tbd.balanced_expert_placement(load, 8)
+    plan = tbd.plan_dispatch(ids[:50], E, expert_place=place)
+    placed = place.long()[ids[:50].flatten()]
+    assert plan.group_offsets.tolist() == [0] + torch.bincount(placed, minlength=E).cumsum(0).tolist()
+
+
 def test_bench_matmul_csv_schema(tmp_path):
     """The YAML/CSV benchmark tool writes the reference's column set (benchmarks/tritonblas_matmul.py:278-291)."""
     from tritonblas_b200 import bench_matmul as bm

@@ -35,7 +35,7 @@ def test_plan_kernels_match_the_index_arithmetic_specification(world, E, T, topk
     counts_all = torch.zeros(world, E, dtype=torch.int32, device="cuda")
     for r in range(world):
         counts_all[r].fill_(-7)          # the call clears its output
-        _lib.check(lib.tb_moe_count(ctypes.c_void_p(ids[r].data_ptr()), int(dtype == torch.int64), T * topk, E,
+        _lib.check(lib.tb_moe_count(ctypes.c_void_p(ids[r].data_ptr()), int(dtype == torch.int64), T * topk, E, None,
                                     ctypes.c_void_p(counts_all[r].data_ptr()), stream), "tb_moe_count")
         assert torch.equal(counts_all[r].cpu().long(), torch.bincount(ids[r].flatten().cpu().long(), minlength=E))
     epr = E // world
@@ -48,7 +48,7 @@ def test_plan_kernels_match_the_index_arithmetic_specification(world, E, T, topk
         offs = torch.empty(epr + 1, dtype=torch.int32, device="cuda")
         cursor = torch.full((E,), 123, dtype=torch.int32, device="cuda")
         for _ in range(2):               # the cursor is cleared by the call: a second call gives a valid plan again
-            _lib.check(lib.tb_moe_plan(ctypes.c_void_p(ids[r].data_ptr()), int(dtype == torch.int64), T * topk, E, world, r,
+            _lib.check(lib.tb_moe_plan(ctypes.c_void_p(ids[r].data_ptr()), int(dtype == torch.int64), T * topk, E, None, world, r,
                                        ctypes.c_void_p(counts_all.data_ptr()), ctypes.c_void_p(cursor.data_ptr()), cap,
                                        ctypes.c_void_p(pair_rank.data_ptr()), ctypes.c_void_p(pair_row.data_ptr()),
                                        ctypes.c_void_p(offs.data_ptr()), stream), "tb_moe_plan")
@@ -117,3 +117,29 @@ def test_capacity_below_the_routing_drops_rows_without_reaching_past_the_buffers
     rms = ref.pow(2).mean().sqrt().item()
     assert bool(((got - ref).abs() <= 2e-2 * ref.abs() + 2e-2 * rms + 2 ** -8 * ref.abs().max()).all())
     assert torch.isfinite(out.float()).all() and tb.device_status() == 0
+
+
+def test_balanced_placement_single_gpu_results_do_not_depend_on_the_layout_order():
+    """expert_place permutes where experts live (and the order of this rank's weights); the MoE output is the same
+    function of the tokens, so it matches the oracle evaluated with the experts' own weights."""
+    E, H, F, T, topk = 16, 256, 128, 300, 4
+    w1, w2 = _experts(E, H, F, 21)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+    ids = _zipf_ids(T, E, topk, 13).cuda()
+    wts = torch.rand(T, topk, generator=g).cuda()
+    load = torch.bincount(ids.flatten().cpu(), minlength=E)
+    place = tbd.balanced_expert_placement(load, 4)
+    assert sorted(place.tolist()) == list(range(E))
+    per_rank = torch.zeros(4, dtype=torch.int64).index_add_(0, (place // (E // 4)).long(), load)
+    contiguous = load.reshape(4, -1).sum(1)
+    assert per_rank.max() <= contiguous.max()
+    inv = torch.empty(E, dtype=torch.int64)
+    inv[place.long()] = torch.arange(E)
+    moe = tbd.PeerMemoryMoE(w1[inv.cuda()].contiguous(), w2[inv.cuda()].contiguous(), E, capacity=T * topk, expert_place=place)
+    out, _ = moe.forward(x, ids, wts)
+    toks = list(range(0, T, 7))
+    ref = moe_oracle.moe_ffn_ref(x, ids, wts, lambda e: w1[e], lambda e: w2[e], toks)
+    got = out[torch.tensor(toks, device="cuda")].float().cpu()
+    rms = ref.pow(2).mean().sqrt().item()
+    assert bool(((got - ref).abs() <= 2e-2 * ref.abs() + 2e-2 * rms + 2 ** -8 * ref.abs().max()).all())

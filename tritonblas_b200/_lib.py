@@ -102,10 +102,10 @@ def _load():
                                           ctypes.c_void_p]
     lib.tb_moe_dispatch_peers.restype = ctypes.c_int
     lib.tb_moe_count.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p,
-                                 ctypes.c_void_p]
+                                 ctypes.c_void_p, ctypes.c_void_p]
     lib.tb_moe_count.restype = ctypes.c_int
-    lib.tb_moe_plan.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
-                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
+    lib.tb_moe_plan.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int32,
+                                ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
                                 ctypes.c_void_p, ctypes.c_void_p]
     lib.tb_moe_plan.restype = ctypes.c_int
     lib.tb_moe_combine_peers.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p,

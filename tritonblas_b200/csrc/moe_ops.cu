@@ -343,12 +343,17 @@ constexpr int kPlanThreads = 256;
 constexpr int kPlanItems = 4;       // pairs per thread
 constexpr int kPlanMaxExperts = 1024;
 
-__device__ __forceinline__ int expert_of(const void* ids, int is64, long long f) {
-  return is64 ? static_cast<int>(static_cast<const long long*>(ids)[f]) : static_cast<const int*>(ids)[f];
+// Expert of pair f in placement order: `place` (or the identity) maps an expert id to its position in the sequence of
+// experts as they are laid out over the ranks (position q lives on rank q / experts_per_rank as its local expert
+// q % experts_per_rank). -1 for an id outside [0, E).
+__device__ __forceinline__ int expert_of(const void* ids, int is64, long long f, const int* place, int E) {
+  const long long e = is64 ? static_cast<const long long*>(ids)[f] : static_cast<long long>(static_cast<const int*>(ids)[f]);
+  if (e < 0 || e >= E) return -1;
+  return place != nullptr ? place[e] : static_cast<int>(e);
 }
 
 __global__ void __launch_bounds__(kPlanThreads) moe_count_kernel(const void* __restrict__ ids, int is64, long long n, int E,
-                                                                  int* __restrict__ counts) {
+                                                                  const int* __restrict__ place, int* __restrict__ counts) {
   __shared__ int hist[kPlanMaxExperts];
   for (int e = threadIdx.x; e < E; e += kPlanThreads) hist[e] = 0;
   __syncthreads();
@@ -357,7 +362,7 @@ __global__ void __launch_bounds__(kPlanThreads) moe_count_kernel(const void* __r
   for (int i = 0; i < kPlanItems; ++i) {
     const long long f = base + i * kPlanThreads + threadIdx.x;
     if (f < n) {
-      const int e = expert_of(ids, is64, f);
+      const int e = expert_of(ids, is64, f, place, E);
       if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
     }
   }
@@ -367,7 +372,8 @@ __global__ void __launch_bounds__(kPlanThreads) moe_count_kernel(const void* __r
 }
 
 __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const void* __restrict__ ids, int is64, long long n, int E,
-                                                                 int world, int rank, const int* __restrict__ counts_all,
+                                                                 const int* __restrict__ place, int world, int rank,
+                                                                 const int* __restrict__ counts_all,
                                                                  int* __restrict__ cursor, long long capacity,
                                                                  int* __restrict__ pair_rank, long long* __restrict__ pair_row,
                                                                  int* __restrict__ group_offsets) {
@@ -411,7 +417,7 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const void* __re
     ex[i] = -1;
     local[i] = 0;
     if (f < n) {
-      const int e = expert_of(ids, is64, f);
+      const int e = expert_of(ids, is64, f, place, E);
       if (e >= 0 && e < E) {
         ex[i] = e;
         local[i] = atomicAdd(&hist[e], 1);
@@ -436,8 +442,8 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const void* __re
 }  // namespace
 }  // namespace tb
 
-extern "C" int tb_moe_count(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts, int32_t* counts,
-                            void* stream) {
+extern "C" int tb_moe_count(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts,
+                            const int32_t* expert_place, int32_t* counts, void* stream) {
   if (topk_ids == nullptr || counts == nullptr || n_pairs < 0 || num_experts < 1 || num_experts > tb::kPlanMaxExperts)
     return TB_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -446,15 +452,15 @@ extern "C" int tb_moe_count(const void* topk_ids, int32_t ids_are_int64, int64_t
   if (n_pairs == 0) return TB_OK;
   const long long per_block = tb::kPlanThreads * tb::kPlanItems;
   const unsigned blocks = static_cast<unsigned>((n_pairs + per_block - 1) / per_block);
-  tb::moe_count_kernel<<<blocks, tb::kPlanThreads, 0, st>>>(topk_ids, ids_are_int64, n_pairs, num_experts, counts);
+  tb::moe_count_kernel<<<blocks, tb::kPlanThreads, 0, st>>>(topk_ids, ids_are_int64, n_pairs, num_experts, expert_place, counts);
   e = cudaGetLastError();
   if (e != cudaSuccess) return tb::cuda_fail(e, "moe_count_kernel launch");
   tb::g_launches.fetch_add(1, std::memory_order_relaxed);
   return TB_OK;
 }
 
-extern "C" int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts, int32_t world,
-                           int32_t rank, const int32_t* counts_all, int32_t* cursor, int64_t capacity_rows,
+extern "C" int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts,
+                           const int32_t* expert_place, int32_t world, int32_t rank, const int32_t* counts_all, int32_t* cursor, int64_t capacity_rows,
                            int32_t* pair_rank, int64_t* pair_row, int32_t* group_offsets, void* stream) {
   if (topk_ids == nullptr || counts_all == nullptr || cursor == nullptr || pair_rank == nullptr || pair_row == nullptr ||
       group_offsets == nullptr)
@@ -467,8 +473,8 @@ extern "C" int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t 
   if (e != cudaSuccess) return tb::cuda_fail(e, "cudaMemsetAsync(cursor)");
   const long long per_block = tb::kPlanThreads * tb::kPlanItems;
   const unsigned blocks = static_cast<unsigned>(n_pairs > 0 ? (n_pairs + per_block - 1) / per_block : 1);
-  tb::moe_plan_kernel<<<blocks, tb::kPlanThreads, 0, st>>>(topk_ids, ids_are_int64, n_pairs, num_experts, world, rank, counts_all,
-                                                          cursor, capacity_rows, pair_rank,
+  tb::moe_plan_kernel<<<blocks, tb::kPlanThreads, 0, st>>>(topk_ids, ids_are_int64, n_pairs, num_experts, expert_place, world, rank,
+                                                          counts_all, cursor, capacity_rows, pair_rank,
                                                           reinterpret_cast<long long*>(pair_row), group_offsets);
   e = cudaGetLastError();
   if (e != cudaSuccess) return tb::cuda_fail(e, "moe_plan_kernel launch");

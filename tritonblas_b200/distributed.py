@@ -109,12 +109,37 @@ class DispatchPlan:
     pos: Optional[torch.Tensor] = None           # position of every (token, k) pair in expert order (inverse of sort_idx)
 
 
-def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None) -> DispatchPlan:
-    """Sort the (token, k) pairs of this rank by expert and exchange per-expert row counts with the other ranks."""
+def balanced_expert_placement(expert_load, world: int) -> torch.Tensor:
+    """Placement of the experts over ``world`` ranks that evens out the rows per rank: ``place[e]`` is expert e's position
+    in the layout order (position q lives on rank q // experts_per_rank as local expert q % experts_per_rank).
+
+    ``expert_load``: rows per expert observed on a calibration batch (any non-negative weights). Greedy longest-processing-
+    time assignment with equal cardinality: experts in descending load order each go to the least loaded rank that still
+    has a free slot. With a skewed (Zipf) routing distribution the contiguous layout can put several popular experts on one
+    rank, whose grouped GEMMs then take a multiple of the mean time; every rank waits for it."""
+    load = torch.as_tensor(expert_load).detach().cpu().to(torch.float64).reshape(-1)
+    E = load.numel()
+    assert E % world == 0, "experts must divide evenly over the ranks"
+    epr = E // world
+    rank_load, rank_fill = [0.0] * world, [0] * world
+    place = torch.empty(E, dtype=torch.int32)
+    for e in torch.argsort(load, descending=True, stable=True).tolist():
+        r = min((r for r in range(world) if rank_fill[r] < epr), key=lambda q: (rank_load[q], q))
+        place[e] = r * epr + rank_fill[r]
+        rank_fill[r] += 1
+        rank_load[r] += float(load[e])
+    return place
+
+
+def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None, expert_place: Optional[torch.Tensor] = None) -> DispatchPlan:
+    """Sort the (token, k) pairs of this rank by expert and exchange per-expert row counts with the other ranks.
+    ``expert_place`` maps expert ids to their position in the layout order (see balanced_expert_placement)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     assert num_experts % world == 0, "experts must divide evenly over the ranks"
     epr = num_experts // world
     flat = topk_ids.reshape(-1).to(torch.int64)
+    if expert_place is not None:
+        flat = expert_place.to(flat.device).to(torch.int64)[flat]
     sort_idx = torch.argsort(flat, stable=True)
     send_counts = torch.bincount(flat, minlength=num_experts).reshape(world, epr)
     if world > 1:
@@ -240,14 +265,16 @@ class ExpertParallelMoE:
     w1: (experts_per_rank, 2*ffn, hidden) and w2: (experts_per_rank, hidden, ffn) hold this rank's experts, K-contiguous.
     """
 
-    def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, group=None, grouped_fn: Optional[Callable] = None):
+    def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, group=None, grouped_fn: Optional[Callable] = None,
+                 expert_place: Optional[torch.Tensor] = None):
         self.w1, self.w2, self.num_experts, self.group = w1, w2, num_experts, group
+        self.expert_place = expert_place        # expert id -> position in the layout order; w1 / w2 follow that order
         if grouped_fn is None:
             from .matmul import grouped_matmul as grouped_fn
         self.grouped_fn = grouped_fn
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor):
-        plan = plan_dispatch(topk_ids, self.num_experts, self.group)
+        plan = plan_dispatch(topk_ids, self.num_experts, self.group, self.expert_place)
         rows = dispatch(x, topk_ids.shape[1], plan, self.group)
         y = self.grouped_fn(_gate_up_swiglu(self.grouped_fn, rows, self.w1, plan.group_offsets), self.w2, plan.group_offsets)
         return combine(y, topk_weights, plan, self.group), plan
@@ -324,7 +351,8 @@ class PeerMemoryMoE:
     With one rank (no process group) the same kernels run on ordinary device buffers, without barriers or collectives.
     """
 
-    def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, capacity: int, group=None):
+    def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, capacity: int, group=None,
+                 expert_place: Optional[torch.Tensor] = None):
         import ctypes
         self.w1, self.w2, self.num_experts, self.group = w1, w2, num_experts, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -354,6 +382,10 @@ class PeerMemoryMoE:
         self._counts_all = torch.zeros(self.world, num_experts, dtype=torch.int32, device=dev)
         self._cursor = torch.zeros(num_experts, dtype=torch.int32, device=dev)
         self._pairs = {}       # n_pairs -> (pair_rank int32, pair_row int64)
+        # expert id -> position in the layout order (w1 / w2 hold this rank's experts in that order); None = identity
+        self._place = None if expert_place is None else expert_place.to(device=dev, dtype=torch.int32).contiguous()
+        if self._place is not None:
+            assert self._place.numel() == num_experts and sorted(self._place.tolist()) == list(range(num_experts))
 
     def plan(self, topk_ids: torch.Tensor) -> PeerDispatchPlan:
         """Device-side dispatch plan of ``topk_ids`` (tokens, topk): no sort, no host synchronisation."""
@@ -370,7 +402,8 @@ class PeerMemoryMoE:
         stream = _lib.current_stream_ptr(ids.device)
         is64 = int(ids.dtype == torch.int64)
         with torch.cuda.device(ids.device):
-            rc = _lib.lib.tb_moe_count(ctypes.c_void_p(ids.data_ptr()), is64, n, self.num_experts,
+            place = ctypes.c_void_p(self._place.data_ptr() if self._place is not None else 0)
+            rc = _lib.lib.tb_moe_count(ctypes.c_void_p(ids.data_ptr()), is64, n, self.num_experts, place,
                                        ctypes.c_void_p(self._counts.data_ptr()), stream)
             _lib.check(rc, "tb_moe_count")
             if self.world > 1:
@@ -378,7 +411,7 @@ class PeerMemoryMoE:
                 counts_all = self._counts_all
             else:
                 counts_all = self._counts
-            rc = _lib.lib.tb_moe_plan(ctypes.c_void_p(ids.data_ptr()), is64, n, self.num_experts, self.world, self.rank,
+            rc = _lib.lib.tb_moe_plan(ctypes.c_void_p(ids.data_ptr()), is64, n, self.num_experts, place, self.world, self.rank,
                                       ctypes.c_void_p(counts_all.data_ptr()), ctypes.c_void_p(self._cursor.data_ptr()),
                                       self.capacity, ctypes.c_void_p(pair_rank.data_ptr()), ctypes.c_void_p(pair_row.data_ptr()),
                                       ctypes.c_void_p(group_offsets.data_ptr()), stream)
