@@ -156,6 +156,15 @@ def cpu_reference_tflops(M, N, K, dtype, target_seconds, seed=0):
     return 2.0 * rows2 * N * K / dt / 1e12, rows2, total
 
 
+def dense_label(wl):
+    M, N, K = wl["M"], wl["N"], wl["K"]
+    fp8 = wl["dtype"] == "fp8"
+    return (f"{wl['dtype']} GEMM M={M} N={N} K={K} TN layout, fp32 accumulate, "
+            f"{'bf16' if fp8 else wl['dtype']} out, inputs N(0,1)*0.02"
+            + (", per-token x per-channel e4m3 scales in the epilogue" if fp8 else "")
+            + (", stream-K" if wl["streamk"] else ""))
+
+
 def run_reference(args, wl, rank):
     if rank != 0:
         return
@@ -175,8 +184,11 @@ def run_reference(args, wl, rank):
         "impl": "reference", "metric": "gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(s[1] for s in samples) / len(samples),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-        "config": {"workload": f"{args.workload}: GEMM M={M} N={N} K={K}, reference semantics (fp32-accumulate "
-                               f"torch.matmul) on the host cores"},
+        # the same workload as the other arm (same name and description); how this arm runs it is said under "arm"
+        "config": {"workload": f"{args.workload}: " + (dense_label(wl) if args.workload != "moe" and wl["dtype"] != "mxfp4"
+                                                        else f"GEMM M={M} N={N} K={K}"),
+                   "gemms_per_step": args.gemms_per_step if args.workload != "moe" else 1,
+                   "arm": "reference semantics (fp32-accumulate torch.matmul, one cast) on the host cores, bounded row sample"},
         "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": f"{samples[-1][2]} of {M} rows of A per step against the full B"},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -258,10 +270,7 @@ class DenseWorkload:
         self.kernel_bytes = es * (M * K + K * self.n_local) + 2 * M * self.n_local + (4 * (M + self.n_local) if self.fp8 else 0)
         self.h2d = es * (M * K + self.n_local * K)
         self.d2h = 2 * M * self.n_local
-        self.label = (f"{wl['dtype']} GEMM M={M} N={N} K={K} TN layout, fp32 accumulate, "
-                      f"{'bf16' if self.fp8 else wl['dtype']} out, inputs N(0,1)*0.02"
-                      + (", per-token x per-channel e4m3 scales in the epilogue" if self.fp8 else "")
-                      + (", stream-K" if self.streamk else ""))
+        self.label = dense_label(wl)
         self.extra = {"tile": f"{self.sel.block_m}x{self.sel.block_n}x{self.sel.block_k}", "cta_pair": self.sel.cta_pair,
                       "operand_sets": nsets,
                       "parallelism": (f"N-sharded x{world}, " + ("epilogue pushes C tiles to all ranks over NVLink "

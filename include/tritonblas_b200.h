@@ -137,6 +137,11 @@ typedef struct tb_gemm_args {
    * bounded waits run out (RESULTS ARE WRONG; the failure-path test uses it). Bit 3 (value 8): every work item walks K
    * forwards. */
   int32_t debug_flags;
+  /* Row gather (tb_grouped_gemm only; no reference counterpart): DEVICE int32[m], or NULL. Row r of the grouped problem is
+   * then row a_gather_index[r] of the matrix `a` (any number of rows, a_stride_m apart, K contiguous, 16-bit elements, rows
+   * starting on 16-byte boundaries); a negative entry reads as a row of zeros. The MoE gate/up projection reads the tokens'
+   * rows in expert order straight from the activation matrix this way, with no gathered copy in between. */
+  const int32_t* a_gather_index;
 } tb_gemm_args;
 
 /* Fill `cfg` for `p`. Stands in for origami.select_config + OrigamiMatmulSelector._compute_sk_grid
@@ -219,12 +224,13 @@ int tb_moe_combine_peers(void* const* y_peers, int32_t num_peers, int64_t y_row_
  *                 pair_rank[f] (owner) and pair_row[f] (row in the owner's buffer; -1 for an id outside [0, num_experts)),
  *                 and group_offsets[num_experts / world + 1], the row offsets of this rank's own experts clamped to
  *                 capacity_rows. cursor is int32[num_experts] scratch (cleared by the call). The order of the rows inside
- *                 an expert is unspecified; num_experts <= 1024. */
+ *                 an expert is unspecified; num_experts <= 1024. row_token (world == 1 only, else NULL): int32[capacity_rows],
+ *                 receives the source token (pair index / topk) of every row, the index tb_gemm_args.a_gather_index takes. */
 int tb_moe_count(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts,
                  const int32_t* expert_place, int32_t* counts, void* stream);
 int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts, const int32_t* expert_place,
-                int32_t world, int32_t rank, const int32_t* counts_all, int32_t* cursor, int64_t capacity_rows, int32_t* pair_rank, int64_t* pair_row,
-                int32_t* group_offsets, void* stream);
+                int32_t world, int32_t rank, const int32_t* counts_all, int32_t* cursor, int64_t capacity_rows,
+                int32_t* pair_rank, int64_t* pair_row, int32_t* group_offsets, int32_t* row_token, int32_t topk, void* stream);
 
 /* MXFP4 GEMM: C (m, n) = sum over 32-element K blocks of (A_e2m1 * 2^(sa-127)) . (B_e2m1 * 2^(sb-127)), fp32
  * accumulate, one cast. A is (m, k/2) bytes and B is (n, k/2) bytes, two e2m1 codes per byte (even element in the low

@@ -51,7 +51,7 @@ def test_plan_kernels_match_the_index_arithmetic_specification(world, E, T, topk
             _lib.check(lib.tb_moe_plan(ctypes.c_void_p(ids[r].data_ptr()), int(dtype == torch.int64), T * topk, E, None, world, r,
                                        ctypes.c_void_p(counts_all.data_ptr()), ctypes.c_void_p(cursor.data_ptr()), cap,
                                        ctypes.c_void_p(pair_rank.data_ptr()), ctypes.c_void_p(pair_row.data_ptr()),
-                                       ctypes.c_void_p(offs.data_ptr()), stream), "tb_moe_plan")
+                                       ctypes.c_void_p(offs.data_ptr()), None, topk, stream), "tb_moe_plan")
         assert offs.cpu().tolist() == spec.group_offsets.tolist()
         assert torch.equal(pair_rank.cpu(), spec.pair_rank)
         # same rows as the specification per expert, in any order

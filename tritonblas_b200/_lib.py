@@ -55,6 +55,7 @@ class GemmArgs(ctypes.Structure):
         ("c_copies", ctypes.POINTER(ctypes.c_void_p)), ("num_c_copies", ctypes.c_int32),
         ("tile_counter", ctypes.c_void_p), ("epilogue_op", ctypes.c_int32),
         ("wait_timeout_ms", ctypes.c_int32), ("debug_flags", ctypes.c_int32),
+        ("a_gather_index", ctypes.c_void_p),
     ]
 
 
@@ -106,7 +107,7 @@ def _load():
     lib.tb_moe_count.restype = ctypes.c_int
     lib.tb_moe_plan.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int32,
                                 ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
-                                ctypes.c_void_p, ctypes.c_void_p]
+                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
     lib.tb_moe_plan.restype = ctypes.c_int
     lib.tb_moe_combine_peers.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p,
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,

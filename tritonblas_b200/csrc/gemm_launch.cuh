@@ -23,19 +23,31 @@ template <int KIND, int CTAS>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const GemmParams& p, int programs, int smem_bytes,
                 cudaStream_t stream, const CUtensorMap* tsfa, const CUtensorMap* tsfb) {
   auto kernel = gemm_kernel<KIND, CTAS, false>;
-  // The instantiation with per-role cycle counters exists for 16-bit operands only (measurement runs).
+  int variant = 0;
+  bool gather = false;
+  // The instantiations with per-role cycle counters (measurement runs) and with a row-gathering A loader (grouped
+  // launches whose rows are picked from another matrix by index) exist for 16-bit operands only.
   if constexpr (KIND == 0) {
-    if ((p.debug_flags & 2) && p.debug_out != nullptr) kernel = gemm_kernel<KIND, CTAS, true>;
+    if (p.a_gather != nullptr) {
+      kernel = gemm_kernel<KIND, CTAS, false, true>;
+      variant = 2;
+      gather = true;
+    } else if ((p.debug_flags & 2) && p.debug_out != nullptr) {
+      kernel = gemm_kernel<KIND, CTAS, true>;
+      variant = 1;
+    }
+  } else if (p.a_gather != nullptr) {
+    return TB_ERR_UNSUPPORTED;
   }
   // The opt-in shared-memory size is set once per kernel instantiation and device (and again if a launch needs more).
-  static int configured[2][64] = {};
+  static int configured[3][64] = {};
   static std::mutex configured_mu;
   int dev_index = 0;
   cudaGetDevice(&dev_index);
   cudaError_t e = cudaSuccess;
   {
     std::lock_guard<std::mutex> lk(configured_mu);
-    int& have = configured[kernel == gemm_kernel<KIND, CTAS, false> ? 0 : 1][dev_index & 63];
+    int& have = configured[variant][dev_index & 63];
     if (smem_bytes > have) {
       e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
       if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
@@ -44,7 +56,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const GemmParams&
   }
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(static_cast<unsigned>(programs * CTAS), 1, 1);
-  lc.blockDim = dim3(gemm_threads<KIND>(), 1, 1);
+  lc.blockDim = dim3(gemm_threads<KIND>(gather), 1, 1);
   lc.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   lc.stream = stream;
   cudaLaunchAttribute attr[2];

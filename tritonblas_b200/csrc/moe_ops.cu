@@ -376,7 +376,8 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const void* __re
                                                                  const int* __restrict__ counts_all,
                                                                  int* __restrict__ cursor, long long capacity,
                                                                  int* __restrict__ pair_rank, long long* __restrict__ pair_row,
-                                                                 int* __restrict__ group_offsets) {
+                                                                 int* __restrict__ group_offsets, int* __restrict__ row_token,
+                                                                 int topk) {
   __shared__ int total[kPlanMaxExperts];      // rows of expert e over all source ranks
   __shared__ long long dest[kPlanMaxExperts]; // first row of this rank's pairs of expert e in the owner's buffer
   __shared__ int hist[kPlanMaxExperts];
@@ -433,8 +434,11 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const void* __re
     if (f < n) {
       const int e = ex[i];
       // an expert id outside [0, E) routes nowhere: row -1 is dropped by the dispatch and skipped by the combine
+      const long long row = e >= 0 ? dest[e] + block_base[e] + local[i] : -1;
       pair_rank[f] = e >= 0 ? e / epr : 0;
-      pair_row[f] = e >= 0 ? dest[e] + block_base[e] + local[i] : -1;
+      pair_row[f] = row;
+      // single rank: the inverse map, source token of every row, for a grouped GEMM that gathers its rows by index
+      if (row_token != nullptr && row >= 0 && row < capacity) row_token[row] = static_cast<int>(f / topk);
     }
   }
 }
@@ -461,12 +465,13 @@ extern "C" int tb_moe_count(const void* topk_ids, int32_t ids_are_int64, int64_t
 
 extern "C" int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, int32_t num_experts,
                            const int32_t* expert_place, int32_t world, int32_t rank, const int32_t* counts_all, int32_t* cursor, int64_t capacity_rows,
-                           int32_t* pair_rank, int64_t* pair_row, int32_t* group_offsets, void* stream) {
+                           int32_t* pair_rank, int64_t* pair_row, int32_t* group_offsets, int32_t* row_token, int32_t topk,
+                           void* stream) {
   if (topk_ids == nullptr || counts_all == nullptr || cursor == nullptr || pair_rank == nullptr || pair_row == nullptr ||
       group_offsets == nullptr)
     return TB_ERR_INVALID;
   if (n_pairs < 0 || num_experts < 1 || num_experts > tb::kPlanMaxExperts || world < 1 || rank < 0 || rank >= world ||
-      (num_experts % world) != 0 || capacity_rows < 0)
+      (num_experts % world) != 0 || capacity_rows < 0 || (row_token != nullptr && (world != 1 || topk < 1)))
     return TB_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemsetAsync(cursor, 0, sizeof(int32_t) * num_experts, st);
@@ -475,7 +480,8 @@ extern "C" int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t 
   const unsigned blocks = static_cast<unsigned>(n_pairs > 0 ? (n_pairs + per_block - 1) / per_block : 1);
   tb::moe_plan_kernel<<<blocks, tb::kPlanThreads, 0, st>>>(topk_ids, ids_are_int64, n_pairs, num_experts, expert_place, world, rank,
                                                           counts_all, cursor, capacity_rows, pair_rank,
-                                                          reinterpret_cast<long long*>(pair_row), group_offsets);
+                                                          reinterpret_cast<long long*>(pair_row), group_offsets, row_token,
+                                                          topk < 1 ? 1 : topk);
   e = cudaGetLastError();
   if (e != cudaSuccess) return tb::cuda_fail(e, "moe_plan_kernel launch");
   tb::g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -249,6 +249,18 @@ __device__ __forceinline__ void tma_store_wait() {
 // Make generic-proxy writes to shared memory visible to the async proxy (TMA store, tcgen05 reads).
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// ---------------------------------------------------------------- cp.async (16-byte copies global -> shared by ordinary threads)
+// Copies `src_bytes` (0..16) bytes and zero-fills the rest of the 16-byte destination; bypasses L1.
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gmem_src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's committed groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 template <int CTAS>
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {

@@ -249,14 +249,17 @@ def swiglu(h: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def _gate_up_swiglu(grouped_fn, rows, w1, group_offsets):
+def _gate_up_swiglu(grouped_fn, rows, w1, group_offsets, row_index=None):
     """silu(rows @ gate.T) * (rows @ up.T) for w1 = [gate | up]: on the GPU with this library's grouped GEMM the activation
     runs inside the GEMM's epilogue when the shape allows it (ffn a multiple of 128, more than 128 rows); otherwise GEMM,
-    then `swiglu`."""
+    then `swiglu`. ``row_index`` (this library's grouped GEMM only): the rows are picked from ``rows`` by index inside the
+    kernel."""
     from .matmul import grouped_matmul
-    if grouped_fn is grouped_matmul and rows.is_cuda and (w1.shape[1] // 2) % 128 == 0 and rows.shape[0] > 128:
-        return grouped_fn(rows, w1, group_offsets, swiglu=True)
-    return swiglu(grouped_fn(rows, w1, group_offsets))
+    kw = {} if row_index is None else {"row_index": row_index}
+    n_rows = rows.shape[0] if row_index is None else row_index.numel()
+    if grouped_fn is grouped_matmul and rows.is_cuda and (w1.shape[1] // 2) % 128 == 0 and n_rows > 128:
+        return grouped_fn(rows, w1, group_offsets, swiglu=True, **kw)
+    return swiglu(grouped_fn(rows, w1, group_offsets, **kw))
 
 
 class ExpertParallelMoE:
@@ -294,6 +297,7 @@ class PeerDispatchPlan:
     pair_rank: torch.Tensor      # int32 (tokens*topk,)  the same, indexed by the flattened (token, k) pair
     pair_row: torch.Tensor       # int64 (tokens*topk,)
     group_offsets: torch.Tensor  # int32 (experts_per_rank + 1,) row offsets of this rank's experts in its receive buffer
+    row_token: Optional[torch.Tensor] = None   # int32 (capacity,) single rank only: source token of every row
 
 
 def plan_peer_dispatch(topk_ids: torch.Tensor, counts_all: torch.Tensor, rank: int,
@@ -382,6 +386,10 @@ class PeerMemoryMoE:
         self._counts_all = torch.zeros(self.world, num_experts, dtype=torch.int32, device=dev)
         self._cursor = torch.zeros(num_experts, dtype=torch.int32, device=dev)
         self._pairs = {}       # n_pairs -> (pair_rank int32, pair_row int64)
+        # One rank: nothing has to travel, so the gate/up GEMM picks the tokens' rows straight from x by index (no dispatch
+        # copy, no receive buffer traffic). Needs 16-byte aligned rows of a 16-bit type.
+        self._gather_rows = self.world == 1 and w1.element_size() == 2 and hidden % 8 == 0
+        self._row_token = None
         # expert id -> position in the layout order (w1 / w2 hold this rank's experts in that order); None = identity
         self._place = None if expert_place is None else expert_place.to(device=dev, dtype=torch.int32).contiguous()
         if self._place is not None:
@@ -399,6 +407,11 @@ class PeerMemoryMoE:
                               torch.empty(n, dtype=torch.int64, device=ids.device))
         pair_rank, pair_row = self._pairs[n]
         group_offsets = torch.empty(self.num_experts // self.world + 1, dtype=torch.int32, device=ids.device)
+        row_token = None
+        if self._gather_rows:
+            if self._row_token is None:
+                self._row_token = torch.full((self.capacity,), -1, dtype=torch.int32, device=ids.device)
+            row_token = self._row_token
         stream = _lib.current_stream_ptr(ids.device)
         is64 = int(ids.dtype == torch.int64)
         with torch.cuda.device(ids.device):
@@ -414,9 +427,11 @@ class PeerMemoryMoE:
             rc = _lib.lib.tb_moe_plan(ctypes.c_void_p(ids.data_ptr()), is64, n, self.num_experts, place, self.world, self.rank,
                                       ctypes.c_void_p(counts_all.data_ptr()), ctypes.c_void_p(self._cursor.data_ptr()),
                                       self.capacity, ctypes.c_void_p(pair_rank.data_ptr()), ctypes.c_void_p(pair_row.data_ptr()),
-                                      ctypes.c_void_p(group_offsets.data_ptr()), stream)
+                                      ctypes.c_void_p(group_offsets.data_ptr()),
+                                      ctypes.c_void_p(row_token.data_ptr() if row_token is not None else 0),
+                                      int(topk_ids.shape[1]), stream)
             _lib.check(rc, "tb_moe_plan")
-        return PeerDispatchPlan(None, pair_rank, pair_row, pair_rank, pair_row, group_offsets)
+        return PeerDispatchPlan(None, pair_rank, pair_row, pair_rank, pair_row, group_offsets, row_token)
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor):
         import ctypes
@@ -427,17 +442,22 @@ class PeerMemoryMoE:
         stream = _lib.current_stream_ptr(x.device)
         code = _lib.DTYPE_CODE[x.dtype]
         x = x if x.stride(1) == 1 else x.contiguous()
-        with torch.cuda.device(x.device):
-            rc = _lib.lib.tb_moe_dispatch_peers(ctypes.c_void_p(x.data_ptr()), x.stride(0), ctypes.c_void_p(0),
-                                                ctypes.c_void_p(plan.pair_rank.data_ptr()),
-                                                ctypes.c_void_p(plan.pair_row.data_ptr()), self._recv_ptrs, self.world,
-                                                self.recv.stride(0), self.capacity, ctypes.c_void_p(self.overflow.data_ptr()),
-                                                tokens * topk, self.hidden, code, topk, stream)
-        _lib.check(rc, "tb_moe_dispatch_peers")
-        if self.recv_h is not None:
-            self.recv_h.barrier(channel=0)                  # every rank's rows have landed in every receive buffer
-        grouped_matmul(_gate_up_swiglu(grouped_matmul, self.recv, self.w1, plan.group_offsets), self.w2,
-                       plan.group_offsets, out=self.y)
+        gather = plan.row_token is not None and (x.stride(0) * x.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0
+        if gather:
+            act = _gate_up_swiglu(grouped_matmul, x, self.w1, plan.group_offsets, row_index=plan.row_token)
+        else:
+            with torch.cuda.device(x.device):
+                rc = _lib.lib.tb_moe_dispatch_peers(ctypes.c_void_p(x.data_ptr()), x.stride(0), ctypes.c_void_p(0),
+                                                    ctypes.c_void_p(plan.pair_rank.data_ptr()),
+                                                    ctypes.c_void_p(plan.pair_row.data_ptr()), self._recv_ptrs, self.world,
+                                                    self.recv.stride(0), self.capacity,
+                                                    ctypes.c_void_p(self.overflow.data_ptr()), tokens * topk, self.hidden,
+                                                    code, topk, stream)
+            _lib.check(rc, "tb_moe_dispatch_peers")
+            if self.recv_h is not None:
+                self.recv_h.barrier(channel=0)              # every rank's rows have landed in every receive buffer
+            act = _gate_up_swiglu(grouped_matmul, self.recv, self.w1, plan.group_offsets)
+        grouped_matmul(act, self.w2, plan.group_offsets, out=self.y)
         if self.y_h is not None:
             self.y_h.barrier(channel=0)                     # every rank's expert outputs are complete
         w = topk_weights.to(torch.float32).contiguous()

@@ -313,7 +313,7 @@ def matmul_a8w8(a, b, a_scale, b_scale, c, enable_streamk=False, work_stealing=F
 
 
 def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, selector=None, swiglu=False,
-                   work_stealing=False):
+                   work_stealing=False, row_index=None):
     """Grouped (MoE) GEMM: out[r] = x[r] @ w[g].T for every row r of group g, rows of group g being
     [group_offsets[g], group_offsets[g+1]).
 
@@ -325,11 +325,16 @@ def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, se
     ``swiglu=True``: w holds [gate | up] projections, (G, 2*F, K); out is (rows, F) = silu(x @ gate.T) * (x @ up.T),
     the activation applied to the fp32 accumulators inside the GEMM's epilogue (F a multiple of 128, more than 128 rows).
     ``work_stealing=True`` selects the dynamic tile schedule.
+    ``row_index``: int32 CUDA tensor; grouped row r is then row ``row_index[r]`` of x (a negative entry is a row of zeros)
+    and the problem has ``row_index.numel()`` rows: the kernel gathers the rows itself, no gathered copy of x is made.
     """
     assert x.ndim == 2 and w.ndim == 3 and x.shape[1] == w.shape[2], "Incompatible Dimensions"
     if not (x.is_cuda and w.is_cuda and group_offsets.is_cuda):
         raise RuntimeError("tritonblas_b200 runs on CUDA tensors only (no CPU path)")
     rows, K = x.shape
+    if row_index is not None:
+        assert row_index.dtype == torch.int32 and row_index.is_cuda and row_index.is_contiguous(), "row_index must be int32 on the GPU"
+        rows = row_index.numel()
     G, N, _ = w.shape
     if swiglu:
         assert N % 256 == 0 and a_scale is None, "swiglu needs F = N / 2 to be a multiple of 128 and no scales"
@@ -360,6 +365,8 @@ def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, se
     args.allow_tf32 = 1
     args.group_offsets, args.num_groups = _ptr(group_offsets), G
     args.epilogue_op = 1 if swiglu else 0
+    if row_index is not None:
+        args.a_gather_index = _ptr(row_index)
     if work_stealing:  # tiles after each program's first come from a device counter (see persistent_matmul_lt)
         args.tile_counter = _ptr(_tile_counter_for(x.device))
     with torch.cuda.device(x.device):
