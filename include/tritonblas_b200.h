@@ -138,10 +138,11 @@ typedef struct tb_gemm_args {
    * forwards. */
   int32_t debug_flags;
   /* Row gather (tb_grouped_gemm only; no reference counterpart): DEVICE int32[m], or NULL. Row r of the grouped problem is
-   * then row a_gather_index[r] of the matrix `a` (any number of rows, a_stride_m apart, K contiguous, 16-bit elements, rows
-   * starting on 16-byte boundaries); a negative entry reads as a row of zeros. The MoE gate/up projection reads the tokens'
-   * rows in expert order straight from the activation matrix this way, with no gathered copy in between. */
+   * then row a_gather_index[r] of the matrix `a`, which has a_rows rows (a_stride_m apart, K contiguous, 16-bit elements,
+   * base and row pitch 16-byte aligned); an entry outside [0, a_rows) reads as a row of zeros. The MoE gate/up projection
+   * reads the tokens' rows in expert order straight from the activation matrix this way, with no gathered copy in between. */
   const int32_t* a_gather_index;
+  int64_t a_rows;
 } tb_gemm_args;
 
 /* Fill `cfg` for `p`. Stands in for origami.select_config + OrigamiMatmulSelector._compute_sk_grid

@@ -146,7 +146,7 @@ def test_row_gather_kernel_matches_index_select():
 @pytest.mark.parametrize("n,k", [(256, 256), (384, 520), (200, 1024)])
 def test_grouped_with_rows_gathered_by_index(counts, n, k, pair):
     """row_index: grouped row r is row row_index[r] of x (tokens repeat; order arbitrary; a negative entry is a zero row).
-    The kernel's own gather warp loads the rows; compared with the oracle on the explicitly gathered matrix. k = 520 ends
+    The kernel's producer loads the rows with gather-mode TMA copies; compared with the oracle on the explicitly gathered matrix. k = 520 ends
     inside a 64-element stage."""
     tokens = 700
     g = torch.Generator().manual_seed(sum(counts) + n + k)

@@ -74,14 +74,15 @@ def _experts(E, H, F, seed):
     return w1, w2
 
 
+@pytest.mark.parametrize("gather_rows", [False, True])
 @pytest.mark.parametrize("E,H,F,T,topk", [(8, 256, 128, 64, 2), (64, 512, 256, 1000, 8), (16, 1024, 384, 333, 4)])
-def test_single_gpu_moe_step_matches_oracle(E, H, F, T, topk):
+def test_single_gpu_moe_step_matches_oracle(E, H, F, T, topk, gather_rows):
     w1, w2 = _experts(E, H, F, E + T)
     g = torch.Generator().manual_seed(T)
     x = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
     ids = _zipf_ids(T, E, topk, 7).cuda()
     wts = torch.rand(T, topk, generator=g).cuda()
-    moe = tbd.PeerMemoryMoE(w1, w2, E, capacity=T * topk)
+    moe = tbd.PeerMemoryMoE(w1, w2, E, capacity=T * topk, gather_rows=gather_rows)
     for _ in range(2):
         out, plan = moe.forward(x, ids, wts)
         toks = list(range(0, T, max(1, T // 48)))

@@ -369,14 +369,9 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   }
   const bool gather = a.a_gather_index != nullptr;
   if (gather) {
-    // rows of A picked by index from another matrix: grouped launches of 16-bit K-contiguous operands whose rows start on
-    // 16-byte boundaries; the gather warp keeps kGatherLag stages in flight, so the ring must be deeper than that
-    if (!grouped || a_mn || es != 2 || a.a_stride_k != 1) return TB_ERR_UNSUPPORTED;
-    if (((a.a_stride_m * es) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.a) & 15) != 0 || (a.k % 8) != 0) return TB_ERR_ALIGNMENT;
-    if (stages < kGatherLag + 2) return TB_ERR_UNSUPPORTED;
+    // rows of A picked by index from another matrix: grouped launches of 16-bit K-contiguous operands that TMA can address
+    if (!grouped || a_mn || es != 2 || a.a_stride_k != 1 || a.a_rows <= 0) return TB_ERR_UNSUPPORTED;
     p.a_gather = a.a_gather_index;
-    p.a_base = a.a;
-    p.a_row_bytes = a.a_stride_m * es;
   }
   if (a.tile_counter != nullptr && !a.streamk) {
     if (reinterpret_cast<uintptr_t>(a.tile_counter) & 3) return TB_ERR_ALIGNMENT;
@@ -476,7 +471,8 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   const int mn_swz = es == 4 ? 2 : 1;
   static const bool no_mn3d = getenv("TB_DISABLE_MN3D") != nullptr;  // measurement knob, read once
   if (gather) {
-    rc = TB_OK;   // A has no tensor map: the kernel gets B's as a placeholder (below)
+    // gather-mode copies take their rows from a map over the whole source matrix whose box is one row of a stage
+    rc = encode_2d(&ta, a.a_dtype, A, a.k, a.a_rows, static_cast<uint64_t>(a.a_stride_m) * es, bk, 1, 1);
   } else if (!a_mn) {
     rc = encode_2d(&ta, a.a_dtype, A, a.k, a.m, static_cast<uint64_t>(a.a_stride_m) * es, bk, 128, 1);
   } else {
@@ -500,7 +496,6 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   }
   if (rc == TB_ERR_ALIGNMENT && !grouped && !swapped) return gemm_generic_loader(a, cfg, stream, dev->status);
   if (rc != TB_OK) return rc;
-  if (gather) ta = tbm;
 
 #define TB_LAUNCH(K, C) return launch_gemm<K, C>(ta, tbm, p, programs, smem_bytes, stream)
   if (pair == 1) {

@@ -24,14 +24,12 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const GemmParams&
                 cudaStream_t stream, const CUtensorMap* tsfa, const CUtensorMap* tsfb) {
   auto kernel = gemm_kernel<KIND, CTAS, false>;
   int variant = 0;
-  bool gather = false;
   // The instantiations with per-role cycle counters (measurement runs) and with a row-gathering A loader (grouped
   // launches whose rows are picked from another matrix by index) exist for 16-bit operands only.
   if constexpr (KIND == 0) {
     if (p.a_gather != nullptr) {
       kernel = gemm_kernel<KIND, CTAS, false, true>;
       variant = 2;
-      gather = true;
     } else if ((p.debug_flags & 2) && p.debug_out != nullptr) {
       kernel = gemm_kernel<KIND, CTAS, true>;
       variant = 1;
@@ -56,7 +54,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb_, const GemmParams&
   }
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(static_cast<unsigned>(programs * CTAS), 1, 1);
-  lc.blockDim = dim3(gemm_threads<KIND>(gather), 1, 1);
+  lc.blockDim = dim3(gemm_threads<KIND>(), 1, 1);
   lc.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   lc.stream = stream;
   cudaLaunchAttribute attr[2];

@@ -39,9 +39,8 @@ constexpr int kSfAtomBytes = 512;      // scale factors of 128 rows x 4 K blocks
 constexpr int kSfGroupsB = 2;          // 128-row scale groups staged for B: tiles are 64, 128 or 192 columns wide and start
                                        // at a multiple of 64 (the MMA takes its scale columns from an even TMEM column),
                                        // so a tile touches at most two groups
-constexpr int kGatherLag = 3;          // stages the row-gather warp keeps in flight before it reports the oldest as filled
 template <int KIND>
-constexpr int gemm_threads(bool gather = false) { return kGemmThreads + (gather ? 32 : 0); }
+constexpr int gemm_threads() { return kGemmThreads; }
 constexpr int kATileBytes = kTileM * kStageRowBytes;  // 16 KB
 
 enum : int { TB_F16 = 0, TB_BF16 = 1, TB_F32 = 2, TB_E4M3 = 3, TB_E5M2 = 4, TB_U8 = 5, TB_I8 = 7 };
@@ -93,11 +92,9 @@ struct GemmParams {
   const int* group_offsets;
   int num_groups;
   // Row gather for A (grouped launches of the GATHER instantiation): row r of the problem is row a_gather[r] of the
-  // matrix at a_base (rows a_row_bytes apart, K contiguous); negative entries and rows past a group's end read as zero.
-  // Loaded by a warp of its own with 16-byte cp.async into the same swizzled stage layout TMA produces.
+  // matrix the A tensor map describes (box = one row of a stage's K extent); negative entries and rows past a group's end
+  // read as zero. Every lane of the producer warp fetches four rows per stage with one gather-mode TMA copy.
   const int* a_gather;
-  const void* a_base;
-  long long a_row_bytes;
   // failure reporting
   int* status;
   unsigned long long timeout_ns;
@@ -504,7 +501,7 @@ __device__ __forceinline__ void glu_drain(const GemmParams& p, uint8_t* stg, uin
 }
 
 template <int KIND, int CTAS, bool PROF = false, bool GATHER = false>
-__global__ void __launch_bounds__(gemm_threads<KIND>(GATHER), 1)
+__global__ void __launch_bounds__(gemm_threads<KIND>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -548,8 +545,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < stages; ++s) {
-      // one arrival from the TMA producer (with the byte count) and, when A is gathered, one from every CTA's gather warp
-      mbar_init(&full_bar[s], GATHER ? 1 + CTAS : 1);
+      mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -559,9 +555,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     mbar_init(publish_bar, kEpiWarps);
     for (int i = 0; i < kSchedDepth; ++i) {
       mbar_init(&sched_full[i], 1);
-      // consumers: MMA issuer + 4 epilogue warps in the even CTA, producer + 4 epilogue warps in the odd one, and every
-      // CTA's gather warp when there is one
-      mbar_init(&sched_empty[i], (5 + (GATHER ? 1 : 0)) * CTAS);
+      // consumers: MMA issuer + 4 epilogue warps in the even CTA, producer + 4 epilogue warps in the odd one
+      mbar_init(&sched_empty[i], 5 * CTAS);
     }
     mbar_fence_init();
     // Everything above touched only shared memory. From here on global memory is read, which has to wait for the
@@ -672,7 +667,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t ph = 0;
       const int a_atom = kStageRowBytes / p.esize;  // elements per 128-byte row
       // In a pair, transaction bytes of both CTAs land on the even CTA's barrier, which expects the sum.
-      const uint32_t expect = static_cast<uint32_t>((GATHER ? 0 : kATileBytes) + nh * b_tile_bytes + sf_bytes) * CTAS;
+      const uint32_t expect = static_cast<uint32_t>(kATileBytes + nh * b_tile_bytes + sf_bytes) * CTAS;
       const int mn_box_bytes = p.k_per_stage * kStageRowBytes;
       bool ok = true;
       long long prof_wait = 0, prof_t0 = clock64();
@@ -695,6 +690,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // ones most likely still in L2 (the accumulation order of those items is reversed with it).
         const bool backwards = p.k_serpentine && (item & 1);
         ++item;
+        int grow[4] = {-1, -1, -1, -1};   // GATHER: source rows of this lane's four A rows (-1: reads as zeros)
+        if constexpr (GATHER) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int r = m0 + 4 * lane + j;
+            if (r < tg.row_end) grow[j] = __ldg(p.a_gather + r);
+          }
+        }
         for (int it = w.kb0; it < w.kb1; ++it) {
           const int kb = backwards ? w.kb0 + w.kb1 - 1 - it : it;
           const long long pw0 = prof ? clock64() : 0;
@@ -708,7 +711,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if constexpr (CTAS == 1) {
               mbar_arrive_expect_tx(&full_bar[s], expect);
               if constexpr (GATHER) {
-                // A arrives through the gather warp
+                // A: every lane fetches its four rows below
               } else if (!p.a_mn) {
                 tma_load_2d(sa, &tmap_a, &full_bar[s], k0, m0);
               } else if (p.a_mn3d) {
@@ -743,7 +746,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               const uint32_t bar = mapa_cluster(smem_u32(&full_bar[s]), 0);
               if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], expect);
               if constexpr (GATHER) {
-                // A arrives through the gather warp
+                // A: every lane fetches its four rows below
               } else if (!p.a_mn) {
                 tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
               } else if (p.a_mn3d) {
@@ -777,6 +780,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
           __syncwarp();
+          if constexpr (GATHER) {
+            // Lane l owns rows 4 l .. 4 l + 3 of the A tile: one gather-mode copy of four rows of the source matrix,
+            // 512 bytes, into its slot of the swizzled stage (the byte count expected above already includes them;
+            // rows out of range arrive as zeros). Issued after the elected lane's expect_tx (the __syncwarp above).
+            if constexpr (CTAS == 1)
+              tma_gather4_2d(sa + lane * 4 * kStageRowBytes, &tmap_a, &full_bar[s], k0, grow[0], grow[1], grow[2], grow[3]);
+            else
+              tma_gather4_2d_pair(sa + lane * 4 * kStageRowBytes, &tmap_a, mapa_cluster(smem_u32(&full_bar[s]), 0), k0,
+                                  grow[0], grow[1], grow[2], grow[3]);
+          }
           if (++s == stages) {
             s = 0;
             ph ^= 1;
@@ -954,83 +967,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         p.debug_out[blockIdx.x * 16 + 3] = prof_tmem;
         p.debug_out[blockIdx.x * 16 + 4] = prof_issue;
         p.debug_out[blockIdx.x * 16 + 5] = clock64() - prof_t0;
-      }
-    }
-  } else if (GATHER && warp == kEpiWarp0 + kEpiWarps) {
-    // ------------------------------------------------------------------ A row gather (one warp, GATHER instantiation)
-    // Lane l copies 16-byte chunk (l & 7) of rows (l >> 3) + 4 i, i = 0..31, of every stage: 32 cp.async per lane and
-    // stage into the 128-byte-swizzled layout the matrix descriptors expect (chunk c of row r at r * 128 + ((c ^ (r & 7)) << 4)).
-    // Copies complete asynchronously: a stage is reported filled kGatherLag stages after its copies were issued, once
-    // cp.async.wait_group says they have landed and a proxy fence has made them visible to the tensor core's reads.
-    WorkIter wi(p, pid, nprog, grouped_tiles);
-    int s = 0, s_sig = 0, pending = 0;
-    uint32_t ph = 0;
-    bool ok = true;
-    int seq = 0;
-    const int chunk = lane & 7, sub = lane >> 3;
-    const uint32_t ring_addr = smem_u32(ring);
-    const uint32_t full_remote = (CTAS == 2) ? mapa_cluster(smem_u32(&full_bar[0]), 0) : 0u;
-    auto report_filled = [&](int stage) {
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        if (CTAS == 1 || cta_rank == 0) mbar_arrive(&full_bar[stage]);
-        else mbar_arrive_remote(full_remote + stage * 8);
-      }
-    };
-    auto next_item = [&]() -> WorkItem {
-      if (!dyn) return wi.next();
-      bool got = true;
-      const WorkItem w = dyn_take(seq, got);
-      ++seq;
-      if (!got) ok = false;
-      return w;
-    };
-    for (WorkItem w = next_item(); w.valid && ok; w = next_item()) {
-      const TileGeom tg = tile_geometry(p, w.tile, kPairTileM, tile_prefix);
-      const int m0 = tg.m0 + static_cast<int>(cta_rank) * kTileM;
-      const uint8_t* src_row[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int r = m0 + sub + 4 * i;
-        const int idx = r < tg.row_end ? __ldg(p.a_gather + r) : -1;
-        src_row[i] = idx >= 0 ? static_cast<const uint8_t*>(p.a_base) + static_cast<long long>(idx) * p.a_row_bytes + chunk * 16
-                              : nullptr;
-      }
-      for (int kb = w.kb0; kb < w.kb1; ++kb) {
-        ok = mbar_wait_warp(&empty_bar[s], ph ^ 1, wctx, TB_DEV_TIMEOUT_SMEM_EMPTY);
-        if (!ok) break;
-        const long long kbyte = static_cast<long long>(kb) * kStageRowBytes;          // byte offset of this stage inside a row
-        const long long left = static_cast<long long>(p.K) * p.esize - kbyte - chunk * 16;  // row bytes from this chunk on
-        const uint32_t nbytes = left >= 16 ? 16u : (left > 0 ? static_cast<uint32_t>(left) : 0u);
-        const uint32_t dst0 = ring_addr + static_cast<uint32_t>(s) * stage_bytes;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int rl = sub + 4 * i;
-          const uint32_t dst = dst0 + rl * kStageRowBytes + ((chunk ^ (rl & 7)) << 4);
-          const bool live = src_row[i] != nullptr;
-          cp_async_16(dst, live ? static_cast<const void*>(src_row[i] + kbyte) : p.a_base, live ? nbytes : 0u);
-        }
-        cp_async_commit();
-        if (++pending > kGatherLag) {
-          cp_async_wait<kGatherLag>();
-          report_filled(s_sig);
-          if (++s_sig == stages) s_sig = 0;
-          --pending;
-        }
-        if (++s == stages) {
-          s = 0;
-          ph ^= 1;
-        }
-      }
-    }
-    // Whatever was issued must land before shared memory goes away; stages still unreported are reported on the normal path.
-    cp_async_wait<0>();
-    if (ok) {
-      while (pending > 0) {
-        report_filled(s_sig);
-        if (++s_sig == stages) s_sig = 0;
-        --pending;
       }
     }
   } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + kEpiWarps) {

@@ -231,6 +231,24 @@ __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorM
       "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Gather-mode 2-D load: four rows (y0..y3, any order, out-of-range rows read as the fill value) of a tensor map whose box
+// is ONE row of `x`-extent; they land as four consecutive rows at smem_dst and complete 4 x box bytes on the barrier.
+__device__ __forceinline__ void tma_gather4_2d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int x, int y0, int y1,
+                                               int y2, int y3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_gather4_2d_pair(void* smem_dst, const CUtensorMap* tmap, uint32_t bar_cluster_addr, int x,
+                                                    int y0, int y1, int y2, int y3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3)
+      : "memory");
+}
 // 2-D tile store shared -> global (bulk group completion).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
@@ -248,18 +266,6 @@ __device__ __forceinline__ void tma_store_wait() {
 }
 // Make generic-proxy writes to shared memory visible to the async proxy (TMA store, tcgen05 reads).
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// ---------------------------------------------------------------- cp.async (16-byte copies global -> shared by ordinary threads)
-// Copies `src_bytes` (0..16) bytes and zero-fills the rest of the 16-byte destination; bypasses L1.
-__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gmem_src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gmem_src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// Waits until at most N of this thread's committed groups are still in flight.
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 
 // ---------------------------------------------------------------- tcgen05 / TMEM
 template <int CTAS>

@@ -356,7 +356,7 @@ class PeerMemoryMoE:
     """
 
     def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, capacity: int, group=None,
-                 expert_place: Optional[torch.Tensor] = None):
+                 expert_place: Optional[torch.Tensor] = None, gather_rows: bool = False):
         import ctypes
         self.w1, self.w2, self.num_experts, self.group = w1, w2, num_experts, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -386,9 +386,12 @@ class PeerMemoryMoE:
         self._counts_all = torch.zeros(self.world, num_experts, dtype=torch.int32, device=dev)
         self._cursor = torch.zeros(num_experts, dtype=torch.int32, device=dev)
         self._pairs = {}       # n_pairs -> (pair_rank int32, pair_row int64)
-        # One rank: nothing has to travel, so the gate/up GEMM picks the tokens' rows straight from x by index (no dispatch
-        # copy, no receive buffer traffic). Needs 16-byte aligned rows of a 16-bit type.
-        self._gather_rows = self.world == 1 and w1.element_size() == 2 and hidden % 8 == 0
+        # One rank, on request: the gate/up GEMM picks the tokens' rows straight from x by index (gather-mode TMA copies, no
+        # dispatch copy, no receive buffer). Measured on B200: a gather-mode copy moves four 128-byte rows and the copy
+        # unit retires one about every 90 clocks, 5-6 bytes per clock and SM where a tensor-bound tile needs 32, so the
+        # projection runs three times slower than on rows copied into place first (0.28 ms for 131072 x 4096 bf16 rows);
+        # it pays only where the grouped GEMM is not bound by its operand rate. Off by default.
+        self._gather_rows = bool(gather_rows) and self.world == 1 and w1.element_size() == 2 and hidden % 8 == 0
         self._row_token = None
         # expert id -> position in the layout order (w1 / w2 hold this rank's experts in that order); None = identity
         self._place = None if expert_place is None else expert_place.to(device=dev, dtype=torch.int32).contiguous()

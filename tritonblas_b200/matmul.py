@@ -313,7 +313,7 @@ def matmul_a8w8(a, b, a_scale, b_scale, c, enable_streamk=False, work_stealing=F
 
 
 def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, selector=None, swiglu=False,
-                   work_stealing=False, row_index=None):
+                   work_stealing=False, row_index=None, _debug_flags=0):
     """Grouped (MoE) GEMM: out[r] = x[r] @ w[g].T for every row r of group g, rows of group g being
     [group_offsets[g], group_offsets[g+1]).
 
@@ -366,7 +366,8 @@ def grouped_matmul(x, w, group_offsets, out=None, a_scale=None, b_scale=None, se
     args.group_offsets, args.num_groups = _ptr(group_offsets), G
     args.epilogue_op = 1 if swiglu else 0
     if row_index is not None:
-        args.a_gather_index = _ptr(row_index)
+        args.a_gather_index, args.a_rows = _ptr(row_index), x.shape[0]
+    args.debug_flags = int(_debug_flags)      # measurement switches of the library (tb_gemm_args.debug_flags); 0 in production
     if work_stealing:  # tiles after each program's first come from a device counter (see persistent_matmul_lt)
         args.tile_counter = _ptr(_tile_counter_for(x.device))
     with torch.cuda.device(x.device):
