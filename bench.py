@@ -260,7 +260,7 @@ class DenseWorkload:
             from tritonblas_b200 import distributed as tbd
             self.layers = [tbd.ColumnShardedGemm(bt) for bt in self.Bt]
             for layer in self.layers:
-                layer.enable_fused_gather(M, self.out_dtype)
+                layer.enable_fused_gather(M, self.out_dtype, block_n=args.fused_block_n or None)
         self.sel = tb.OrigamiMatmulSelector(M, self.n_local, K, self.in_dtype, self.in_dtype, self.out_dtype, dev,
                                             streamk=self.streamk)
         self.cfg = tb.matmul_preamble(self.sel)
@@ -655,6 +655,13 @@ def moe_block(args, run, nccl):
     n = max(5, min(args.steps, 12))
     total, unit, ck, launches = run.timed(lambda i: w.step(i, run.dist), 3, n, clocks=run.world == 1)
     ok, err = run.all_ok(*w.parity_check(run.dist))
+    phases = None
+    if w.path != "nccl":
+        # one more step with an event after every phase (outside the timed steps): where the step's time goes on rank 0
+        evs = []
+        w.moe.forward(w.x, w.ids, w.wts, phase_events=evs)
+        run.barrier()
+        phases = {name: round(evs[i - 1][1].elapsed_time(ev), 4) for i, (name, ev) in enumerate(evs) if i > 0}
     out = {"value": w.flops * n / (total * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": total / n, "steps": n,
            "rows_per_rank": w.rows_per_rank, "expert_placement": w.placement, "path": w.path, "gpu_launches": launches,
            "parity_check": {"ok": ok, "max_err": err, "ranks_checked": run.world, "tokens_per_rank": 64,
@@ -662,6 +669,8 @@ def moe_block(args, run, nccl):
            "frac_of_nominal_dense": w.flops * n / (total * 1e-3) / 1e12 / (NOMINAL_TFLOPS["bf16"] * run.world)}
     if ck:
         out["clocks"] = ck
+    if phases is not None:
+        out["phases_ms_rank0"] = phases
     del w
     release()
     return out
@@ -681,6 +690,8 @@ def main():
                     help="default workload: skip the MoE, sustained, cuBLAS and per-workload blocks (profiling runs)")
     ap.add_argument("--nccl-moe", action="store_true",
                     help="moe workload on several GPUs: NCCL all-to-all dispatch/combine instead of the peer-memory kernels")
+    ap.add_argument("--fused-block-n", type=int, default=0,
+                    help="multi-GPU default workload: tile width of the fused GEMM + push launch (0 = the library's choice)")
     ap.add_argument("--contiguous-experts", action="store_true",
                     help="MoE on several GPUs: experts laid out over the ranks in id order instead of balanced by load")
     ap.add_argument("--nccl-gather", action="store_true",

@@ -51,7 +51,7 @@ class ColumnShardedGemm:
                                     group=self.group)
         return gathered
 
-    def enable_fused_gather(self, m: int, dtype=None):
+    def enable_fused_gather(self, m: int, dtype=None, block_n: Optional[int] = None):
         """Allocate the gathered C (world, M, n_local) in symmetric memory and map every peer's copy, so that
         forward_fused() can let the GEMM epilogue write each tile straight into all ranks' buffers over NVLink
         (ordinary stores to peer-mapped memory; no TMA or multicast access to peer memory is involved)."""
@@ -69,6 +69,8 @@ class ColumnShardedGemm:
         # tile's main loop; a wide tile's drains are exposed (8 GPUs: 3.88 PFLOP/s wide against 4.11 narrow)
         self._fused_selector = OrigamiMatmulSelector(m, n_local, self.b_shard_t.shape[1], self.b_shard_t.dtype,
                                                      self.b_shard_t.dtype, dtype, self.b_shard_t.device, max_halves=1)
+        if block_n:
+            self._fused_selector.override(block_n=int(block_n))     # tile width of the fused launch (tuning)
         return self._gathered
 
     def forward_fused(self, a: torch.Tensor, pre_barrier: bool = True, b_shard_t: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -436,17 +438,29 @@ class PeerMemoryMoE:
             _lib.check(rc, "tb_moe_plan")
         return PeerDispatchPlan(None, pair_rank, pair_row, pair_rank, pair_row, group_offsets, row_token)
 
-    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor):
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, phase_events=None):
+        """``phase_events``: a list that receives (name, torch.cuda.Event) after each phase (plan, dispatch, gate_up, down,
+        combine) for a timing breakdown; each closes with the barrier that follows it, if any."""
         import ctypes
         from . import _lib
         from .matmul import grouped_matmul
         tokens, topk = topk_ids.shape
+
+        def mark(name):
+            if phase_events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                phase_events.append((name, ev))
+
+        mark("start")
         plan = self.plan(topk_ids)
+        mark("plan")
         stream = _lib.current_stream_ptr(x.device)
         code = _lib.DTYPE_CODE[x.dtype]
         x = x if x.stride(1) == 1 else x.contiguous()
         gather = plan.row_token is not None and (x.stride(0) * x.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0
         if gather:
+            mark("dispatch")
             act = _gate_up_swiglu(grouped_matmul, x, self.w1, plan.group_offsets, row_index=plan.row_token)
         else:
             with torch.cuda.device(x.device):
@@ -459,10 +473,13 @@ class PeerMemoryMoE:
             _lib.check(rc, "tb_moe_dispatch_peers")
             if self.recv_h is not None:
                 self.recv_h.barrier(channel=0)              # every rank's rows have landed in every receive buffer
+            mark("dispatch")
             act = _gate_up_swiglu(grouped_matmul, self.recv, self.w1, plan.group_offsets)
+        mark("gate_up")
         grouped_matmul(act, self.w2, plan.group_offsets, out=self.y)
         if self.y_h is not None:
             self.y_h.barrier(channel=0)                     # every rank's expert outputs are complete
+        mark("down")
         w = topk_weights.to(torch.float32).contiguous()
         out = x.new_empty(tokens, self.hidden)
         with torch.cuda.device(x.device):
@@ -472,4 +489,5 @@ class PeerMemoryMoE:
                                                ctypes.c_void_p(out.data_ptr()), out.stride(0), tokens, topk, self.hidden,
                                                code, self.capacity, stream)
         _lib.check(rc, "tb_moe_combine_peers")
+        mark("combine")
         return out, plan
