@@ -233,6 +233,14 @@ int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, in
                 int32_t world, int32_t rank, const int32_t* counts_all, int32_t* cursor, int64_t capacity_rows,
                 int32_t* pair_rank, int64_t* pair_row, int32_t* group_offsets, int32_t* row_token, int32_t topk, void* stream);
 
+/* Diagnostic (no reference counterpart): stores `passes` times `rows` rows of `run_bytes` contiguous bytes each, `pitch_bytes`
+ * apart, into dst (a local buffer, or a peer GPU's buffer mapped into this process) from `blocks` x `threads` threads with
+ * 16-byte stores: the store pattern of an epilogue that pushes output tiles to other GPUs. Timing it gives the egress rate
+ * that bounds the fused GEMM + all-gather and the MoE dispatch (python -m tritonblas_b200.peer_bandwidth). dst, pitch and
+ * run 16-byte aligned; run_bytes below 512 must divide 512. dst needs rows * pitch_bytes bytes. */
+int tb_peer_store_probe(void* dst, int64_t pitch_bytes, int32_t run_bytes, int64_t rows, int32_t blocks, int32_t threads,
+                        int32_t passes, void* stream);
+
 /* MXFP4 GEMM: C (m, n) = sum over 32-element K blocks of (A_e2m1 * 2^(sa-127)) . (B_e2m1 * 2^(sb-127)), fp32
  * accumulate, one cast. A is (m, k/2) bytes and B is (n, k/2) bytes, two e2m1 codes per byte (even element in the low
  * nibble), K contiguous, row strides in bytes (multiples of 16). Scales are e8m0 bytes in the "atom" arrangement the

@@ -212,17 +212,42 @@ __global__ void __launch_bounds__(256) combine_peers_kernel(PeerPtrs y_peers, lo
     const int t = static_cast<int>(i / vec_per_row);
     const int c = static_cast<int>(i - static_cast<long long>(t) * vec_per_row) * 8;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < topk; ++k) {
-      const long long f = static_cast<long long>(t) * topk + k;
-      const long long prow = pair_row[f];
-      // a pair whose row the dispatch dropped (beyond the owner's capacity) contributes nothing
-      if (prow < 0 || prow >= capacity_rows) continue;
-      const T* y = static_cast<const T*>(y_peers.p[pair_rank[f]]);
-      const float wk = w[f];
-      float v[8];
-      Vec8<T>::load(y + prow * y_stride + c, v);
+    // Eight experts at a time: first all their indices, then all their rows (eight independent 16-byte loads in flight per
+    // thread instead of one), then the sum in k order.
+    for (int k0 = 0; k0 < topk; k0 += 8) {
+      const T* src[8];
+      float wk[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = fmaf(v[j], wk, acc[j]);
+      for (int j = 0; j < 8; ++j) {
+        src[j] = nullptr;
+        wk[j] = 0.f;
+        if (k0 + j < topk) {
+          const long long f = static_cast<long long>(t) * topk + k0 + j;
+          const long long prow = pair_row[f];
+          // a pair whose row the dispatch dropped (beyond the owner's capacity) contributes nothing
+          if (prow >= 0 && prow < capacity_rows) {
+            src[j] = static_cast<const T*>(y_peers.p[pair_rank[f]]) + prow * y_stride + c;
+            wk[j] = w[f];
+          }
+        }
+      }
+      float v[8][8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (src[j] != nullptr) {
+          Vec8<T>::load(src[j], v[j]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (src[j] != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = fmaf(v[j][i], wk[j], acc[i]);
+        }
+      }
     }
     Vec8<T>::store(out + static_cast<long long>(t) * out_stride + c, acc);
   }
@@ -484,6 +509,45 @@ extern "C" int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t 
                                                           topk < 1 ? 1 : topk);
   e = cudaGetLastError();
   if (e != cudaSuccess) return tb::cuda_fail(e, "moe_plan_kernel launch");
+  tb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return TB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Diagnostic: how fast this GPU's SMs can store into a buffer (local, or a peer's mapped into this process) when every
+// row is written as one contiguous run of `run_bytes` at a pitch of `pitch_bytes`, the pattern of an epilogue that pushes
+// output tiles to other GPUs. The fused GEMM + all-gather and the MoE dispatch are bounded by this rate; the figure
+// depends on the run length and hardly on the number of storing warps. No reference counterpart.
+namespace tb {
+namespace {
+__global__ void peer_store_probe_kernel(uint4* dst, long long pitch_vec, int run_vec, long long rows, int passes) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const long long warp_id = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * warps_per_block;
+  const int lanes_per_row = run_vec < 32 ? run_vec : 32;   // lanes that cover one row per store instruction
+  const int rows_per_inst = 32 / lanes_per_row;
+  const uint4 v = make_uint4(lane, blockIdx.x, 2, 3);
+  for (int pass = 0; pass < passes; ++pass)
+    for (long long r0 = warp_id * rows_per_inst; r0 < rows; r0 += nwarps * rows_per_inst) {
+      const long long r = r0 + lane / lanes_per_row;
+      if (r < rows)
+        for (int c = lane % lanes_per_row; c < run_vec; c += lanes_per_row) dst[r * pitch_vec + c] = v;
+    }
+}
+}  // namespace
+}  // namespace tb
+
+extern "C" int tb_peer_store_probe(void* dst, int64_t pitch_bytes, int32_t run_bytes, int64_t rows, int32_t blocks,
+                                   int32_t threads, int32_t passes, void* stream) {
+  if (dst == nullptr || rows <= 0 || passes < 1 || blocks < 1 || threads < 32 || threads > 1024 || (threads & 31)) return TB_ERR_INVALID;
+  if ((reinterpret_cast<uintptr_t>(dst) & 15) || (pitch_bytes & 15) || (run_bytes & 15) || run_bytes < 16 || run_bytes > pitch_bytes)
+    return TB_ERR_ALIGNMENT;
+  if (run_bytes < 512 && (512 % run_bytes) != 0) return TB_ERR_INVALID;   // whole rows per 32-lane store instruction
+  tb::peer_store_probe_kernel<<<static_cast<unsigned>(blocks), static_cast<unsigned>(threads), 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(dst), pitch_bytes / 16, run_bytes / 16, rows, passes);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return tb::cuda_fail(e, "peer_store_probe_kernel launch");
   tb::g_launches.fetch_add(1, std::memory_order_relaxed);
   return TB_OK;
 }
