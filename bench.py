@@ -307,9 +307,14 @@ class DenseWorkload:
         return c
 
     def cublas_step(self, i):
-        """torch.matmul (cuBLAS) on the same operands, for the same-run comparison; not part of `value`."""
+        """torch.matmul (cuBLAS), or torch._scaled_mm (cuBLASLt, row-wise scales) for fp8, on the same operands, for the
+        same-run comparison; not part of `value`."""
         s = i % self.nsets
-        torch.matmul(self.A[s], self.Bt[s].T, out=self.C[i % len(self.C)])
+        if self.fp8:
+            torch._scaled_mm(self.A[s], self.Bt[s].T, scale_a=self.a_s[s].view(-1, 1), scale_b=self.b_s[s].view(1, -1),
+                             out_dtype=torch.bfloat16, out=self.C[i % len(self.C)])
+        else:
+            torch.matmul(self.A[s], self.Bt[s].T, out=self.C[i % len(self.C)])
 
     def e2e_step(self, i, dist):
         """Host operands in, host result out, through the public API. H2D of step i+1 and D2H of step i-1 run on their own
@@ -805,11 +810,20 @@ def main():
             n = max(20, min(4000, int(250.0 / max(est, 1e-3))))
             total, unit, ck, nl = run.timed(lambda i: xw.step(i, dist), 3, n)
             ok, err = xw.parity_check(dist)
+            lib_run = None
+            if hasattr(xw, "cublas_step"):
+                # the vendor library on the same operands in the same run (context, not a denominator)
+                try:
+                    _, lib_unit, _, _ = run.timed(lambda i: xw.cublas_step(i), 3, n, clocks=False)
+                    lib_run = {"ms": lib_unit, "ours_over_library": lib_unit / unit,
+                               "how": "torch._scaled_mm (cuBLASLt, row-wise scales)" if xw.fp8 else "torch.matmul (cuBLAS)"}
+                except Exception as exc:      # a torch build without this cuBLASLt path
+                    lib_run = {"unavailable": str(exc).splitlines()[0][:200]}
             flops = xw.kernel_flops if name != "mxfp4_quant" else 0.0
             items.append({"workload": f"{name}: {xw.label}", "value": (flops / (unit * 1e-3) / 1e12) if flops else None,
                           "unit": "TFLOP/s", "kernel_ms": unit, "launches": n, "gpu_launches": nl,
                           "roofline": roofline_of(name, xw, unit, total * 1e-3, peaks, 1), "clocks": ck,
-                          "parity_check": {"ok": ok, "max_err": err}})
+                          "parity_check": {"ok": ok, "max_err": err}, "library_same_run": lib_run})
             del xw
             release()
         line["workloads"] = items

@@ -133,7 +133,8 @@ typedef struct tb_gemm_args {
    * unbounded, kernels/streamk_gemm.py:295-300). */
   int32_t wait_timeout_ms;
   /* Measurement and test switches, 0 in production. Bit 1 (value 2): per-role cycle counters are written to the start of
-   * `workspace` (148 x 16 int64). Bit 2 (value 4): stream-K programs never publish their partial tile, so the owners'
+   * `workspace` (148 x 16 int64: clocks spent waiting / issuing / draining per role in words 0-8, wall-clock stamps in ns of
+   * kernel entry, dependency wait, first filled stage, last MMA, last store and exit in words 9, 10, 12-15). Bit 2 (value 4): stream-K programs never publish their partial tile, so the owners'
    * bounded waits run out (RESULTS ARE WRONG; the failure-path test uses it). Bit 3 (value 8): every work item walks K
    * forwards. */
   int32_t debug_flags;

@@ -543,6 +543,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   constexpr bool prof = PROF;  // measurement instantiation: per-role cycle counters written to debug_out
 
   if (threadIdx.x == 0) {
+    // measurement instantiation: wall-clock stamps (ns) of this CTA's phases in words 9..15 of its counter block
+    if (prof && p.debug_out != nullptr) p.debug_out[blockIdx.x * 16 + 9] = static_cast<long long>(global_timer_ns());
     *abort_flag = 0;
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -563,6 +565,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // previous kernel of the stream when this launch was allowed to start before that one finished.
     griddep_launch_dependents();
     griddep_wait();
+    if (prof && p.debug_out != nullptr) p.debug_out[blockIdx.x * 16 + 10] = static_cast<long long>(global_timer_ns());
     if (p.group_offsets != nullptr) {
       // tile_prefix[0 .. G] = tiles before each group, followed by a copy of the G + 1 row offsets. The copy is clamped to
       // [0, M] and made non-decreasing: offsets that describe more rows than A and C hold (a receive buffer sized below
@@ -825,7 +828,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
       const uint32_t idesc = p.idesc;
       bool ok = true;
-      long long prof_full = 0, prof_tmem = 0, prof_issue = 0, prof_t0 = clock64();
+      long long prof_full = 0, prof_tmem = 0, prof_issue = 0, prof_t0 = clock64(), prof_first_full = 0;
       uint32_t acc_parity = 0u;  // bit a: parity of how often TMEM accumulator a has been handed to the epilogue
       // The four MMAs of one stage (32 bytes of K each) into one accumulator; called by the elected lane.
       auto issue_stage = [&](uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t first) {
@@ -872,6 +875,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (!ok) break;
             const long long pf1 = PROF ? clock64() : 0;
             if (PROF) prof_full += pf1 - pf0;
+            if (PROF && prof_first_full == 0) prof_first_full = static_cast<long long>(global_timer_ns());
             const uint64_t soff = static_cast<uint64_t>(s * stage_step);
             const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
             const uint32_t first = (kb > w.kb0) ? 1u : 0u;
@@ -963,6 +967,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
       }
       if (prof && p.debug_out != nullptr && lane == 0) {
+        p.debug_out[blockIdx.x * 16 + 12] = prof_first_full;
+        p.debug_out[blockIdx.x * 16 + 13] = static_cast<long long>(global_timer_ns());
         p.debug_out[blockIdx.x * 16 + 2] = prof_full;
         p.debug_out[blockIdx.x * 16 + 3] = prof_tmem;
         p.debug_out[blockIdx.x * 16 + 4] = prof_issue;
@@ -1210,6 +1216,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       if (nh == 1) acc ^= 1;
     }
     if (prof && p.debug_out != nullptr && threadIdx.x == kEpiWarp0 * 32) {
+      p.debug_out[blockIdx.x * 16 + 14] = static_cast<long long>(global_timer_ns());
       p.debug_out[blockIdx.x * 16 + 6] = prof_wait;
       p.debug_out[blockIdx.x * 16 + 7] = clock64() - prof_t0;
       p.debug_out[blockIdx.x * 16 + 8] = prof_drain;
@@ -1232,6 +1239,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc<CTAS>(tmem_base, p.tmem_cols);
   }
+  if (prof && p.debug_out != nullptr && threadIdx.x == 0) p.debug_out[blockIdx.x * 16 + 15] = static_cast<long long>(global_timer_ns());
 }
 
 }  // namespace tb
