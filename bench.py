@@ -261,6 +261,18 @@ class DenseWorkload:
             self.layers = [tbd.ColumnShardedGemm(bt) for bt in self.Bt]
             for layer in self.layers:
                 layer.enable_fused_gather(M, self.out_dtype, block_n=args.fused_block_n or None)
+        self.gps = max(int(args.gemms_per_step), 1)
+        self.overlap_tail = 0.0
+        if self.layers is not None:
+            # share of a product's tiles that is sent after the launch, beside the next product: what the link cannot
+            # carry while the product computes (link-bound shards), at least the tiles of the last wave
+            push_ms = (world - 1) * M * self.n_local * 2 / 600e9 * 1e3
+            compute_ms = 2.0 * M * self.n_local * K / 1.45e15 * 1e3
+            tiles = -(-M // 256) * -(-self.n_local // 256)
+            waves = -(-tiles // 74)
+            last_wave = (tiles - (waves - 1) * 74) / tiles
+            auto = max(last_wave, 1.0 - compute_ms / push_ms) if world > 2 else 0.0
+            self.overlap_tail = auto if args.overlap_tail < 0 else float(args.overlap_tail)
         self.sel = tb.OrigamiMatmulSelector(M, self.n_local, K, self.in_dtype, self.in_dtype, self.out_dtype, dev,
                                             streamk=self.streamk)
         self.cfg = tb.matmul_preamble(self.sel)
@@ -274,7 +286,9 @@ class DenseWorkload:
         self.extra = {"tile": f"{self.sel.block_m}x{self.sel.block_n}x{self.sel.block_k}", "cta_pair": self.sel.cta_pair,
                       "operand_sets": nsets,
                       "parallelism": (f"N-sharded x{world}, " + ("epilogue pushes C tiles to all ranks over NVLink "
-                                      "(symmetric memory) + barrier" if self.layers else "NCCL all-gather of C"))
+                                      "(symmetric memory) + barrier" + (f"; the last {self.overlap_tail:.2f} of every "
+                                      "product's tiles are sent from a side stream beside the step's next product"
+                                      if self.overlap_tail > 0 else "") if self.layers else "NCCL all-gather of C"))
                       if world > 1 else "single GPU"}
         # end-to-end leg: copies and compute on separate streams, double-buffered device operands
         self.s_in, self.s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
@@ -298,8 +312,15 @@ class DenseWorkload:
 
     def step(self, i, dist):
         if self.layers is not None:
-            # two gathered buffers alternate, so the opening barrier is not needed (see forward_fused)
-            return self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets], pre_barrier=self.nsets < 2)
+            # two gathered buffers alternate, so the opening barrier is not needed (see forward_fused). The last tiles of
+            # every product cross NVLink from a side stream while the next product of the step starts; the step ends when
+            # all of its products' gathered results are complete.
+            out = self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets], pre_barrier=self.nsets < 2,
+                                                            overlap_tail=self.overlap_tail)
+            if self.overlap_tail > 0 and (i + 1) % self.gps == 0:
+                for layer in self.layers:
+                    layer.wait_gathered()
+            return out
         c = self.gemm(i)
         if self.world > 1:
             dist.all_gather_into_tensor(self.Cg, c)
@@ -358,7 +379,7 @@ class DenseWorkload:
         every rank's block, against the CPU oracle."""
         from oracle import gemm_oracle
         out = self.step(0, dist)
-        torch.cuda.synchronize()
+        torch.cuda.synchronize()            # every stream of the device, the side stream of the tail copies included
         if dist is not None:
             dist.barrier()
         g = torch.Generator().manual_seed(2024)
@@ -697,6 +718,9 @@ def main():
                     help="moe workload on several GPUs: NCCL all-to-all dispatch/combine instead of the peer-memory kernels")
     ap.add_argument("--fused-block-n", type=int, default=0,
                     help="multi-GPU default workload: tile width of the fused GEMM + push launch (0 = the library's choice)")
+    ap.add_argument("--overlap-tail", type=float, default=-1.0,
+                    help="multi-GPU default workload: share of every product's tiles pushed after the launch from a side "
+                         "stream (0 = everything from the epilogue, -1 = chosen from the shard's compute and link times)")
     ap.add_argument("--contiguous-experts", action="store_true",
                     help="MoE on several GPUs: experts laid out over the ranks in id order instead of balanced by load")
     ap.add_argument("--nccl-gather", action="store_true",

@@ -144,6 +144,10 @@ typedef struct tb_gemm_args {
    * reads the tokens' rows in expert order straight from the activation matrix this way, with no gathered copy in between. */
   const int32_t* a_gather_index;
   int64_t a_rows;
+  /* Fan-out of only the first tiles (tb_gemm with c_copies). 0: every tile goes to the copies. > 0: only tiles with index
+   * below this do (the kernel enumerates tiles in waves, so these are the launch's first waves); the caller sends the rest
+   * with tb_push_c_tiles, typically on another stream beside the next launch, whose first tiles have nothing to send yet. */
+  int32_t c_copies_tile_limit;
 } tb_gemm_args;
 
 /* Fill `cfg` for `p`. Stands in for origami.select_config + OrigamiMatmulSelector._compute_sk_grid
@@ -156,6 +160,14 @@ int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override);
 
 /* Enqueue one GEMM. `cfg` may be NULL (the library selects). */
 int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream);
+
+/* Tiles of the data-parallel launch tb_gemm would make for (args, cfg): tb_gemm_tile_count gives their number (what
+ * c_copies_tile_limit is measured against); tb_push_c_tiles copies tiles [first_tile, count) of args->c into every
+ * args->c_copies[x], in the kernel's own tile order. For the tail of a launch made with c_copies_tile_limit = first_tile.
+ * 16-byte aligned rows of a unit-stride C; not for stream-K, grouped or transposed (swap_ab) configurations. No reference
+ * counterpart. */
+int tb_gemm_tile_count(const tb_gemm_args* args, const tb_config* cfg);
+int tb_push_c_tiles(const tb_gemm_args* args, const tb_config* cfg, int32_t first_tile, void* stream);
 
 /* Stream-K GEMM for callers that cannot allocate device memory: a serving process that handed all of HBM to its own
  * arena at start-up, or a latency path on which cudaMalloc (which synchronises the whole device) is not allowed, has no

@@ -156,6 +156,26 @@ def test_output_fan_out_to_further_buffers(m, n, k):
         assert torch.equal(t, c)
 
 
+@pytest.mark.parametrize("fraction", [0.3, 0.5, 1.0])
+@pytest.mark.parametrize("m,n,k,pair,bn,nh", [(2048, 4096, 512, 2, 256, 1), (1000, 3000, 264, 1, 128, 1), (2048, 4096, 512, 2, 256, 2),
+                                              (520, 776, 128, 2, 64, 1)])
+def test_output_fan_out_with_the_tail_tiles_sent_after_the_launch(m, n, k, pair, bn, nh, fraction):
+    """c_copies_tail_fraction: the epilogue sends only the launch's first tiles to the further buffers; a copy kernel on a
+    side stream sends the rest in the kernel's own tile order. Afterwards every buffer holds the whole product (checked on
+    one GPU with local buffers; ragged right and bottom edges included)."""
+    a, b = make_operands(m, n, k, torch.bfloat16, "T", "T", seed=19)
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    copies = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    sel = _selector(m, n, k, torch.bfloat16, cta_pair=pair, block_n=bn, n_halves=nh)
+    side = torch.cuda.Stream()
+    tb.persistent_matmul_lt(a, b, c, sel, None, c_copies=[t.data_ptr() for t in copies], c_copies_tail_stream=side,
+                            c_copies_tail_fraction=fraction)
+    torch.cuda.current_stream().wait_stream(side)
+    assert_close_to_oracle(c, a, b, what=f"tail fan-out {(m, n, k)}")
+    for t in copies:
+        assert torch.equal(t, c)
+
+
 @pytest.mark.parametrize("pair", [1, 2])
 def test_strided_output_and_out_argument(pair):
     m, n, k = 300, 200, 256

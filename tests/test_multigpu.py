@@ -33,6 +33,12 @@ layer.enable_fused_gather(M)
 for _ in range(2):
     c2 = tbd.ColumnShardedGemm.as_matrix(layer.forward_fused(a)).float()
     assert torch.allclose(c2, ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item()), "fused push path"
+for frac in (0.4, 1.0):        # the last tiles of the launch cross NVLink from a side stream
+    for _ in range(2):
+        g3 = layer.forward_fused(a, overlap_tail=frac)
+        layer.wait_gathered()
+        c4 = tbd.ColumnShardedGemm.as_matrix(g3).float()
+        assert torch.allclose(c4, ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item()), "fused push with tail copy"
 # expert-parallel MoE against a single-device evaluation of the same experts
 E, H, F, T, topk = 8, 256, 128, 64, 2
 w1 = (torch.randn(E, 2 * F, H, generator=g) * 0.1).to(torch.bfloat16).to(dev)

@@ -55,7 +55,7 @@ class GemmArgs(ctypes.Structure):
         ("c_copies", ctypes.POINTER(ctypes.c_void_p)), ("num_c_copies", ctypes.c_int32),
         ("tile_counter", ctypes.c_void_p), ("epilogue_op", ctypes.c_int32),
         ("wait_timeout_ms", ctypes.c_int32), ("debug_flags", ctypes.c_int32),
-        ("a_gather_index", ctypes.c_void_p), ("a_rows", ctypes.c_int64),
+        ("a_gather_index", ctypes.c_void_p), ("a_rows", ctypes.c_int64), ("c_copies_tile_limit", ctypes.c_int32),
     ]
 
 
@@ -82,6 +82,10 @@ def _load():
     lib.tb_gemm_workspace_bytes.restype = ctypes.c_int64
     lib.tb_gemm.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p]
     lib.tb_gemm.restype = ctypes.c_int
+    lib.tb_gemm_tile_count.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config)]
+    lib.tb_gemm_tile_count.restype = ctypes.c_int
+    lib.tb_push_c_tiles.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_int32, ctypes.c_void_p]
+    lib.tb_push_c_tiles.restype = ctypes.c_int
     lib.tb_gemm_streamk_builtin.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(Config), ctypes.c_void_p,
                                             ctypes.POINTER(ctypes.c_int32)]
     lib.tb_gemm_streamk_builtin.restype = ctypes.c_int

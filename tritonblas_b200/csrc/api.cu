@@ -225,6 +225,26 @@ static int builtin_scratch(unsigned char** out) {
   return TB_OK;
 }
 
+int launch_push_tiles(const void* c, void* const* peers, int n_peers, long long pitch_bytes, int m, long long n_bytes, int tile_m,
+                      int tile_n_bytes, int tiles_m, int tiles_n, int group_m, int first_tile, int num_tiles,
+                      cudaStream_t stream);  // push_tiles.cu
+
+// Tile grid of a dense data-parallel launch with this configuration: what the kernel enumerates and what a copy of
+// the launch's tail tiles must enumerate the same way.
+struct TileGrid {
+  int pair, bn, halves, tiles_m, tiles_n, group_m;
+};
+static TileGrid tile_grid(const tb_gemm_args& a, const tb_config& cfg) {
+  TileGrid g;
+  g.pair = cfg.cta_pair == 2 ? 2 : 1;
+  g.bn = cfg.block_n;
+  g.halves = (cfg.n_halves == 2 && !a.streamk) ? 2 : 1;
+  g.tiles_m = (a.m + 128 * g.pair - 1) / (128 * g.pair);
+  g.tiles_n = (a.n + g.bn * g.halves - 1) / (g.bn * g.halves);
+  g.group_m = cfg.group_m > 0 ? cfg.group_m : 8;
+  return g;
+}
+
 int gemm_fp32_exact(const tb_gemm_args& a, cudaStream_t stream);                 // simt_gemm.cu
 int gemm_generic_loader(const tb_gemm_args& a, const tb_config& cfg, cudaStream_t stream, int* status);  // unaligned operands
 
@@ -333,10 +353,11 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   p.n_halves = halves;
   p.k_per_stage = bk;
   p.num_k_blocks = (a.k + bk - 1) / bk;
-  p.tiles_m = (a.m + 128 * pair - 1) / (128 * pair);
+  const TileGrid tgrid = tile_grid(a, cfg);
+  p.tiles_m = tgrid.tiles_m;
   p.glu = glu ? 1 : 0;
-  p.tiles_n = glu ? a.n / (bn / 2) : (a.n + bn * halves - 1) / (bn * halves);
-  p.group_m = cfg.group_m > 0 ? cfg.group_m : 8;
+  p.tiles_n = glu ? a.n / (bn / 2) : tgrid.tiles_n;
+  p.group_m = tgrid.group_m;
   p.stages = stages;
   p.esize = es;
   p.a_mn = a_mn; p.b_mn = b_mn;
@@ -347,6 +368,7 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   if (a.num_c_copies < 0 || a.num_c_copies > 7 || (a.num_c_copies > 0 && a.c_copies == nullptr)) return TB_ERR_INVALID;
   for (int x = 0; x < a.num_c_copies; ++x) p.c_extra[x] = a.c_copies[x];
   p.num_c_extra = a.num_c_copies;
+  p.c_extra_tile_limit = a.c_copies_tile_limit > 0 ? a.c_copies_tile_limit : 0x7fffffff;
   {
     bool ok16 = (a.c_dtype == TB_DTYPE_BF16 || a.c_dtype == TB_DTYPE_F16) && a.c_stride_n == 1 && ((a.c_stride_m * 2) & 15) == 0 &&
                 (reinterpret_cast<uintptr_t>(a.c) & 15) == 0;
@@ -644,6 +666,30 @@ int64_t tb_gemm_workspace_bytes(const tb_config* cfg, int32_t sk_grid_override) 
 int tb_gemm(const tb_gemm_args* args, const tb_config* cfg, void* stream) {
   if (args == nullptr) return TB_ERR_INVALID;
   return tb::gemm_impl(*args, cfg, static_cast<cudaStream_t>(stream));
+}
+
+int tb_gemm_tile_count(const tb_gemm_args* args, const tb_config* cfg) {
+  if (args == nullptr || cfg == nullptr || args->m <= 0 || args->n <= 0 || cfg->block_n <= 0) return 0;
+  const tb::TileGrid g = tb::tile_grid(*args, *cfg);
+  return g.tiles_m * g.tiles_n;
+}
+
+int tb_push_c_tiles(const tb_gemm_args* args, const tb_config* cfg, int32_t first_tile, void* stream) {
+  if (args == nullptr || cfg == nullptr || args->c == nullptr || first_tile < 0) return TB_ERR_INVALID;
+  if (args->num_c_copies < 0 || args->num_c_copies > 7 || (args->num_c_copies > 0 && args->c_copies == nullptr)) return TB_ERR_INVALID;
+  if (cfg->swap_ab || args->streamk || args->group_offsets != nullptr || args->epilogue_op != TB_EPILOGUE_NONE) return TB_ERR_UNSUPPORTED;
+  const int es = tb::esize_of(args->c_dtype);
+  if (es == 0 || args->c_stride_n != 1) return TB_ERR_UNSUPPORTED;
+  const long long pitch = args->c_stride_m * es, n_bytes = static_cast<long long>(args->n) * es;
+  if ((pitch & 15) || (n_bytes & 15) || (reinterpret_cast<uintptr_t>(args->c) & 15)) return TB_ERR_ALIGNMENT;
+  for (int x = 0; x < args->num_c_copies; ++x)
+    if (reinterpret_cast<uintptr_t>(args->c_copies[x]) & 15) return TB_ERR_ALIGNMENT;
+  const tb::TileGrid g = tb::tile_grid(*args, *cfg);
+  const int tiles = g.tiles_m * g.tiles_n;
+  if (first_tile >= tiles) return TB_OK;
+  return tb::launch_push_tiles(args->c, args->c_copies, args->num_c_copies, pitch, args->m, n_bytes, 128 * g.pair,
+                               g.bn * g.halves * es, g.tiles_m, g.tiles_n, g.group_m, first_tile, tiles - first_tile,
+                               static_cast<cudaStream_t>(stream));
 }
 
 int tb_gemm_streamk_builtin(const tb_gemm_args* args, const tb_config* cfg, void* stream, int32_t* prev_status) {

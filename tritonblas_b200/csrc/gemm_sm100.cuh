@@ -66,6 +66,7 @@ struct GemmParams {
   // output and epilogue
   void* c_extra[7];  // further destinations with C's shape and strides (peer GPUs' buffers mapped into this process);
   int num_c_extra;   // every tile is stored to C and to each of them with ordinary stores
+  int c_extra_tile_limit;  // only tiles with index below this go to the further destinations (the caller pushes the rest)
   void* C;
   long long ldc_m, ldc_n;
   int c_dtype;
@@ -1033,6 +1034,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
       const float a_s = (p.a_scale != nullptr && row < row_end) ? p.a_scale[row] : 1.0f;
       const int nchunks = p.block_n / 32;
+      // further destinations of this tile (the tiles of a launch's tail may be left to a copy that follows the launch)
+      const int n_extra = w.tile < p.c_extra_tile_limit ? p.num_c_extra : 0;
       // staged stores need whole 32-column chunks inside N and 16-byte aligned rows in every destination (host-checked)
       const bool staged = owner && p.staged_store && (n0 + p.block_n <= p.N);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc_i * acc_stride);
@@ -1052,7 +1055,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           glu_drain<true>(p, stg, t_row, t_row + p.block_n / 2, p.block_n / 64, lane, q, m0, tg.n0, row_end, release_accumulator);
         else
           glu_drain<false>(p, stg, t_row, t_row + p.block_n / 2, p.block_n / 64, lane, q, m0, tg.n0, row_end, release_accumulator);
-      } else if (owner && staged && (p.block_n & 63) == 0 && (complete || p.num_c_extra == 0)) {
+      } else if (owner && staged && (p.block_n & 63) == 0 && (complete || n_extra == 0)) {
         // Common case (whole tile or a stream-K owner's fix-up, 16-bit row-major output, tile width a multiple of 64).
         // Every taken branch inside the drain loop costs an instruction refetch, and a handful of them per 64 columns is
         // what made a drain through the general path three to four times slower than its loads and stores take; so the
@@ -1069,7 +1072,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (!complete) {
           if (p.c_dtype == TB_BF16) { if (has_math) TB_FAST_DRAIN(true, true, false, true); else TB_FAST_DRAIN(true, false, false, true); }
           else { if (has_math) TB_FAST_DRAIN(false, true, false, true); else TB_FAST_DRAIN(false, false, false, true); }
-        } else if (p.num_c_extra > 0) {
+        } else if (n_extra > 0) {
           if (p.c_dtype == TB_BF16) { if (has_math) TB_FAST_DRAIN(true, true, true, false); else TB_FAST_DRAIN(true, false, true, false); }
           else { if (has_math) TB_FAST_DRAIN(false, true, true, false); else TB_FAST_DRAIN(false, false, true, false); }
         } else if (p.c_dtype == TB_BF16) {
@@ -1145,7 +1148,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
             if (!staged) {
               store_row_chunk(p, p.C, row, col0, v);
-              for (int x = 0; x < p.num_c_extra; ++x) store_row_chunk(p, p.c_extra[x], row, col0, v);
+              for (int x = 0; x < n_extra; ++x) store_row_chunk(p, p.c_extra[x], row, col0, v);
             }
           }
           if (staged) {
@@ -1190,7 +1193,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                   if (row_g < row_end) {
                     const long long off = static_cast<long long>(row_g) * p.ldc_m + colw + seg * 8;
                     *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.C) + off) = val[it];
-                    for (int x = 0; x < p.num_c_extra; ++x)
+                    for (int x = 0; x < n_extra; ++x)
                       *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.c_extra[x]) + off) = val[it];
                   }
                 }

@@ -39,6 +39,8 @@ class ColumnShardedGemm:
         if matmul_fn is None:
             from .matmul import matmul as matmul_fn
         self.matmul_fn = matmul_fn
+        self.tail_stream = None          # side stream of forward_fused(overlap_tail > 0)
+        self._tail_done = None
 
     def forward(self, a: torch.Tensor, out_local: Optional[torch.Tensor] = None, gathered: Optional[torch.Tensor] = None):
         c_local = self.matmul_fn(a, self.b_shard_t.T) if out_local is None else (self.matmul_fn(a, self.b_shard_t.T, out_local) or out_local)
@@ -73,7 +75,8 @@ class ColumnShardedGemm:
             self._fused_selector.override(block_n=int(block_n))     # tile width of the fused launch (tuning)
         return self._gathered
 
-    def forward_fused(self, a: torch.Tensor, pre_barrier: bool = True, b_shard_t: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward_fused(self, a: torch.Tensor, pre_barrier: bool = True, b_shard_t: Optional[torch.Tensor] = None,
+                      overlap_tail: float = 0.0) -> torch.Tensor:
         """One kernel computes this rank's block of C and pushes it into every rank's gathered buffer; a symmetric-memory
         barrier then orders the ranks. Returns this rank's (world, M, n_local) buffer.
 
@@ -81,15 +84,37 @@ class ColumnShardedGemm:
         overwrites them. It can be dropped (one barrier less per call) when calls alternate between two or more
         gathered buffers and each buffer is read on this stream before the next call is enqueued: a rank can then only
         start overwriting a buffer after every rank has passed the closing barrier of the call in between, which on each
-        rank's stream comes after its reads. ``b_shard_t`` replaces this rank's block of B for one call (same shape)."""
+        rank's stream comes after its reads. ``b_shard_t`` replaces this rank's block of B for one call (same shape).
+
+        ``overlap_tail`` in (0, 1]: the epilogue pushes only the first tiles; the last ``overlap_tail`` of the tiles are
+        copied to the peers, and the closing barrier runs, on a side stream (``self.tail_stream``). The call returns with
+        the GEMM enqueued on the current stream: a product enqueued next (one that does not read this gathered buffer)
+        starts while this one's last tiles are still crossing NVLink, at the time its own first tiles have nothing to
+        send. ``wait_gathered()`` makes the current stream wait until this rank's buffer is complete."""
         from .matmul import persistent_matmul_lt
         if pre_barrier:
             self._handle.barrier(channel=0)      # nobody is still reading the previous contents
         b_t = self.b_shard_t if b_shard_t is None else b_shard_t
-        persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None,
-                             c_copies=self._peer_slots)
-        self._handle.barrier(channel=1)          # every rank's pushes have landed
+        if overlap_tail <= 0.0:
+            persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None, c_copies=self._peer_slots)
+            self._handle.barrier(channel=1)      # every rank's pushes have landed
+            return self._gathered
+        if self.tail_stream is None:
+            self.tail_stream = torch.cuda.Stream(a.device)
+        if self._tail_done is not None:
+            torch.cuda.current_stream(a.device).wait_event(self._tail_done)   # the previous tail copy has read its tiles
+        persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None, c_copies=self._peer_slots,
+                             c_copies_tail_stream=self.tail_stream, c_copies_tail_fraction=overlap_tail)
+        with torch.cuda.stream(self.tail_stream):
+            self._handle.barrier(channel=1)      # every rank's pushes, epilogue and tail copy, have landed
+            self._tail_done = self.tail_stream.record_event()
         return self._gathered
+
+    def wait_gathered(self):
+        """Make the current stream wait for the side stream's tail copy and closing barrier of the last
+        ``forward_fused(..., overlap_tail > 0)`` call."""
+        if self._tail_done is not None:
+            torch.cuda.current_stream().wait_event(self._tail_done)
 
     @staticmethod
     def as_matrix(gathered: torch.Tensor) -> torch.Tensor:

@@ -127,7 +127,7 @@ def _ptr(t):
 
 
 def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, streamk=False, sk_grid=None,
-          c_copies=None, work_stealing=False):
+          c_copies=None, work_stealing=False, c_copies_tail_stream=None, c_copies_tail_fraction=0.0):
     assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
     if not (a.is_cuda and b.is_cuda and c.is_cuda):
         raise RuntimeError("tritonblas_b200 runs on CUDA tensors only (no CPU path)")
@@ -166,6 +166,14 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
         # raw device addresses of further destinations laid out exactly like c (peer GPUs' buffers)
         ptrs = (ctypes.c_void_p * len(c_copies))(*[int(p) for p in c_copies])
         args.c_copies, args.num_c_copies = ptrs, len(c_copies)
+    tail_first = None
+    if c_copies and c_copies_tail_stream is not None and c_copies_tail_fraction > 0 and not streamk and not cfg.swap_ab \
+            and c.stride(1) == 1 and (c.stride(0) * c.element_size()) % 16 == 0 and (N * c.element_size()) % 16 == 0 \
+            and _tma_loadable(a) and _tma_loadable(b) and (a.dtype != torch.float32 or torch.backends.cuda.matmul.allow_tf32):
+        tiles = int(_lib.lib.tb_gemm_tile_count(ctypes.byref(args), ctypes.byref(cfg)))
+        first = tiles - int(tiles * min(float(c_copies_tail_fraction), 1.0))
+        if 0 < first < tiles:
+            args.c_copies_tile_limit = tail_first = first
     args.allow_tf32 = int(torch.backends.cuda.matmul.allow_tf32)
     if config is not None:
         args.wait_timeout_ms, args.debug_flags = int(config.wait_timeout_ms), int(config.debug_flags)
@@ -187,16 +195,28 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
             rc = _lib.lib.tb_gemm(ctypes.byref(args), ctypes.byref(cfg), _lib.current_stream_ptr(a.device))
     if rc:
         _lib.check(rc, "tb_gemm")
+    if tail_first is not None:
+        # the launch's last tiles travel on the side stream, beside whatever the caller enqueues next on this one
+        main = torch.cuda.current_stream(a.device)
+        c_copies_tail_stream.wait_stream(main)
+        with torch.cuda.stream(c_copies_tail_stream):
+            rc = _lib.lib.tb_push_c_tiles(ctypes.byref(args), ctypes.byref(cfg), tail_first,
+                                          ctypes.c_void_p(c_copies_tail_stream.cuda_stream))
+        _lib.check(rc, "tb_push_c_tiles")
     return c
 
 
 def persistent_matmul_lt(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, quantized=False,
-                         work_stealing=False, c_copies=None):
+                         work_stealing=False, c_copies=None, c_copies_tail_stream=None, c_copies_tail_fraction=0.0):
     """Data-parallel persistent GEMM (reference: matmul.py:69-200). ``work_stealing`` selects the dynamic tile schedule
     (tiles taken from a device counter, matmul.py:112-159) instead of the static round-robin. ``c_copies``: device addresses of further buffers laid out like ``c`` (peer GPUs) that the
-    epilogue also writes."""
+    epilogue also writes. With ``c_copies_tail_stream`` (a torch.cuda.Stream) and ``c_copies_tail_fraction`` in (0, 1] the
+    epilogue sends only the first tiles and the last ``fraction`` of the tiles are copied to the peers by a kernel on that
+    stream after the launch, where they overlap whatever is enqueued next on the current stream; the caller waits for that
+    stream before the copies are read."""
     return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=False, c_copies=c_copies,
-                 work_stealing=work_stealing)
+                 work_stealing=work_stealing, c_copies_tail_stream=c_copies_tail_stream,
+                 c_copies_tail_fraction=c_copies_tail_fraction)
 
 
 def streamk_matmul_lt(a, b, c, selector, config=None, bias=None, sk_grid=None, a_scale=None, b_scale=None,
