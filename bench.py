@@ -264,14 +264,12 @@ class DenseWorkload:
         self.gps = max(int(args.gemms_per_step), 1)
         self.overlap_tail = 0.0
         if self.layers is not None:
-            # share of a product's tiles that is sent after the launch, beside the next product: what the link cannot
-            # carry while the product computes (link-bound shards), at least the tiles of the last wave
-            push_ms = (world - 1) * M * self.n_local * 2 / 600e9 * 1e3
-            compute_ms = 2.0 * M * self.n_local * K / 1.45e15 * 1e3
-            tiles = -(-M // 256) * -(-self.n_local // 256)
-            waves = -(-tiles // 74)
-            last_wave = (tiles - (waves - 1) * 74) / tiles
-            auto = max(last_wave, 1.0 - compute_ms / push_ms) if world > 2 else 0.0
+            # Share of a product's tiles sent after the launch from a side stream, beside the next product. Measured on 4 GPUs
+            # (value in TFLOP/s, per-step join): 0 -> 4059, 0.15 -> 4028, 0.3 -> 3977, 0.5 -> 3801, 1.0 -> 4196: pushes from
+            # the epilogue hold accumulators back while the link is busy and the link idles during a launch's first wave, so
+            # from 4 GPUs up (where the step is link-bound) the whole transfer goes to the side stream; on 2 GPUs the
+            # epilogue push is hidden behind compute and stays.
+            auto = 1.0 if world > 2 else 0.0
             self.overlap_tail = auto if args.overlap_tail < 0 else float(args.overlap_tail)
         self.sel = tb.OrigamiMatmulSelector(M, self.n_local, K, self.in_dtype, self.in_dtype, self.out_dtype, dev,
                                             streamk=self.streamk)
@@ -283,13 +281,18 @@ class DenseWorkload:
         self.h2d = es * (M * K + self.n_local * K)
         self.d2h = 2 * M * self.n_local
         self.label = dense_label(wl)
+        if world == 1:
+            how = "single GPU"
+        elif self.layers is None:
+            how = f"N-sharded x{world}, NCCL all-gather of C"
+        elif self.overlap_tail <= 0:
+            how = f"N-sharded x{world}, epilogue pushes C tiles to all ranks over NVLink (symmetric memory) + barrier"
+        else:
+            how = (f"N-sharded x{world}, the last {self.overlap_tail:.2f} of every product's C tiles are copied to all ranks over "
+                   "NVLink by a kernel on a side stream beside the next product, the rest by the epilogue (symmetric memory) "
+                   "+ barrier; the timed region ends after every transfer and barrier")
         self.extra = {"tile": f"{self.sel.block_m}x{self.sel.block_n}x{self.sel.block_k}", "cta_pair": self.sel.cta_pair,
-                      "operand_sets": nsets,
-                      "parallelism": (f"N-sharded x{world}, " + ("epilogue pushes C tiles to all ranks over NVLink "
-                                      "(symmetric memory) + barrier" + (f"; the last {self.overlap_tail:.2f} of every "
-                                      "product's tiles are sent from a side stream beside the step's next product"
-                                      if self.overlap_tail > 0 else "") if self.layers else "NCCL all-gather of C"))
-                      if world > 1 else "single GPU"}
+                      "operand_sets": nsets, "parallelism": how}
         # end-to-end leg: copies and compute on separate streams, double-buffered device operands
         self.s_in, self.s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         self.a_dev = [torch.empty_like(self.A[0]) for _ in range(2)]
@@ -312,20 +315,23 @@ class DenseWorkload:
 
     def step(self, i, dist):
         if self.layers is not None:
-            # two gathered buffers alternate, so the opening barrier is not needed (see forward_fused). The last tiles of
-            # every product cross NVLink from a side stream while the next product of the step starts; the step ends when
-            # all of its products' gathered results are complete.
-            out = self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets], pre_barrier=self.nsets < 2,
-                                                            overlap_tail=self.overlap_tail)
-            if self.overlap_tail > 0 and (i + 1) % self.gps == 0:
-                for layer in self.layers:
-                    layer.wait_gathered()
-            return out
+            # two gathered buffers alternate, so the opening barrier is not needed (see forward_fused). With overlap_tail
+            # the tiles of a product cross NVLink from a side stream while the next product computes (products are
+            # independent: nothing reads a gathered result before `finish`); the launch loop never waits, the timed
+            # region ends only after every product's transfer and closing barrier (`finish`).
+            return self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets], pre_barrier=self.nsets < 2,
+                                                             overlap_tail=self.overlap_tail)
         c = self.gemm(i)
         if self.world > 1:
             dist.all_gather_into_tensor(self.Cg, c)
             return self.Cg.view(self.world, self.M, self.n_local)
         return c
+
+    def finish(self):
+        """Make the launching stream wait for everything the steps left on side streams (inside the timed region)."""
+        if self.layers is not None and self.overlap_tail > 0:
+            for layer in self.layers:
+                layer.wait_gathered()
 
     def cublas_step(self, i):
         """torch.matmul (cuBLAS), or torch._scaled_mm (cuBLASLt, row-wise scales) for fp8, on the same operands, for the
@@ -611,13 +617,16 @@ class Runner:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return t[0].item() == 0.0, t[1].item()
 
-    def timed(self, step, n_warm, n_timed, clocks=True, first=0):
-        """(total ms, mean ms of one call, clocks, launches of this library) of n_timed calls of step(i)."""
+    def timed(self, step, n_warm, n_timed, clocks=True, first=0, finish=None):
+        """(total ms, mean ms of one call, clocks, launches of this library) of n_timed calls of step(i). ``finish`` runs
+        after the last call and before the closing event (joins side streams: their work is inside the timed region)."""
         from tritonblas_b200 import _lib
         it = first
         for _ in range(n_warm):
             step(it)
             it += 1
+        if finish is not None:
+            finish()
         self.barrier()
         launches0 = _lib.lib.tb_launch_count()
         sampler = ClockSampler(self.local_rank) if (clocks and self.rank == 0) else None
@@ -635,6 +644,8 @@ class Runner:
             e1.record(self.stream)
             events.append((e0, e1))
             it += 1
+        if finish is not None:
+            finish()
         t1.record(self.stream)
         self.barrier()
         wall1 = time.time()
@@ -642,6 +653,8 @@ class Runner:
         launches = _lib.lib.tb_launch_count() - launches0
         total = t0.elapsed_time(t1)
         unit = sum(a.elapsed_time(b) for a, b in events) / len(events)
+        if finish is not None:
+            unit = total / n_timed      # calls overlap one another across streams: only the whole region's time counts
         total, unit = self.max_over_ranks(total, unit)
         if self.world > 1:
             lt = torch.tensor([launches], device=self.dev, dtype=torch.int64)
@@ -751,7 +764,8 @@ def main():
 
     w = make_workload(args.workload, args, dev, rank, world, **({"nccl": args.nccl_moe} if args.workload == "moe" else {}))
     gps = 1 if args.workload == "moe" else args.gemms_per_step
-    ms_total, unit_ms, clocks, launches = run.timed(lambda i: w.step(i, dist), args.warmup * gps, args.steps * gps)
+    join = w.finish if (isinstance(w, DenseWorkload) and w.overlap_tail > 0) else None
+    ms_total, unit_ms, clocks, launches = run.timed(lambda i: w.step(i, dist), args.warmup * gps, args.steps * gps, finish=join)
     status = tb.device_status(local_rank)
 
     e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))

@@ -90,7 +90,10 @@ class ColumnShardedGemm:
         copied to the peers, and the closing barrier runs, on a side stream (``self.tail_stream``). The call returns with
         the GEMM enqueued on the current stream: a product enqueued next (one that does not read this gathered buffer)
         starts while this one's last tiles are still crossing NVLink, at the time its own first tiles have nothing to
-        send. ``wait_gathered()`` makes the current stream wait until this rank's buffer is complete."""
+        send. ``wait_gathered()`` makes the current stream wait until this rank's buffer is complete. The launching stream
+        never waits for a barrier in this mode, so a caller that READS the gathered buffers must keep ``pre_barrier=True``
+        (every rank arrives there only after its reads of the previous contents are enqueued); products nobody reads in
+        between (a throughput run) can drop it when two buffers alternate."""
         from .matmul import persistent_matmul_lt
         if pre_barrier:
             self._handle.barrier(channel=0)      # nobody is still reading the previous contents
