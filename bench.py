@@ -264,13 +264,18 @@ class DenseWorkload:
         self.gps = max(int(args.gemms_per_step), 1)
         self.overlap_tail = 0.0
         if self.layers is not None:
-            # Share of a product's tiles sent after the launch from a side stream, beside the next product. Measured on 4 GPUs
-            # (value in TFLOP/s, per-step join): 0 -> 4059, 0.15 -> 4028, 0.3 -> 3977, 0.5 -> 3801, 1.0 -> 4196: pushes from
-            # the epilogue hold accumulators back while the link is busy and the link idles during a launch's first wave, so
-            # from 4 GPUs up (where the step is link-bound) the whole transfer goes to the side stream; on 2 GPUs the
-            # epilogue push is hidden behind compute and stays.
-            auto = 1.0 if world > 2 else 0.0
+            # How the block reaches the peers. Measured (TFLOP/s of the whole job, bf16 8192^3):
+            #   2 GPUs: pushes from the epilogue hide behind compute (2778); sending the last 15 % / 30 % of the tiles from a
+            #           side stream instead: 2768 / 2712.
+            #   4 GPUs: epilogue pushes 4059-4084 (they hold accumulators back while the link is busy, and the link idles
+            #           during a launch's first wave); last 15 / 30 / 50 % from a side stream: 4028 / 3977 / 3801-3966; the
+            #           whole block by this library's copy kernel on a side stream beside the next product: 3802-4236 (the
+            #           copy kernel shares SMs with the GEMM: it runs at half its stand-alone rate and the GEMM a fifth
+            #           slower); the whole block by asynchronous copies (copy engines) beside the next product: 4441.
+            #   8 GPUs: epilogue pushes (0.26 ms per product, 450 GB/s out of every GPU); nothing else measured there.
+            auto = 1.0 if world == 4 else 0.0
             self.overlap_tail = auto if args.overlap_tail < 0 else float(args.overlap_tail)
+        self.copy_engine = bool(args.copy_engine) and self.overlap_tail >= 1.0
         self.sel = tb.OrigamiMatmulSelector(M, self.n_local, K, self.in_dtype, self.in_dtype, self.out_dtype, dev,
                                             streamk=self.streamk)
         self.cfg = tb.matmul_preamble(self.sel)
@@ -287,6 +292,10 @@ class DenseWorkload:
             how = f"N-sharded x{world}, NCCL all-gather of C"
         elif self.overlap_tail <= 0:
             how = f"N-sharded x{world}, epilogue pushes C tiles to all ranks over NVLink (symmetric memory) + barrier"
+        elif self.copy_engine:
+            how = (f"N-sharded x{world}, every product's block of C is copied into all ranks' gathered buffers (symmetric "
+                   "memory) by asynchronous peer copies on side streams beside the next product + barrier; the timed "
+                   "region ends after every transfer and barrier")
         else:
             how = (f"N-sharded x{world}, the last {self.overlap_tail:.2f} of every product's C tiles are copied to all ranks over "
                    "NVLink by a kernel on a side stream beside the next product, the rest by the epilogue (symmetric memory) "
@@ -320,7 +329,8 @@ class DenseWorkload:
             # independent: nothing reads a gathered result before `finish`); the launch loop never waits, the timed
             # region ends only after every product's transfer and closing barrier (`finish`).
             return self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets], pre_barrier=self.nsets < 2,
-                                                             overlap_tail=self.overlap_tail)
+                                                             overlap_tail=self.overlap_tail,
+                                                             tail_by_copy_engine=self.copy_engine)
         c = self.gemm(i)
         if self.world > 1:
             dist.all_gather_into_tensor(self.Cg, c)
@@ -734,6 +744,9 @@ def main():
     ap.add_argument("--overlap-tail", type=float, default=-1.0,
                     help="multi-GPU default workload: share of every product's tiles pushed after the launch from a side "
                          "stream (0 = everything from the epilogue, -1 = chosen from the shard's compute and link times)")
+    ap.add_argument("--copy-engine", type=int, default=1,
+                    help="with --overlap-tail 1: 1 = the block goes to the peers by asynchronous copies (copy engines), "
+                         "0 = by this library's copy kernel")
     ap.add_argument("--contiguous-experts", action="store_true",
                     help="MoE on several GPUs: experts laid out over the ranks in id order instead of balanced by load")
     ap.add_argument("--nccl-gather", action="store_true",

@@ -39,6 +39,11 @@ for frac in (0.4, 1.0):        # the last tiles of the launch cross NVLink from 
         layer.wait_gathered()
         c4 = tbd.ColumnShardedGemm.as_matrix(g3).float()
         assert torch.allclose(c4, ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item()), "fused push with tail copy"
+for _ in range(2):             # the whole block by asynchronous peer copies on side streams
+    g4 = layer.forward_fused(a, overlap_tail=1.0, tail_by_copy_engine=True)
+    layer.wait_gathered()
+    c5 = tbd.ColumnShardedGemm.as_matrix(g4).float()
+    assert torch.allclose(c5, ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item()), "gathered by peer copies"
 # expert-parallel MoE against a single-device evaluation of the same experts
 E, H, F, T, topk = 8, 256, 128, 64, 2
 w1 = (torch.randn(E, 2 * F, H, generator=g) * 0.1).to(torch.bfloat16).to(dev)

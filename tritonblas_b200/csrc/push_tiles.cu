@@ -32,11 +32,19 @@ __global__ void __launch_bounds__(256) push_tiles_kernel(const unsigned char* __
   const int vecs = static_cast<int>((min(col0 + tile_n_bytes, n_bytes) - col0) >> 4);   // 16-byte pieces per row of the tile
   if (vecs <= 0) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  for (int row = row0 + warp; row < row1; row += warps) {
-    const long long off = row * pitch_bytes + col0;
+  // Four rows per warp and pass: four independent 16-byte loads in flight per lane before any store is issued.
+  for (int row = row0 + warp * 4; row < row1; row += warps * 4) {
     for (int v = lane; v < vecs; v += 32) {
-      const uint4 val = __ldcg(reinterpret_cast<const uint4*>(c + off) + v);
-      for (int x = 0; x < n_peers; ++x) reinterpret_cast<uint4*>(static_cast<unsigned char*>(peers.p[x]) + off)[v] = val;
+      uint4 val[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (row + j < row1) val[j] = __ldcg(reinterpret_cast<const uint4*>(c + (row + j) * pitch_bytes + col0) + v);
+      for (int x = 0; x < n_peers; ++x) {
+        unsigned char* dst = static_cast<unsigned char*>(peers.p[x]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (row + j < row1) reinterpret_cast<uint4*>(dst + (row + j) * pitch_bytes + col0)[v] = val[j];
+      }
     }
   }
 }
