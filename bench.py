@@ -260,7 +260,7 @@ class DenseWorkload:
             from tritonblas_b200 import distributed as tbd
             self.layers = [tbd.ColumnShardedGemm(bt) for bt in self.Bt]
             for layer in self.layers:
-                layer.enable_fused_gather(M, self.out_dtype, block_n=args.fused_block_n or None)
+                layer.enable_fused_gather(M, self.out_dtype, block_n=args.fused_block_n or None, reserve_sms=args.reserve_sms)
         self.gps = max(int(args.gemms_per_step), 1)
         self.overlap_tail = 0.0
         if self.layers is not None:
@@ -744,6 +744,8 @@ def main():
     ap.add_argument("--overlap-tail", type=float, default=-1.0,
                     help="multi-GPU default workload: share of every product's tiles pushed after the launch from a side "
                          "stream (0 = everything from the epilogue, -1 = chosen from the shard's compute and link times)")
+    ap.add_argument("--reserve-sms", type=int, default=0,
+                    help="multi-GPU default workload: SMs the GEMM leaves to the copy kernel of --overlap-tail (with --copy-engine 0)")
     ap.add_argument("--copy-engine", type=int, default=1,
                     help="with --overlap-tail 1: 1 = the block goes to the peers by asynchronous copies (copy engines), "
                          "0 = by this library's copy kernel")

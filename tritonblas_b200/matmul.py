@@ -172,8 +172,12 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
             and _tma_loadable(a) and _tma_loadable(b) and (a.dtype != torch.float32 or torch.backends.cuda.matmul.allow_tf32):
         tiles = int(_lib.lib.tb_gemm_tile_count(ctypes.byref(args), ctypes.byref(cfg)))
         first = tiles - int(tiles * min(float(c_copies_tail_fraction), 1.0))
-        if 0 < first < tiles:
-            args.c_copies_tile_limit = tail_first = first
+        if 0 <= first < tiles:
+            tail_first = first
+            if first > 0:
+                args.c_copies_tile_limit = first
+            else:
+                args.num_c_copies = 0       # nothing leaves from the epilogue; the copy kernel sends every tile
     args.allow_tf32 = int(torch.backends.cuda.matmul.allow_tf32)
     if config is not None:
         args.wait_timeout_ms, args.debug_flags = int(config.wait_timeout_ms), int(config.debug_flags)
@@ -199,6 +203,7 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
         # the launch's last tiles travel on the side stream, beside whatever the caller enqueues next on this one
         main = torch.cuda.current_stream(a.device)
         c_copies_tail_stream.wait_stream(main)
+        args.num_c_copies = len(c_copies)
         with torch.cuda.stream(c_copies_tail_stream):
             rc = _lib.lib.tb_push_c_tiles(ctypes.byref(args), ctypes.byref(cfg), tail_first,
                                           ctypes.c_void_p(c_copies_tail_stream.cuda_stream))
