@@ -168,12 +168,16 @@ def test_output_fan_out_with_the_tail_tiles_sent_after_the_launch(m, n, k, pair,
     copies = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
     sel = _selector(m, n, k, torch.bfloat16, cta_pair=pair, block_n=bn, n_halves=nh)
     side = torch.cuda.Stream()
-    tb.persistent_matmul_lt(a, b, c, sel, None, c_copies=[t.data_ptr() for t in copies], c_copies_tail_stream=side,
-                            c_copies_tail_fraction=fraction)
-    torch.cuda.current_stream().wait_stream(side)
-    assert_close_to_oracle(c, a, b, what=f"tail fan-out {(m, n, k)}")
-    for t in copies:
-        assert torch.equal(t, c)
+    for ws in (False, True):       # static and dynamic tile schedule (the tile index decides who sends a tile, not the program)
+        c.fill_(float("nan"))
+        for t in copies:
+            t.fill_(float("nan"))
+        tb.persistent_matmul_lt(a, b, c, sel, None, c_copies=[t.data_ptr() for t in copies], c_copies_tail_stream=side,
+                                c_copies_tail_fraction=fraction, work_stealing=ws)
+        torch.cuda.current_stream().wait_stream(side)
+        assert_close_to_oracle(c, a, b, what=f"tail fan-out {(m, n, k)} ws={ws}")
+        for t in copies:
+            assert torch.equal(t, c)
 
 
 @pytest.mark.parametrize("pair", [1, 2])
