@@ -260,7 +260,7 @@ class DenseWorkload:
             from tritonblas_b200 import distributed as tbd
             self.layers = [tbd.ColumnShardedGemm(bt) for bt in self.Bt]
             for layer in self.layers:
-                layer.enable_fused_gather(M, self.out_dtype, block_n=args.fused_block_n or None, reserve_sms=args.reserve_sms)
+                layer.enable_fused_gather(M, self.out_dtype, block_n=args.fused_block_n or None)
         self.gps = max(int(args.gemms_per_step), 1)
         self.overlap_tail = 0.0
         if self.layers is not None:
@@ -269,9 +269,11 @@ class DenseWorkload:
             #           side stream instead: 2768 / 2712.
             #   4 GPUs: epilogue pushes 4059-4084 (they hold accumulators back while the link is busy, and the link idles
             #           during a launch's first wave); last 15 / 30 / 50 % from a side stream: 4028 / 3977 / 3801-3966; the
-            #           whole block by this library's copy kernel on a side stream beside the next product: 3802-4236 (the
-            #           copy kernel shares SMs with the GEMM: it runs at half its stand-alone rate and the GEMM a fifth
-            #           slower); the whole block by asynchronous copies (copy engines) beside the next product: 4441.
+            #           epilogue pushes with only the closing barrier on a side stream: 4196-4236; the whole block by this
+            #           library's copy kernel on a side stream beside the next product: 3350 (the copy kernel shares SMs
+            #           with the GEMM: it runs at half its stand-alone rate and the GEMM a fifth slower; kept off the GEMM's
+            #           SMs, with the GEMM on 8-16 fewer: 3191-3214); the whole block by asynchronous copies (copy
+            #           engines) beside the next product: 4407-4441.
             #   8 GPUs: epilogue pushes (0.26 ms per product, 450 GB/s out of every GPU); nothing else measured there.
             auto = 1.0 if world == 4 else 0.0
             self.overlap_tail = auto if args.overlap_tail < 0 else float(args.overlap_tail)
@@ -744,8 +746,6 @@ def main():
     ap.add_argument("--overlap-tail", type=float, default=-1.0,
                     help="multi-GPU default workload: share of every product's tiles pushed after the launch from a side "
                          "stream (0 = everything from the epilogue, -1 = chosen from the shard's compute and link times)")
-    ap.add_argument("--reserve-sms", type=int, default=0,
-                    help="multi-GPU default workload: SMs the GEMM leaves to the copy kernel of --overlap-tail (with --copy-engine 0)")
     ap.add_argument("--copy-engine", type=int, default=1,
                     help="with --overlap-tail 1: 1 = the block goes to the peers by asynchronous copies (copy engines), "
                          "0 = by this library's copy kernel")

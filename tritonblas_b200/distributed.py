@@ -55,7 +55,7 @@ class ColumnShardedGemm:
                                     group=self.group)
         return gathered
 
-    def enable_fused_gather(self, m: int, dtype=None, block_n: Optional[int] = None, reserve_sms: int = 0):
+    def enable_fused_gather(self, m: int, dtype=None, block_n: Optional[int] = None):
         """Allocate the gathered C (world, M, n_local) in symmetric memory and map every peer's copy, so that
         forward_fused() can let the GEMM epilogue write each tile straight into all ranks' buffers over NVLink
         (ordinary stores to peer-mapped memory; no TMA or multicast access to peer memory is involved)."""
@@ -71,14 +71,8 @@ class ColumnShardedGemm:
         from .origami import OrigamiMatmulSelector
         # narrow tiles: their drains, which here also carry the pushes to every peer over NVLink, hide behind the next
         # tile's main loop; a wide tile's drains are exposed (8 GPUs: 3.88 PFLOP/s wide against 4.11 narrow)
-        # reserve_sms: the GEMM runs on that many fewer SMs (with the dynamic tile schedule, so programs that start late
-        # take fewer tiles), which leaves SMs to the copy kernel of forward_fused(overlap_tail > 0): it never shares an SM
-        # with a GEMM CTA, so it can only run there
-        self._reserve_sms = int(reserve_sms)
-        n_sms = 148
         self._fused_selector = OrigamiMatmulSelector(m, n_local, self.b_shard_t.shape[1], self.b_shard_t.dtype,
-                                                     self.b_shard_t.dtype, dtype, self.b_shard_t.device, max_halves=1,
-                                                     active_cus=(n_sms - self._reserve_sms) if self._reserve_sms > 0 else None)
+                                                     self.b_shard_t.dtype, dtype, self.b_shard_t.device, max_halves=1)
         if block_n:
             self._fused_selector.override(block_n=int(block_n))     # tile width of the fused launch (tuning)
         return self._gathered
@@ -135,8 +129,7 @@ class ColumnShardedGemm:
                 self.tail_stream.wait_stream(st)
         else:
             persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None, c_copies=self._peer_slots,
-                                 c_copies_tail_stream=self.tail_stream, c_copies_tail_fraction=overlap_tail,
-                                 work_stealing=self._reserve_sms > 0)
+                                 c_copies_tail_stream=self.tail_stream, c_copies_tail_fraction=overlap_tail)
         with torch.cuda.stream(self.tail_stream):
             self._handle.barrier(channel=1)      # every rank's pushes, epilogue and tail copy, have landed
             self._tail_done = self.tail_stream.record_event()
