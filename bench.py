@@ -278,6 +278,7 @@ class DenseWorkload:
             auto = 1.0 if world == 4 else 0.0
             self.overlap_tail = auto if args.overlap_tail < 0 else float(args.overlap_tail)
         self.copy_engine = bool(args.copy_engine) and self.overlap_tail >= 1.0
+        self.side_barrier = self.layers is not None and self.overlap_tail <= 0 and bool(args.side_barrier)
         self.sel = tb.OrigamiMatmulSelector(M, self.n_local, K, self.in_dtype, self.in_dtype, self.out_dtype, dev,
                                             streamk=self.streamk)
         self.cfg = tb.matmul_preamble(self.sel)
@@ -293,7 +294,8 @@ class DenseWorkload:
         elif self.layers is None:
             how = f"N-sharded x{world}, NCCL all-gather of C"
         elif self.overlap_tail <= 0:
-            how = f"N-sharded x{world}, epilogue pushes C tiles to all ranks over NVLink (symmetric memory) + barrier"
+            how = (f"N-sharded x{world}, epilogue pushes C tiles to all ranks over NVLink (symmetric memory) + barrier"
+                   + (" on a side stream (the next product does not wait for it; the timed region does)" if self.side_barrier else ""))
         elif self.copy_engine:
             how = (f"N-sharded x{world}, every product's block of C is copied into all ranks' gathered buffers (symmetric "
                    "memory) by asynchronous peer copies on side streams beside the next product + barrier; the timed "
@@ -332,7 +334,8 @@ class DenseWorkload:
             # region ends only after every product's transfer and closing barrier (`finish`).
             return self.layers[i % self.nsets].forward_fused(self.A[i % self.nsets], pre_barrier=self.nsets < 2,
                                                              overlap_tail=self.overlap_tail,
-                                                             tail_by_copy_engine=self.copy_engine)
+                                                             tail_by_copy_engine=self.copy_engine,
+                                                             barrier_on_side_stream=self.side_barrier)
         c = self.gemm(i)
         if self.world > 1:
             dist.all_gather_into_tensor(self.Cg, c)
@@ -341,7 +344,7 @@ class DenseWorkload:
 
     def finish(self):
         """Make the launching stream wait for everything the steps left on side streams (inside the timed region)."""
-        if self.layers is not None and self.overlap_tail > 0:
+        if self.layers is not None and (self.overlap_tail > 0 or self.side_barrier):
             for layer in self.layers:
                 layer.wait_gathered()
 
@@ -746,6 +749,9 @@ def main():
     ap.add_argument("--overlap-tail", type=float, default=-1.0,
                     help="multi-GPU default workload: share of every product's tiles pushed after the launch from a side "
                          "stream (0 = everything from the epilogue, -1 = chosen from the shard's compute and link times)")
+    ap.add_argument("--side-barrier", type=int, default=1,
+                    help="multi-GPU default workload with epilogue pushes: 1 = the closing barrier of every product runs on a "
+                         "side stream (the next product does not wait for the other ranks), 0 = on the launching stream")
     ap.add_argument("--copy-engine", type=int, default=1,
                     help="with --overlap-tail 1: 1 = the block goes to the peers by asynchronous copies (copy engines), "
                          "0 = by this library's copy kernel")
@@ -779,7 +785,7 @@ def main():
 
     w = make_workload(args.workload, args, dev, rank, world, **({"nccl": args.nccl_moe} if args.workload == "moe" else {}))
     gps = 1 if args.workload == "moe" else args.gemms_per_step
-    join = w.finish if (isinstance(w, DenseWorkload) and w.overlap_tail > 0) else None
+    join = w.finish if (isinstance(w, DenseWorkload) and (w.overlap_tail > 0 or w.side_barrier)) else None
     ms_total, unit_ms, clocks, launches = run.timed(lambda i: w.step(i, dist), args.warmup * gps, args.steps * gps, finish=join)
     status = tb.device_status(local_rank)
 

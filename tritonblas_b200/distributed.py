@@ -78,7 +78,8 @@ class ColumnShardedGemm:
         return self._gathered
 
     def forward_fused(self, a: torch.Tensor, pre_barrier: bool = True, b_shard_t: Optional[torch.Tensor] = None,
-                      overlap_tail: float = 0.0, tail_by_copy_engine: bool = False) -> torch.Tensor:
+                      overlap_tail: float = 0.0, tail_by_copy_engine: bool = False,
+                      barrier_on_side_stream: bool = False) -> torch.Tensor:
         """One kernel computes this rank's block of C and pushes it into every rank's gathered buffer; a symmetric-memory
         barrier then orders the ranks. Returns this rank's (world, M, n_local) buffer.
 
@@ -87,6 +88,8 @@ class ColumnShardedGemm:
         gathered buffers and each buffer is read on this stream before the next call is enqueued: a rank can then only
         start overwriting a buffer after every rank has passed the closing barrier of the call in between, which on each
         rank's stream comes after its reads. ``b_shard_t`` replaces this rank's block of B for one call (same shape).
+
+        ``barrier_on_side_stream``: the launch is as above but the closing barrier runs on ``self.tail_stream``.
 
         ``overlap_tail`` in (0, 1]: the epilogue pushes only the first tiles; the last ``overlap_tail`` of the tiles are
         copied to the peers, and the closing barrier runs, on a side stream (``self.tail_stream``). The call returns with
@@ -100,7 +103,7 @@ class ColumnShardedGemm:
         if pre_barrier:
             self._handle.barrier(channel=0)      # nobody is still reading the previous contents
         b_t = self.b_shard_t if b_shard_t is None else b_shard_t
-        if overlap_tail <= 0.0:
+        if overlap_tail <= 0.0 and not barrier_on_side_stream:
             persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None, c_copies=self._peer_slots)
             self._handle.barrier(channel=1)      # every rank's pushes have landed
             return self._gathered
@@ -127,9 +130,14 @@ class ColumnShardedGemm:
                 with torch.cuda.stream(st):
                     view.copy_(mine, non_blocking=True)
                 self.tail_stream.wait_stream(st)
-        else:
+        elif overlap_tail > 0.0:
             persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None, c_copies=self._peer_slots,
                                  c_copies_tail_stream=self.tail_stream, c_copies_tail_fraction=overlap_tail)
+        else:
+            # every tile leaves from the epilogue; only the closing barrier moves to the side stream, so the next product
+            # (one that does not read this result) starts without waiting for the other ranks
+            persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None, c_copies=self._peer_slots)
+            self.tail_stream.wait_stream(main)
         with torch.cuda.stream(self.tail_stream):
             self._handle.barrier(channel=1)      # every rank's pushes, epilogue and tail copy, have landed
             self._tail_done = self.tail_stream.record_event()
