@@ -45,14 +45,15 @@ if ROOT not in sys.path:
 FP8 = torch.float8_e4m3fn
 NOMINAL_TFLOPS = {"bf16": 2250.0, "fp16": 2250.0, "fp8": 4500.0, "mxfp4": 9000.0}
 
-# name: dict(M, N, K, dtype, streamk, bound)
+# name: dict(M, N, K, dtype, streamk, bound[, static_b]). static_b: the decode shapes promise the library that B (the
+# weights) is not written by anything in flight, which lets a kernel start fetching it while its predecessor drains.
 WORKLOADS = {
     "bf16_8192": dict(M=8192, N=8192, K=8192, dtype="bf16", streamk=False, bound="tensor"),
     "fp16_1024": dict(M=1024, N=1024, K=1024, dtype="fp16", streamk=False, bound="tensor"),
-    "bf16_skinny_m1": dict(M=1, N=28672, K=8192, dtype="bf16", streamk=True, bound="hbm"),
-    "bf16_skinny_m16": dict(M=16, N=28672, K=8192, dtype="bf16", streamk=True, bound="hbm"),
-    "bf16_skinny_m128": dict(M=128, N=28672, K=8192, dtype="bf16", streamk=True, bound="hbm"),
-    "fp8_m16": dict(M=16, N=28672, K=8192, dtype="fp8", streamk=True, bound="hbm"),
+    "bf16_skinny_m1": dict(M=1, N=28672, K=8192, dtype="bf16", streamk=True, bound="hbm", static_b=True),
+    "bf16_skinny_m16": dict(M=16, N=28672, K=8192, dtype="bf16", streamk=True, bound="hbm", static_b=True),
+    "bf16_skinny_m128": dict(M=128, N=28672, K=8192, dtype="bf16", streamk=True, bound="hbm", static_b=True),
+    "fp8_m16": dict(M=16, N=28672, K=8192, dtype="fp8", streamk=True, bound="hbm", static_b=True),
     "fp8_m256": dict(M=256, N=28672, K=8192, dtype="fp8", streamk=False, bound="hbm"),
     "fp8_m4096": dict(M=4096, N=28672, K=8192, dtype="fp8", streamk=False, bound="tensor"),
     "mxfp4_8192": dict(M=8192, N=8192, K=8192, dtype="mxfp4", streamk=False, bound="tensor"),
@@ -228,6 +229,7 @@ class DenseWorkload:
         self.out_dtype = torch.bfloat16 if self.fp8 else TORCH_DTYPES[wl["dtype"]]
         self.in_dtype = FP8 if self.fp8 else self.out_dtype
         self.streamk = wl["streamk"]
+        self.static_b = bool(wl.get("static_b", False))
         nsets = 2 if M * K + self.n_local * K < (1 << 29) else 1
         # small operands: rotate enough sets to exceed the 126 MB L2
         set_bytes = (M * K + self.n_local * K) * (1 if self.fp8 else 2) + M * self.n_local * 2
@@ -306,6 +308,8 @@ class DenseWorkload:
                    "+ barrier; the timed region ends after every transfer and barrier")
         self.extra = {"tile": f"{self.sel.block_m}x{self.sel.block_n}x{self.sel.block_k}", "cta_pair": self.sel.cta_pair,
                       "operand_sets": nsets, "parallelism": how}
+        if self.static_b:
+            self.extra["static_b"] = True
         # end-to-end leg: copies and compute on separate streams, double-buffered device operands
         self.s_in, self.s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         self.a_dev = [torch.empty_like(self.A[0]) for _ in range(2)]
@@ -320,10 +324,12 @@ class DenseWorkload:
         a = self.A[s] if a is None else a
         b_t = self.Bt[s] if b_t is None else b_t
         c = self.C[i % len(self.C)] if c is None else c
+        static = self.static_b and b_t is self.Bt[s]   # only the resident weights; the end-to-end leg's are copied in
         if self.fp8:
-            self.tb.matmul_a8w8_lt(a, b_t.T, self.a_s[s], self.b_s[s], c, self.sel, self.cfg, enable_streamk=self.streamk)
+            self.tb.matmul_a8w8_lt(a, b_t.T, self.a_s[s], self.b_s[s], c, self.sel, self.cfg, enable_streamk=self.streamk,
+                                   static_b=static)
         else:
-            self.tb.matmul_lt(a, b_t.T, c, self.sel, self.cfg, enable_streamk=self.streamk)
+            self.tb.matmul_lt(a, b_t.T, c, self.sel, self.cfg, enable_streamk=self.streamk, static_b=static)
         return c
 
     def step(self, i, dist):

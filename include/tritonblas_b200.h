@@ -148,6 +148,12 @@ typedef struct tb_gemm_args {
    * below this do (the kernel enumerates tiles in waves, so these are the launch's first waves); the caller sends the rest
    * with tb_push_c_tiles, typically on another stream beside the next launch, whose first tiles have nothing to send yet. */
   int32_t c_copies_tile_limit;
+  /* Operands that no work still in flight on the stream writes (weights): bit 0 = a, bit 1 = b. Launches are made with
+   * programmatic stream serialization, so a CTA can be scheduled while the previous kernel of the stream is still
+   * draining; it then starts filling its shared-memory ring with such an operand at once instead of waiting for that
+   * kernel first (single-CTA tiles, static schedules; ignored elsewhere). Everything else, the other operand, scales,
+   * bias and workspace included, is only touched after the wait. 0: no promise, nothing is read early. */
+  int32_t static_operands;
 } tb_gemm_args;
 
 /* Fill `cfg` for `p`. Stands in for origami.select_config + OrigamiMatmulSelector._compute_sk_grid

@@ -249,6 +249,36 @@ def test_streamk_matches_oracle_and_is_deterministic(m, n, k, sk_grid, pair):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])  # fix-up order is fixed
 
 
+@pytest.mark.parametrize("streamk", [False, True])
+@pytest.mark.parametrize("m", [8, 128, 300])
+def test_static_weights_are_read_before_the_previous_kernel_ends_and_nothing_else_is(m, streamk):
+    """static_b: the kernel may request b before the stream's previous kernel has finished. A chain of launches whose
+    activations are each written by the kernel just before (the previous product, rescaled in place) must give the same
+    values as the same chain without the promise; the weights alternate between two matrices."""
+    n = k = 2048
+    dt = torch.bfloat16
+    w = [make_operands(n, n, k, dt, "T", "T", seed=70 + i, scale=0.03)[1] for i in range(2)]
+    x0 = make_operands(m, n, k, dt, "T", "T", seed=3)[0]
+    sel = _selector(m, n, k, dt, streamk=streamk)
+    cfg = tb.matmul_preamble(sel)
+
+    def chain(static):
+        x = x0.clone()
+        outs = []
+        for step in range(6):
+            y = torch.empty(m, n, dtype=dt, device="cuda")
+            tb.matmul_lt(x, w[step & 1], y, sel, cfg, enable_streamk=streamk, static_b=static)
+            outs.append(y)
+            x = y          # the next launch's activations are what this one is still writing
+        return outs
+
+    plain = chain(False)
+    early = chain(True)
+    assert_close_to_oracle(plain[0], x0, w[0], what="first link")
+    for p_, e_ in zip(plain, early):
+        assert torch.equal(p_, e_)
+
+
 @pytest.mark.parametrize("m", [1, 16, 128])
 def test_streamk_skinny_decode_shapes(m):
     """BASELINE config 2b: M in {1,16,128}, N=28672, K=8192, stream-K enabled; sampled columns checked."""

@@ -55,7 +55,7 @@ class GemmArgs(ctypes.Structure):
         ("c_copies", ctypes.POINTER(ctypes.c_void_p)), ("num_c_copies", ctypes.c_int32),
         ("tile_counter", ctypes.c_void_p), ("epilogue_op", ctypes.c_int32),
         ("wait_timeout_ms", ctypes.c_int32), ("debug_flags", ctypes.c_int32),
-        ("a_gather_index", ctypes.c_void_p), ("a_rows", ctypes.c_int64), ("c_copies_tile_limit", ctypes.c_int32),
+        ("a_gather_index", ctypes.c_void_p), ("a_rows", ctypes.c_int64), ("c_copies_tile_limit", ctypes.c_int32), ("static_operands", ctypes.c_int32),
     ]
 
 

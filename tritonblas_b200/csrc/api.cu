@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstring>
@@ -306,6 +307,7 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
     t.b = a.a; t.b_stride_k = a.a_stride_k; t.b_stride_n = a.a_stride_m;
     t.c_stride_m = a.c_stride_n; t.c_stride_n = a.c_stride_m;
     t.a_scale = a.b_scale; t.b_scale = a.a_scale;
+    t.static_operands = ((a.static_operands & 1) << 1) | ((a.static_operands >> 1) & 1);
     tb_config c2 = cfg;
     c2.swap_ab = 0;
     rc = gemm_impl(t, &c2, stream, false, true, builtin);
@@ -398,6 +400,13 @@ static int gemm_impl(const tb_gemm_args& a_in, const tb_config* user_cfg, cudaSt
   if (a.tile_counter != nullptr && !a.streamk) {
     if (reinterpret_cast<uintptr_t>(a.tile_counter) & 3) return TB_ERR_ALIGNMENT;
     p.tile_counter = static_cast<unsigned*>(a.tile_counter);
+  }
+  // An operand nothing in flight writes is requested before the wait for the previous kernel (single CTAs, static
+  // schedules): the larger one per stage if both are.
+  if (pair == 1 && !grouped && !gather && p.tile_counter == nullptr && pdl_enabled()) {
+    if ((a.static_operands & 3) == 3) p.early_operand = bn * halves > 128 ? 2 : 1;
+    else if (a.static_operands & 1) p.early_operand = 1;
+    else if (a.static_operands & 2) p.early_operand = 2;
   }
   {
     p.debug_flags = a.debug_flags;

@@ -96,6 +96,11 @@ struct GemmParams {
   // matrix the A tensor map describes (box = one row of a stage's K extent); negative entries and rows past a group's end
   // read as zero. Every lane of the producer warp fetches four rows per stage with one gather-mode TMA copy.
   const int* a_gather;
+  // Operand that no earlier work of the stream still writes (weights): 1 = the operand of tensor map A, 2 = of B, 0 =
+  // none. With programmatic dependent launch a CTA can start while the previous kernel of the stream drains; it then
+  // fills its shared-memory ring with that operand before it waits for the previous kernel (single CTAs, static
+  // schedules, plain 2-D / 3-D operand copies).
+  int early_operand;
   // failure reporting
   int* status;
   unsigned long long timeout_ns;
@@ -111,7 +116,7 @@ struct WorkItem {
   bool valid;
 };
 
-// Enumerates the work of one program: first its data-parallel tiles, then its slice of the stream-K iteration space.
+// Enumerates the work of one program: first its slice of the stream-K iteration space, then its data-parallel tiles.
 struct WorkIter {
   int pid, nprog, nkb, dp_tiles, sk_tiles;
   int dp_next;
@@ -128,16 +133,11 @@ struct WorkIter {
     b = q * base + (q < rem ? q : rem);
     e = b + base + (q < rem ? 1 : 0);
   }
+  // The split tiles come first: a program's partial tile is then published early in the launch, and the owners' fix-ups
+  // (flag, partial tiles from L2, store: several round trips to a memory system that every SM is loading) happen while
+  // the whole tiles still stream, instead of standing at the end of the launch where nothing hides them.
   __device__ WorkItem next() {
     WorkItem w;
-    if (dp_next < dp_tiles) {
-      w.tile = dp_next;
-      w.kb0 = 0;
-      w.kb1 = nkb;
-      w.valid = true;
-      dp_next += nprog;
-      return w;
-    }
     if (it < it_end) {
       const int t = static_cast<int>(it / nkb);
       const long long tile_end = static_cast<long long>(t + 1) * nkb;
@@ -147,6 +147,14 @@ struct WorkIter {
       w.kb1 = static_cast<int>(e - static_cast<long long>(t) * nkb);
       w.valid = true;
       it = e;
+      return w;
+    }
+    if (dp_next < dp_tiles) {
+      w.tile = dp_next;
+      w.kb0 = 0;
+      w.kb1 = nkb;
+      w.valid = true;
+      dp_next += nprog;
       return w;
     }
     w.valid = false;
@@ -501,6 +509,56 @@ __device__ __forceinline__ void glu_drain(const GemmParams& p, uint8_t* stg, uin
   }
 }
 
+// Stream-K owner of a split tile: finds the programs after `pid` whose slice starts inside the tile and waits (bounded)
+// until each has published its partial tile. Returns one past the last such program, or -1 if a wait gave up.
+// One lane per warp polls (128 polling threads per CTA would load L2 for nothing while the peers still compute); once it
+// has seen a flag, every lane reads it once itself, which is its own acquire. Out of line for the same reason as below.
+template <int CTAS>
+__device__ __noinline__ int wait_for_peers(const unsigned* flags, unsigned epoch, int sk_tiles, int nkb, int dp_tiles, int tile,
+                                           int pid, int nprog, int cta_rank, int lane, volatile int* abort_flag, int* status,
+                                           unsigned long long timeout_ns) {
+  const WaitCtx wctx{abort_flag, status, timeout_ns};
+  int peer_end = pid + 1;
+  const long long tile_end = static_cast<long long>(tile - dp_tiles + 1) * nkb;
+  const long long total = static_cast<long long>(sk_tiles) * nkb;
+  const long long base = total / nprog, rem = total % nprog;
+  while (peer_end < nprog) {  // same split as WorkIter::range
+    const long long b = peer_end * base + (peer_end < rem ? peer_end : rem);
+    const long long e = b + base + (peer_end < rem ? 1 : 0);
+    if (b >= tile_end || b >= e) break;
+    ++peer_end;
+  }
+  bool ok = true;
+  for (int pp = pid + 1; pp < peer_end && ok; ++pp) {
+    const unsigned* flag = &flags[pp * CTAS + cta_rank];
+    bool seen = true;
+    if (lane == 0) seen = flag_wait(flag, epoch, wctx, TB_DEV_TIMEOUT_PEER_FLAG);
+    ok = __shfl_sync(0xffffffffu, seen ? 1 : 0, 0) != 0;
+    __syncwarp();
+    if (ok) ok = flag_wait(flag, epoch, wctx, TB_DEV_TIMEOUT_PEER_FLAG);
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  return ok ? peer_end : -1;
+}
+
+// Stream-K owner with 32-column accumulators: the partial tiles of `count` peers (`stride` floats apart, `src` already
+// offset to this thread's row) are added up in program order and the 32 sums parked in this lane's 128-byte staging row
+// (16-byte pieces XOR-swizzled with the lane, like every use of that buffer). Out of line: its registers would
+// otherwise weigh on the drains of every launch.
+static __device__ __noinline__ void park_peer_partials(const float* src, int count, size_t stride, uint8_t* mine, int lane) {
+  float pre[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) pre[j] = 0.0f;
+  for (int pp = 0; pp < count; ++pp, src += stride) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) pre[j] += __ldcg(src + j * kTileM);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<float4*>(mine + ((j ^ (lane & 7)) << 4)) =
+        make_float4(pre[4 * j], pre[4 * j + 1], pre[4 * j + 2], pre[4 * j + 3]);
+}
+
 template <int KIND, int CTAS, bool PROF = false, bool GATHER = false>
 __global__ void __launch_bounds__(gemm_threads<KIND>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -543,9 +601,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   WaitCtx wctx{abort_flag, p.status, p.timeout_ns};
   constexpr bool prof = PROF;  // measurement instantiation: per-role cycle counters written to debug_out
 
+  // One stage's copies of one operand for a single CTA (called by one thread; the barrier already expects the bytes).
+  const int a_atom = kStageRowBytes / p.esize;  // elements per 128-byte row
+  const int mn_box_bytes = p.k_per_stage * kStageRowBytes;
+  auto load_a_single = [&](uint8_t* sa, uint64_t* bar, int k0, int m0) {
+    if (!p.a_mn) {
+      tma_load_2d(sa, &tmap_a, bar, k0, m0);
+    } else if (p.a_mn3d) {
+      tma_load_3d(sa, &tmap_a, bar, 0, k0, m0 / a_atom);
+    } else {
+      for (int j = 0; j < kTileM / a_atom; ++j) tma_load_2d(sa + j * mn_box_bytes, &tmap_a, bar, m0 + j * a_atom, k0);
+    }
+  };
+  auto load_b_single = [&](uint8_t* sb, uint64_t* bar, int k0, int n0) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (h >= nh) break;
+      uint8_t* sbh = sb + h * b_tile_bytes;
+      const int nh0 = n0 + h * p.block_n;
+      if (!p.b_mn) {
+        tma_load_2d(sbh, &tmap_b, bar, k0, nh0);
+      } else if (p.b_mn3d) {
+        tma_load_3d(sbh, &tmap_b, bar, 0, k0, nh0 / a_atom);
+      } else {
+        for (int j = 0; j < bn_local / a_atom; ++j) tma_load_2d(sbh + j * mn_box_bytes, &tmap_b, bar, nh0 + j * a_atom, k0);
+      }
+    }
+  };
+  // Stages of this program's first work item whose early operand was requested before the dependency wait (thread 0
+  // counts them; the producer warp picks the number up from its lane 0).
+  int early_stages = 0;
+
   if (threadIdx.x == 0) {
     // measurement instantiation: wall-clock stamps (ns) of this CTA's phases in words 9..15 of its counter block
-    if (prof && p.debug_out != nullptr) p.debug_out[blockIdx.x * 16 + 9] = static_cast<long long>(global_timer_ns());
+    if (prof && p.debug_out != nullptr) {
+      p.debug_out[blockIdx.x * 16 + 9] = static_cast<long long>(global_timer_ns());
+      p.debug_out[blockIdx.x * 16 + 11] = static_cast<long long>(sm_id());  // which SM the CTA ran on
+    }
     *abort_flag = 0;
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -563,8 +655,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     mbar_fence_init();
     // Everything above touched only shared memory. From here on global memory is read, which has to wait for the
-    // previous kernel of the stream when this launch was allowed to start before that one finished.
+    // previous kernel of the stream when this launch was allowed to start before that one finished; only an operand the
+    // caller declared untouched by earlier work may be requested before that.
     griddep_launch_dependents();
+    if constexpr (CTAS == 1 && !GATHER && KIND != 3) {
+      if (p.early_operand != 0 && p.group_offsets == nullptr && p.tile_counter == nullptr) {
+        prefetch_tmap(p.early_operand == 1 ? &tmap_a : &tmap_b);
+        WorkIter wi0(p, blockIdx.x, gridDim.x, -1);
+        const WorkItem w0 = wi0.next();
+        if (w0.valid) {
+          const TileGeom tg = tile_geometry(p, w0.tile, kTileM, tile_prefix);
+          early_stages = min(stages, w0.kb1 - w0.kb0);
+          for (int st = 0; st < early_stages; ++st) {
+            uint8_t* sa = ring + static_cast<size_t>(st) * stage_bytes;
+            const int k0 = (w0.kb0 + st) * p.k_per_stage;  // a program's first item walks K forwards
+            mbar_arrive_expect_tx(&full_bar[st], static_cast<uint32_t>(kATileBytes + nh * b_tile_bytes));
+            if (p.early_operand == 1) load_a_single(sa, &full_bar[st], k0, tg.m0);
+            else load_b_single(sa + kATileBytes, &full_bar[st], k0, tg.b_row0);
+          }
+        }
+      }
+    }
     griddep_wait();
     if (prof && p.debug_out != nullptr) p.debug_out[blockIdx.x * 16 + 10] = static_cast<long long>(global_timer_ns());
     if (p.group_offsets != nullptr) {
@@ -669,10 +780,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       WorkIter wi(p, pid, nprog, grouped_tiles);
       int s = 0, item = 0;
       uint32_t ph = 0;
-      const int a_atom = kStageRowBytes / p.esize;  // elements per 128-byte row
       // In a pair, transaction bytes of both CTAs land on the even CTA's barrier, which expects the sum.
       const uint32_t expect = static_cast<uint32_t>(kATileBytes + nh * b_tile_bytes + sf_bytes) * CTAS;
-      const int mn_box_bytes = p.k_per_stage * kStageRowBytes;
+      // first stages of the first item: barrier armed and one operand already on its way (see the prologue)
+      int early_left = __shfl_sync(0xffffffffu, early_stages, 0);
       bool ok = true;
       long long prof_wait = 0, prof_t0 = clock64();
       int seq = 0;
@@ -713,31 +824,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const int k0 = kb * p.k_per_stage;
           if (elect_one()) {
             if constexpr (CTAS == 1) {
-              mbar_arrive_expect_tx(&full_bar[s], expect);
+              if (early_left == 0) mbar_arrive_expect_tx(&full_bar[s], expect);
               if constexpr (GATHER) {
                 // A: every lane fetches its four rows below
-              } else if (!p.a_mn) {
-                tma_load_2d(sa, &tmap_a, &full_bar[s], k0, m0);
-              } else if (p.a_mn3d) {
-                tma_load_3d(sa, &tmap_a, &full_bar[s], 0, k0, m0 / a_atom);
-              } else {
-                for (int j = 0; j < kTileM / a_atom; ++j)
-                  tma_load_2d(sa + j * mn_box_bytes, &tmap_a, &full_bar[s], m0 + j * a_atom, k0);
+              } else if (early_left == 0 || p.early_operand != 1) {
+                load_a_single(sa, &full_bar[s], k0, m0);
               }
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                if (h >= nh) break;
-                uint8_t* sbh = sb + h * b_tile_bytes;
-                const int nh0 = n0 + h * p.block_n;
-                if (!p.b_mn) {
-                  tma_load_2d(sbh, &tmap_b, &full_bar[s], k0, nh0);
-                } else if (p.b_mn3d) {
-                  tma_load_3d(sbh, &tmap_b, &full_bar[s], 0, k0, nh0 / a_atom);
-                } else {
-                  for (int j = 0; j < bn_local / a_atom; ++j)
-                    tma_load_2d(sbh + j * mn_box_bytes, &tmap_b, &full_bar[s], nh0 + j * a_atom, k0);
-                }
-              }
+              if (early_left == 0 || p.early_operand != 2) load_b_single(sb, &full_bar[s], k0, n0);
               if constexpr (KIND == 3) {
                 uint8_t* sf = sb + b_tile_bytes;
                 // scale tensor maps are [row group][K atom][128 words]; a box holds the stage's two K atoms
@@ -794,6 +887,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               tma_gather4_2d_pair(sa + lane * 4 * kStageRowBytes, &tmap_a, mapa_cluster(smem_u32(&full_bar[s]), 0), k0,
                                   grow[0], grow[1], grow[2], grow[3]);
           }
+          if (early_left > 0) --early_left;
           if (++s == stages) {
             s = 0;
             ph ^= 1;
@@ -1010,25 +1104,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int row = m0 + row_in_tile;
       const bool owner = (w.kb0 == 0);
       const bool complete = owner && (w.kb1 == p.num_k_blocks);
+      // Peers that hold the rest of this tile's K range: programs after this one whose slice starts inside the tile.
+      // Single CTAs wait for their partial tiles while this program's own share of the tile is still being accumulated:
+      // a peer's share of the tile is the first thing it does after its whole tiles, so the flags are normally set long
+      // before, and the round trips to L2 (a microsecond each while every SM streams) stay off the end of the launch.
+      int peer_end = pid + 1;
+      // 32-column accumulators (the decode orientation): the peers' partial tiles, summed in program order, are fetched
+      // early as well and parked in this lane's 128-byte row of the staging buffer, which is idle until the drain
+      const bool prefetch_fix = CTAS == 1 && owner && !complete && p.block_n == 32;
+      // Only where the early fetch applies is the wait moved ahead of the accumulator's: elsewhere it measured 2 % slower
+      // (M = 128, 256-column tiles), and in the pair instantiation the order cost the main drain registers.
+      if constexpr (CTAS == 1) {
+        if (prefetch_fix) {
+          peer_end = wait_for_peers<CTAS>(p.flags, p.epoch, p.sk_tiles, p.num_k_blocks, p.dp_tiles, w.tile, pid, nprog,
+                                          static_cast<int>(cta_rank), lane, abort_flag, p.status, p.timeout_ns);
+          ok = peer_end >= 0;
+          if (!ok) break;
+          park_peer_partials(p.partials + static_cast<size_t>(pid + 1) * slot_elems + row_in_tile, peer_end - pid - 1,
+                             slot_elems, stg + lane * kEpiRowPitch, lane);
+        }
+      }
       // Every decision to unwind is made warp-uniform: the TMEM loads below need the whole warp.
       ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[acc_i], (epi_parity >> acc_i) & 1u, wctx, TB_DEV_TIMEOUT_TMEM_FULL));
       if (!ok) break;
       if (prof) prof_wait += clock64() - pe0;
       tc_fence_after();
-
-      // Peers that hold the rest of this tile's K range: programs after this one whose slice starts inside the tile.
-      int peer_end = pid + 1;
-      if (owner && !complete) {
-        const long long tile_end = static_cast<long long>(w.tile - p.dp_tiles + 1) * p.num_k_blocks;
-        long long b, e;
-        while (peer_end < nprog) {
-          wi.range(peer_end, b, e);
-          if (b >= tile_end || b >= e) break;
-          ++peer_end;
-        }
-        for (int pp = pid + 1; pp < peer_end && ok; ++pp)
-          ok = flag_wait(&p.flags[pp * CTAS + static_cast<int>(cta_rank)], p.epoch, wctx, TB_DEV_TIMEOUT_PEER_FLAG);
-        ok = __all_sync(0xffffffffu, ok);
+      if (owner && !complete && !prefetch_fix) {
+        peer_end = wait_for_peers<CTAS>(p.flags, p.epoch, p.sk_tiles, p.num_k_blocks, p.dp_tiles, w.tile, pid, nprog,
+                                        static_cast<int>(cta_rank), lane, abort_flag, p.status, p.timeout_ns);
+        ok = peer_end >= 0;
         if (!ok) break;
       }
 
@@ -1119,11 +1223,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             for (int j = 0; j < 32; ++j) dst[j * kTileM] = v[j];
             continue;
           }
-          for (int pp = pid + 1; pp < peer_end; ++pp) {
-            const float* src =
-                p.partials + (pp * CTAS + static_cast<int>(cta_rank)) * slot_elems + static_cast<size_t>(c * 32) * kTileM + row_in_tile;
+          if (prefetch_fix) {
+            const uint8_t* mine = stg + lane * kEpiRowPitch;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * kTileM);
+            for (int j = 0; j < 8; ++j) {
+              const float4 t = *reinterpret_cast<const float4*>(mine + ((j ^ (lane & 7)) << 4));
+              v[4 * j] += t.x;
+              v[4 * j + 1] += t.y;
+              v[4 * j + 2] += t.z;
+              v[4 * j + 3] += t.w;
+            }
+          } else {
+            for (int pp = pid + 1; pp < peer_end; ++pp) {
+              const float* src = p.partials + (pp * CTAS + static_cast<int>(cta_rank)) * slot_elems +
+                                 static_cast<size_t>(c * 32) * kTileM + row_in_tile;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * kTileM);
+            }
           }
           const int col0 = n0 + c * 32;
           if (col0 < p.N && (staged || row < row_end)) {

@@ -144,6 +144,12 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   }
 }
 
+__device__ __forceinline__ uint32_t sm_id() {
+  uint32_t v;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(v));
+  return v;
+}
+
 // One lane of a converged warp (all 32 lanes must call this together).
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
@@ -188,7 +194,7 @@ __device__ __forceinline__ bool flag_wait(const unsigned* flag, unsigned want, c
         return false;
       }
     }
-    __nanosleep(64);
+    __nanosleep(spins < 8 ? 64 : 256);  // short waits stay short, long ones poll L2 four times less often
   }
 }
 __device__ __forceinline__ void flag_release(unsigned* flag, unsigned v) {

@@ -106,6 +106,10 @@ int select_config(const tb_problem& p_in, const MachineModel& hw, tb_config* out
       const int stage_bytes = (128 * 128 + halves * bn_local * 128 + sf_bytes + 1023) & ~1023;
       int stages = (hw.smem_optin - 2048 - 16384) / stage_bytes;
       stages = std::min(stages, 12);
+      // Transposed (decode) orientation: the launch is bound by the rate at which one SM pulls its rows out of HBM, and
+      // that rate peaks with about 160 KB requested ahead (measured on 16 x 28672 x 8192 bf16: 3 / 4 / 6 / 8 / 10 stages
+      // of 20 KB: 98.9 / 91.6 / 87.8 / 86.8 / 89.3 us; 64-column tiles: best at 6-7 stages of 24 KB).
+      if (swap) stages = std::min(stages, std::max(4, 168 * 1024 / stage_bytes));
       if (stages < 2) continue;
       const long long active_ctas = std::min<long long>(tiles, programs) * pair;
       // L2 -> shared memory: one SM alone pulls fabric_bytes_per_clk, all of them together share the L2's total

@@ -127,7 +127,7 @@ def _ptr(t):
 
 
 def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, streamk=False, sk_grid=None,
-          c_copies=None, work_stealing=False, c_copies_tail_stream=None, c_copies_tail_fraction=0.0):
+          c_copies=None, work_stealing=False, c_copies_tail_stream=None, c_copies_tail_fraction=0.0, static_b=False):
     assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
     if not (a.is_cuda and b.is_cuda and c.is_cuda):
         raise RuntimeError("tritonblas_b200 runs on CUDA tensors only (no CPU path)")
@@ -137,6 +137,7 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
         raise RuntimeError(f"output has shape {tuple(c.shape)}, expected {(M, N)}")
     if M == 0 or N == 0:
         return c
+    b_in_ptr = b.data_ptr()
     a = _unit_stride_2d(a)
     b = _unit_stride_2d(b)
     if M * N * K >= _REPITCH_MIN_MACS and a.dtype != torch.float32:
@@ -179,6 +180,8 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
             else:
                 args.num_c_copies = 0       # nothing leaves from the epilogue; the copy kernel sends every tile
     args.allow_tf32 = int(torch.backends.cuda.matmul.allow_tf32)
+    if static_b and b.data_ptr() == b_in_ptr:
+        args.static_operands = 2    # the caller's own b (not a re-pitched copy made above, which this stream just wrote)
     if config is not None:
         args.wait_timeout_ms, args.debug_flags = int(config.wait_timeout_ms), int(config.debug_flags)
     args.streamk = int(bool(streamk))
@@ -212,38 +215,42 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
 
 
 def persistent_matmul_lt(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, quantized=False,
-                         work_stealing=False, c_copies=None, c_copies_tail_stream=None, c_copies_tail_fraction=0.0):
+                         work_stealing=False, c_copies=None, c_copies_tail_stream=None, c_copies_tail_fraction=0.0,
+                         static_b=False):
     """Data-parallel persistent GEMM (reference: matmul.py:69-200). ``work_stealing`` selects the dynamic tile schedule
     (tiles taken from a device counter, matmul.py:112-159) instead of the static round-robin. ``c_copies``: device addresses of further buffers laid out like ``c`` (peer GPUs) that the
     epilogue also writes. With ``c_copies_tail_stream`` (a torch.cuda.Stream) and ``c_copies_tail_fraction`` in (0, 1] the
     epilogue sends only the first tiles and the last ``fraction`` of the tiles are copied to the peers by a kernel on that
     stream after the launch, where they overlap whatever is enqueued next on the current stream; the caller waits for that
-    stream before the copies are read."""
+    stream before the copies are read. ``static_b``: a promise that nothing still in flight on the stream writes ``b``
+    (weights); the kernel may then start reading it while the previous kernel of the stream is still draining."""
     return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=False, c_copies=c_copies,
                  work_stealing=work_stealing, c_copies_tail_stream=c_copies_tail_stream,
-                 c_copies_tail_fraction=c_copies_tail_fraction)
+                 c_copies_tail_fraction=c_copies_tail_fraction, static_b=static_b)
 
 
 def streamk_matmul_lt(a, b, c, selector, config=None, bias=None, sk_grid=None, a_scale=None, b_scale=None,
-                      quantized=False, work_stealing=False):
-    """Hybrid stream-K GEMM (reference: matmul.py:202-366)."""
-    return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=True, sk_grid=sk_grid)
+                      quantized=False, work_stealing=False, static_b=False):
+    """Hybrid stream-K GEMM (reference: matmul.py:202-366). ``static_b``: see persistent_matmul_lt."""
+    return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=True, sk_grid=sk_grid, static_b=static_b)
 
 
-def matmul_lt(a, b, c, selector, config: Optional[MatmulConfig] = None, enable_streamk=False, work_stealing=False):
+def matmul_lt(a, b, c, selector, config: Optional[MatmulConfig] = None, enable_streamk=False, work_stealing=False,
+              static_b=False):
     assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
     if enable_streamk:
-        return streamk_matmul_lt(a, b, c, selector, config, work_stealing=work_stealing)
-    return persistent_matmul_lt(a, b, c, selector, config, work_stealing=work_stealing)
+        return streamk_matmul_lt(a, b, c, selector, config, work_stealing=work_stealing, static_b=static_b)
+    return persistent_matmul_lt(a, b, c, selector, config, work_stealing=work_stealing, static_b=static_b)
 
 
 def matmul_a8w8_lt(a, b, a_scale, b_scale, c, selector, config: Optional[MatmulConfig] = None, enable_streamk=False,
-                   work_stealing=False):
+                   work_stealing=False, static_b=False):
     assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
     if enable_streamk:
-        return streamk_matmul_lt(a, b, c, selector, config, a_scale=a_scale, b_scale=b_scale, quantized=True)
+        return streamk_matmul_lt(a, b, c, selector, config, a_scale=a_scale, b_scale=b_scale, quantized=True,
+                                 static_b=static_b)
     return persistent_matmul_lt(a, b, c, selector, config, a_scale=a_scale, b_scale=b_scale, quantized=True,
-                                work_stealing=work_stealing)
+                                work_stealing=work_stealing, static_b=static_b)
 
 
 _selector_cache = {}

@@ -135,6 +135,8 @@ class OrigamiMatmulSelector:
                 if "stages" not in fields and not self._mx_block_size:
                     stage = (128 * 128 + halves * (cfg.block_n // pair) * 128 + 1023) & ~1023
                     cfg.stages = max(2, min(12, (self._hardware.lds_capacity - 2048 - 16384) // stage))
+                    if cfg.swap_ab:     # same cap as the selector's: about 160 KB requested ahead per SM
+                        cfg.stages = min(cfg.stages, max(4, 168 * 1024 // stage))
                 if "group_m" not in fields:
                     g = round((programs * cfg.block_n * halves / cfg.block_m) ** 0.5)
                     cfg.group_m = max(1, min(tiles_m, g))
