@@ -252,6 +252,15 @@ int tb_moe_plan(const void* topk_ids, int32_t ids_are_int64, int64_t n_pairs, in
                 int32_t world, int32_t rank, const int32_t* counts_all, int32_t* cursor, int64_t capacity_rows,
                 int32_t* pair_rank, int64_t* pair_row, int32_t* group_offsets, int32_t* row_token, int32_t topk, void* stream);
 
+/* Diagnostic: streams rows x row_bytes of a row-major matrix (pitch_bytes between rows) out of HBM with the access pattern
+ * of the GEMM's K-major operand loader and drops the data: `programs` CTAs (one per SM), each keeping `stages` TMA boxes of
+ * box_rows rows x 128 bytes in flight, row blocks dealt round-robin, K walked in 128-byte steps. Time it with events:
+ * rows / box_rows * box_rows * row_bytes bytes per launch. row_bytes a multiple of 128, box_rows a multiple of 8 up to 256,
+ * stages * box_rows * 128 bytes within 196 KB. Waits are bounded and report through tb_device_status. No reference
+ * counterpart. */
+int tb_tma_stream_probe(const void* base, int64_t rows, int64_t row_bytes, int64_t pitch_bytes, int32_t stages,
+                        int32_t box_rows, int32_t programs, void* stream);
+
 /* Diagnostic (no reference counterpart): stores `passes` times `rows` rows of `run_bytes` contiguous bytes each, `pitch_bytes`
  * apart, into dst (a local buffer, or a peer GPU's buffer mapped into this process) from `blocks` x `threads` threads with
  * 16-byte stores: the store pattern of an epilogue that pushes output tiles to other GPUs. Timing it gives the egress rate

@@ -42,3 +42,13 @@ def test_selector_pick_is_close_to_the_best_configuration():
             assert eff >= 0.90, (m, n, k, dt, sk, eff, [(r["cta_pair"], r["block_n"], r["n_halves"], r["us"]) for r in rows])
     finally:
         sweep._MODE["steady"] = False
+
+
+@pytest.mark.gpu
+def test_hbm_stream_probe_runs_and_reports():
+    """The streaming probe (TMA boxes, data dropped) completes with a clean status and a plausible rate."""
+    from tritonblas_b200 import hbm_stream
+    res = hbm_stream.measure(rows=16384, k=4096, configs=((4, 128), (2, 256), (8, 64)))
+    assert len(res) == 3
+    for r in res:
+        assert r["status"] == 0 and 100.0 < r["gb_s"] < 20000.0, r

@@ -117,6 +117,9 @@ def _load():
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
                                          ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p]
     lib.tb_moe_combine_peers.restype = ctypes.c_int
+    lib.tb_tma_stream_probe.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
+                                        ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+    lib.tb_tma_stream_probe.restype = ctypes.c_int32
     lib.tb_peer_store_probe.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32,
                                         ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
     lib.tb_peer_store_probe.restype = ctypes.c_int

@@ -13,7 +13,7 @@ LIB = os.path.join(PKG, "libtritonblas_b200.so")
 # the gemm_inst_* files hold the kernel instantiations (one MMA kind each) and dominate the build: they go first so that
 # the parallel compile below starts them before the small files
 SOURCES = ["gemm_inst_f16.cu", "gemm_inst_f8.cu", "gemm_inst_mxf4.cu", "gemm_inst_tf32.cu", "gemm_inst_i8.cu", "api.cu",
-           "simt_gemm.cu", "quant_mxfp4.cu", "quant_fp8.cu", "moe_ops.cu", "push_tiles.cu", "selector.cpp"]
+           "simt_gemm.cu", "quant_mxfp4.cu", "quant_fp8.cu", "moe_ops.cu", "push_tiles.cu", "stream_probe.cu", "selector.cpp"]
 HEADERS_DIRS = [HERE, os.path.join(os.path.dirname(PKG), "include")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
