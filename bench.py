@@ -638,9 +638,11 @@ class Runner:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return t[0].item() == 0.0, t[1].item()
 
-    def timed(self, step, n_warm, n_timed, clocks=True, first=0, finish=None):
+    def timed(self, step, n_warm, n_timed, clocks=True, first=0, finish=None, per_call_events=True):
         """(total ms, mean ms of one call, clocks, launches of this library) of n_timed calls of step(i). ``finish`` runs
-        after the last call and before the closing event (joins side streams: their work is inside the timed region)."""
+        after the last call and before the closing event (joins side streams: their work is inside the timed region).
+        ``per_call_events=False`` records nothing between the calls (an event between two kernels keeps the second from
+        being scheduled while the first drains); the mean is then the whole region's time over the number of calls."""
         from tritonblas_b200 import _lib
         it = first
         for _ in range(n_warm):
@@ -659,11 +661,14 @@ class Runner:
         wall0 = time.time()
         t0.record(self.stream)
         for _ in range(n_timed):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(self.stream)
-            step(it)
-            e1.record(self.stream)
-            events.append((e0, e1))
+            if per_call_events:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(self.stream)
+                step(it)
+                e1.record(self.stream)
+                events.append((e0, e1))
+            else:
+                step(it)
             it += 1
         if finish is not None:
             finish()
@@ -673,7 +678,7 @@ class Runner:
         ck = sampler.stop(wall0, wall1) if sampler else None
         launches = _lib.lib.tb_launch_count() - launches0
         total = t0.elapsed_time(t1)
-        unit = sum(a.elapsed_time(b) for a, b in events) / len(events)
+        unit = sum(a.elapsed_time(b) for a, b in events) / len(events) if events else total / n_timed
         if finish is not None:
             unit = total / n_timed      # calls overlap one another across streams: only the whole region's time counts
         total, unit = self.max_over_ranks(total, unit)
@@ -884,11 +889,19 @@ def main():
                                "how": "torch._scaled_mm (cuBLASLt, row-wise scales)" if xw.fp8 else "torch.matmul (cuBLAS)"}
                 except Exception as exc:      # a torch build without this cuBLASLt path
                     lib_run = {"unavailable": str(exc).splitlines()[0][:200]}
+            # the same launches with nothing recorded between them: what a chain of such kernels costs per link (launch
+            # gaps included; kernels that start while their predecessor drains get to show it)
+            _, b2b, _, _ = run.timed(lambda i: xw.step(i, dist), 3, n, clocks=False, per_call_events=False)
+            back_to_back = {"ms": b2b}
+            if lib_run is not None and "ms" in lib_run:
+                _, lib_b2b, _, _ = run.timed(lambda i: xw.cublas_step(i), 3, n, clocks=False, per_call_events=False)
+                back_to_back.update({"library_ms": lib_b2b, "ours_over_library": lib_b2b / b2b})
             flops = xw.kernel_flops if name != "mxfp4_quant" else 0.0
             items.append({"workload": f"{name}: {xw.label}", "value": (flops / (unit * 1e-3) / 1e12) if flops else None,
                           "unit": "TFLOP/s", "kernel_ms": unit, "launches": n, "gpu_launches": nl,
                           "roofline": roofline_of(name, xw, unit, total * 1e-3, peaks, 1), "clocks": ck,
-                          "parity_check": {"ok": ok, "max_err": err}, "library_same_run": lib_run})
+                          "parity_check": {"ok": ok, "max_err": err}, "library_same_run": lib_run,
+                          "back_to_back": back_to_back})
             del xw
             release()
         line["workloads"] = items
