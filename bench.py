@@ -276,8 +276,11 @@ class DenseWorkload:
             #           with the GEMM: it runs at half its stand-alone rate and the GEMM a fifth slower; kept off the GEMM's
             #           SMs, with the GEMM on 8-16 fewer: 3191-3214); the whole block by asynchronous copies (copy
             #           engines) beside the next product: 4407-4441.
-            #   8 GPUs: epilogue pushes (0.26 ms per product, 450 GB/s out of every GPU); nothing else measured there.
-            auto = 1.0 if world == 4 else 0.0
+            #   8 GPUs: epilogue pushes 4147, with the closing barrier on a side stream 4300 (0.256 ms per product, 459 GB/s
+            #           out of every GPU); the last half of the tiles by the copy kernel on a side stream instead: 4782 (a
+            #           rank's shard is 128 tiles on 74 CTA pairs, which leaves the copy kernel room); the whole block by
+            #           copy engines: 3204 (seven copies out and seven in per GPU); NCCL all-gather after the GEMM: 3400.
+            auto = 1.0 if world == 4 else (0.5 if world >= 8 else 0.0)
             self.overlap_tail = auto if args.overlap_tail < 0 else float(args.overlap_tail)
         self.copy_engine = bool(args.copy_engine) and self.overlap_tail >= 1.0
         self.side_barrier = self.layers is not None and self.overlap_tail <= 0 and bool(args.side_barrier)
