@@ -51,3 +51,43 @@ def test_library_sources_name_no_device_allocator():
         if path.endswith((".cu", ".cuh", ".cpp", ".h")):
             with open(path) as f:
                 assert not pat.search(f.read()), path
+
+
+def test_ctypes_structures_mirror_the_header_field_for_field(tmp_path):
+    """Every structure of the C header, compiled by the host C compiler, has the size the ctypes mirror has, and every
+    field sits at the same offset: a field added on one side only cannot go unnoticed."""
+    import os
+    import re
+    import shutil
+    import subprocess
+    from tritonblas_b200 import _lib
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no host C compiler")
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = os.path.join(here, "include", "tritonblas_b200.h")
+    text = open(header).read()
+    pairs = {"tb_problem": _lib.Problem, "tb_config": _lib.Config, "tb_gemm_args": _lib.GemmArgs, "tb_mxfp4_args": _lib.Mxfp4Args}
+    lines = ["#include <stdio.h>", "#include <stddef.h>", f'#include "{header}"', "int main(void) {"]
+    for cname, mirror in pairs.items():
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        names = []
+        for stmt in body.split(";"):
+            for piece in stmt.split(","):       # "int32_t m, n, k" declares three fields
+                found = re.findall(r"(\w+)\s*(?:\[\d+\])?\s*$", piece.strip())
+                names += found
+        assert names == [f[0] for f in mirror._fields_], (cname, names, [f[0] for f in mirror._fields_])
+        lines.append(f'printf("{cname} %zu\\n", sizeof({cname}));')
+        for n in names:
+            lines.append(f'printf("{cname}.{n} %zu\\n", offsetof({cname}, {n}));')
+    lines += ["return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([cc, "-std=c11", "-o", str(exe), str(src)], check=True)
+    out = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for cname, mirror in pairs.items():
+        assert int(out[cname]) == ctypes.sizeof(mirror), cname
+        for fname, _ in mirror._fields_:
+            assert int(out[f"{cname}.{fname}"]) == getattr(mirror, fname).offset, (cname, fname)

@@ -41,6 +41,10 @@ def test_entry_point_signatures_keep_reference_argument_order():
     assert sig(tritonblas.matmul_fp4)[:5] == ["a", "b", "c", "a_scales", "b_scales"]
     assert sig(tritonblas.addmm)[:4] == ["bias", "a", "b", "out"]
     assert sig(tritonblas.OrigamiMatmulSelector.__init__)[1:8] == ["m", "n", "k", "a_dtype", "b_dtype", "out_dtype", "device"]
+    # extensions beyond the reference are keyword arguments behind the reference's own, off by default
+    for f in (tritonblas.matmul_lt, tritonblas.matmul_a8w8_lt):
+        p = inspect.signature(f).parameters["static_b"]
+        assert p.default is False and list(inspect.signature(f).parameters)[-1] == "static_b"
 
 
 class TestEstimateTritonLdsBytes:
