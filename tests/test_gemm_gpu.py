@@ -249,17 +249,20 @@ def test_streamk_matches_oracle_and_is_deterministic(m, n, k, sk_grid, pair):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])  # fix-up order is fixed
 
 
+@pytest.mark.parametrize("trans_b", ["T", "N"])
 @pytest.mark.parametrize("streamk", [False, True])
 @pytest.mark.parametrize("m", [8, 128, 300])
-def test_static_weights_are_read_before_the_previous_kernel_ends_and_nothing_else_is(m, streamk):
+def test_static_weights_are_read_before_the_previous_kernel_ends_and_nothing_else_is(m, streamk, trans_b):
     """static_b: the kernel may request b before the stream's previous kernel has finished. A chain of launches whose
     activations are each written by the kernel just before (the previous product, rescaled in place) must give the same
     values as the same chain without the promise; the weights alternate between two matrices."""
     n = k = 2048
     dt = torch.bfloat16
-    w = [make_operands(n, n, k, dt, "T", "T", seed=70 + i, scale=0.03)[1] for i in range(2)]
+    w = [make_operands(n, n, k, dt, "T", trans_b, seed=70 + i, scale=0.03)[1] for i in range(2)]
     x0 = make_operands(m, n, k, dt, "T", "T", seed=3)[0]
-    sel = _selector(m, n, k, dt, streamk=streamk)
+    # single CTAs: the early request exists for them only (few rows: the weights are the tile's 128-row operand; more
+    # rows: its column operand, K- or N-contiguous)
+    sel = _selector(m, n, k, dt, streamk=streamk, cta_pair=1, block_n=128) if m > 64 else _selector(m, n, k, dt, streamk=streamk)
     cfg = tb.matmul_preamble(sel)
 
     def chain(static):
