@@ -65,7 +65,8 @@ EXTRA_WORKLOADS = ["fp8_m4096", "mxfp4_8192", "mxfp4_quant", "bf16_skinny_m16", 
 TORCH_DTYPES = {"bf16": torch.bfloat16, "fp16": torch.float16}
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the workload's dominant kernel, from the ncu captures
 # summarised under profiles/ (same shapes; a capture is not repeated inside the bench)
-NCU_TRAFFIC_BYTES = {"bf16_8192": 0.794e9 + 0.124e9, "mxfp4_8192": 0.1565e9 + 0.1132e9, "mxfp4_quant": 0.1343e9 + 0.0078e9}
+NCU_TRAFFIC_BYTES = {"bf16_8192": 0.794e9 + 0.124e9, "mxfp4_8192": 0.1565e9 + 0.1132e9, "mxfp4_quant": 0.1343e9 + 0.0078e9,
+                     "bf16_skinny_m16": 0.4718e9 + 0.0075e9, "fp8_m4096": 0.5615e9 + 0.2225e9}
 MOE = dict(experts=64, topk=8, tokens=16384, hidden=4096, ffn=1536)
 
 
