@@ -277,13 +277,17 @@ class DenseWorkload:
             #           with the GEMM: it runs at half its stand-alone rate and the GEMM a fifth slower; kept off the GEMM's
             #           SMs, with the GEMM on 8-16 fewer: 3191-3214); the whole block by asynchronous copies (copy
             #           engines) beside the next product: 4407-4441.
+            #           The first tile groups from the epilogue and the rows of the last 25 / 50 / 75 % by copy engines:
+            #           4202 / 4094 / 3977 against 4273 for the whole block by copy engines in the same call.
             #   8 GPUs: epilogue pushes 4147, with the closing barrier on a side stream 4300 (0.256 ms per product, 459 GB/s
             #           out of every GPU); the last half of the tiles by the copy kernel on a side stream instead: 4782 (a
             #           rank's shard is 128 tiles on 74 CTA pairs, which leaves the copy kernel room); the whole block by
             #           copy engines: 3204 (seven copies out and seven in per GPU); NCCL all-gather after the GEMM: 3400.
             auto = 1.0 if world == 4 else (0.5 if world >= 8 else 0.0)
             self.overlap_tail = auto if args.overlap_tail < 0 else float(args.overlap_tail)
-        self.copy_engine = bool(args.copy_engine) and self.overlap_tail >= 1.0
+        # --copy-engine 1: the whole block by copy engines when overlap_tail is 1; 2: also a partial tail (the rows of the
+        # last tile groups by copy engines, the first groups from the epilogue) instead of the copy kernel
+        self.copy_engine = (int(args.copy_engine) == 1 and self.overlap_tail >= 1.0) or (int(args.copy_engine) == 2 and self.overlap_tail > 0)
         self.side_barrier = self.layers is not None and self.overlap_tail <= 0 and bool(args.side_barrier)
         self.sel = tb.OrigamiMatmulSelector(M, self.n_local, K, self.in_dtype, self.in_dtype, self.out_dtype, dev,
                                             streamk=self.streamk)
@@ -302,6 +306,11 @@ class DenseWorkload:
         elif self.overlap_tail <= 0:
             how = (f"N-sharded x{world}, epilogue pushes C tiles to all ranks over NVLink (symmetric memory) + barrier"
                    + (" on a side stream (the next product does not wait for it; the timed region does)" if self.side_barrier else ""))
+        elif self.copy_engine and self.overlap_tail < 1.0:
+            how = (f"N-sharded x{world}, the first tile groups of every product's C go to all ranks from the epilogue over NVLink, "
+                   f"the rows of the last groups (about {self.overlap_tail:.2f} of the tiles) by asynchronous peer copies on side "
+                   "streams beside the next product (symmetric memory) + barrier; the timed region ends after every transfer "
+                   "and barrier")
         elif self.copy_engine:
             how = (f"N-sharded x{world}, every product's block of C is copied into all ranks' gathered buffers (symmetric "
                    "memory) by asynchronous peer copies on side streams beside the next product + barrier; the timed "

@@ -44,6 +44,28 @@ for _ in range(2):             # the whole block by asynchronous peer copies on 
     layer.wait_gathered()
     c5 = tbd.ColumnShardedGemm.as_matrix(g4).float()
     assert torch.allclose(c5, ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item()), "gathered by peer copies"
+# first row groups of tiles from the epilogue, the rows of the last ones by peer copies; a taller product so that the tile
+# order has several groups, and the buffers poisoned before every call so that a row nobody sent cannot pass
+M2, K2 = 4096, 256
+a2 = (torch.randn(M2, K2, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+b2 = (torch.randn(N, K2, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+layer2 = tbd.ColumnShardedGemm(b2[lo:hi].contiguous())
+buf2 = layer2.enable_fused_gather(M2)
+layer2._fused_selector.override(group_m=4)
+ref2 = a2.float() @ b2.float().T
+for frac in (0.3, 0.5, 0.8):
+    first_tile, first_row = layer2._tail_split(a2, layer2.b_shard_t, frac)
+    assert 0 < first_row < M2 and first_tile > 0, (frac, first_tile, first_row)
+    for _ in range(2):
+        buf2.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        g5 = layer2.forward_fused(a2, overlap_tail=frac, tail_by_copy_engine=True)
+        layer2.wait_gathered()
+        c6 = tbd.ColumnShardedGemm.as_matrix(g5).float()
+        assert torch.allclose(c6, ref2, rtol=1e-2, atol=1e-2 * ref2.abs().max().item()), ("epilogue pushes + peer copies", frac)
+        torch.cuda.synchronize()
+        dist.barrier()
 # expert-parallel MoE against a single-device evaluation of the same experts
 E, H, F, T, topk = 8, 256, 128, 64, 2
 w1 = (torch.randn(E, 2 * F, H, generator=g) * 0.1).to(torch.bfloat16).to(dev)

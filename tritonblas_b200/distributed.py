@@ -112,24 +112,21 @@ class ColumnShardedGemm:
         main = torch.cuda.current_stream(a.device)
         if self._tail_done is not None:
             main.wait_event(self._tail_done)     # the previous tail copy has read its tiles
-        if tail_by_copy_engine:
+        if tail_by_copy_engine and 0.0 < overlap_tail < 1.0:
+            # The first row groups of tiles leave from the epilogue, while the product computes; the rows of the last ones
+            # (the kernel walks the tiles in groups of group_m tile rows, so a whole number of groups is a contiguous row
+            # range of C) by the copy engines, beside the next product.
+            first_tile, first_row = self._tail_split(a, b_t, overlap_tail)
+            persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None, c_copies=self._peer_slots,
+                                 c_copies_tile_limit=first_tile)
+            self._copy_rows_to_peers(a.device, main, first_row)
+        elif tail_by_copy_engine:
             # The whole block travels by the GPU's copy engines (one asynchronous copy per peer, each on its own stream):
             # no SM is shared with the products that follow on the launching stream. Measured on 4 GPUs: an SM copy
             # kernel beside a GEMM runs at half its stand-alone rate (0.31 against 0.17 ms per block) and slows the GEMM
             # by a fifth (0.235 against 0.19 ms).
             persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None)
-            if self._peer_views is None:
-                shape = tuple(self._gathered.shape)
-                self._peer_views = [self._handle.get_buffer(r, shape, self._gathered.dtype)[self.rank]
-                                    for r in range(self.world) if r != self.rank]
-                self._copy_streams = [torch.cuda.Stream(a.device) for _ in self._peer_views]
-            ready = main.record_event()
-            mine = self._gathered[self.rank]
-            for view, st in zip(self._peer_views, self._copy_streams):
-                st.wait_event(ready)
-                with torch.cuda.stream(st):
-                    view.copy_(mine, non_blocking=True)
-                self.tail_stream.wait_stream(st)
+            self._copy_rows_to_peers(a.device, main, 0)
         elif overlap_tail > 0.0:
             persistent_matmul_lt(a, b_t.T, self._gathered[self.rank], self._fused_selector, None, c_copies=self._peer_slots,
                                  c_copies_tail_stream=self.tail_stream, c_copies_tail_fraction=overlap_tail)
@@ -142,6 +139,39 @@ class ColumnShardedGemm:
             self._handle.barrier(channel=1)      # every rank's pushes, epilogue and tail copy, have landed
             self._tail_done = self.tail_stream.record_event()
         return self._gathered
+
+    def _copy_rows_to_peers(self, device, main, first_row: int):
+        """Rows [first_row, M) of this rank's block to every peer's gathered buffer: one asynchronous copy per peer, each
+        on a stream of its own, after everything enqueued on ``main`` so far; ``self.tail_stream`` waits for all of them."""
+        if self._peer_views is None:
+            shape = tuple(self._gathered.shape)
+            self._peer_views = [self._handle.get_buffer(r, shape, self._gathered.dtype)[self.rank]
+                                for r in range(self.world) if r != self.rank]
+            self._copy_streams = [torch.cuda.Stream(device) for _ in self._peer_views]
+        ready = main.record_event()
+        mine = self._gathered[self.rank]
+        for view, st in zip(self._peer_views, self._copy_streams):
+            st.wait_event(ready)
+            with torch.cuda.stream(st):
+                view[first_row:].copy_(mine[first_row:], non_blocking=True)
+            self.tail_stream.wait_stream(st)
+
+    def _tail_split(self, a, b_t, fraction: float):
+        """(first tile, first row) of the last row groups of tiles, about ``fraction`` of all of them: tiles below the
+        first go from the epilogue, rows from the second on by copies. Follows the kernel's tile order (tile index ->
+        group of group_m tile rows, swept column by column)."""
+        from .matmul import _is_mn_major, _unit_stride_2d
+        m, n = a.shape[0], b_t.shape[0]
+        cfg = self._fused_selector.config_for(_is_mn_major(_unit_stride_2d(a), 1), _is_mn_major(_unit_stride_2d(b_t.T), 0))
+        tile_n = cfg.block_n * max(cfg.n_halves, 1)
+        tiles_m, tiles_n = -(-m // cfg.block_m), -(-n // tile_n)
+        group_m = cfg.group_m if cfg.group_m > 0 else 8
+        groups = -(-tiles_m // group_m)
+        if cfg.swap_ab or groups < 2:
+            return tiles_m * tiles_n, m             # a single group (or a transposed launch): everything from the epilogue
+        tail_groups = min(groups - 1, max(1, round(fraction * groups)))
+        head = groups - tail_groups
+        return head * group_m * tiles_n, min(head * group_m * cfg.block_m, m)
 
     def wait_gathered(self):
         """Make the current stream wait for the side stream's tail copy and closing barrier of the last

@@ -127,7 +127,8 @@ def _ptr(t):
 
 
 def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, streamk=False, sk_grid=None,
-          c_copies=None, work_stealing=False, c_copies_tail_stream=None, c_copies_tail_fraction=0.0, static_b=False):
+          c_copies=None, work_stealing=False, c_copies_tail_stream=None, c_copies_tail_fraction=0.0, static_b=False,
+          c_copies_tile_limit=0):
     assert a.shape[1] == b.shape[0], "Incompatible Dimensions"
     if not (a.is_cuda and b.is_cuda and c.is_cuda):
         raise RuntimeError("tritonblas_b200 runs on CUDA tensors only (no CPU path)")
@@ -167,6 +168,8 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
         # raw device addresses of further destinations laid out exactly like c (peer GPUs' buffers)
         ptrs = (ctypes.c_void_p * len(c_copies))(*[int(p) for p in c_copies])
         args.c_copies, args.num_c_copies = ptrs, len(c_copies)
+    if c_copies and c_copies_tile_limit > 0:
+        args.c_copies_tile_limit = int(c_copies_tile_limit)     # the caller sends the other tiles itself
     tail_first = None
     if c_copies and c_copies_tail_stream is not None and c_copies_tail_fraction > 0 and not streamk and not cfg.swap_ab \
             and c.stride(1) == 1 and (c.stride(0) * c.element_size()) % 16 == 0 and (N * c.element_size()) % 16 == 0 \
@@ -216,17 +219,18 @@ def _gemm(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None,
 
 def persistent_matmul_lt(a, b, c, selector, config=None, bias=None, a_scale=None, b_scale=None, quantized=False,
                          work_stealing=False, c_copies=None, c_copies_tail_stream=None, c_copies_tail_fraction=0.0,
-                         static_b=False):
+                         static_b=False, c_copies_tile_limit=0):
     """Data-parallel persistent GEMM (reference: matmul.py:69-200). ``work_stealing`` selects the dynamic tile schedule
     (tiles taken from a device counter, matmul.py:112-159) instead of the static round-robin. ``c_copies``: device addresses of further buffers laid out like ``c`` (peer GPUs) that the
     epilogue also writes. With ``c_copies_tail_stream`` (a torch.cuda.Stream) and ``c_copies_tail_fraction`` in (0, 1] the
     epilogue sends only the first tiles and the last ``fraction`` of the tiles are copied to the peers by a kernel on that
     stream after the launch, where they overlap whatever is enqueued next on the current stream; the caller waits for that
-    stream before the copies are read. ``static_b``: a promise that nothing still in flight on the stream writes ``b``
+    stream before the copies are read. ``c_copies_tile_limit`` > 0 alone: the epilogue sends only tiles with a launch-order
+    index below it and the caller moves the rest of ``c`` itself. ``static_b``: a promise that nothing still in flight on the stream writes ``b``
     (weights); the kernel may then start reading it while the previous kernel of the stream is still draining."""
     return _gemm(a, b, c, selector, config, bias, a_scale, b_scale, streamk=False, c_copies=c_copies,
                  work_stealing=work_stealing, c_copies_tail_stream=c_copies_tail_stream,
-                 c_copies_tail_fraction=c_copies_tail_fraction, static_b=static_b)
+                 c_copies_tail_fraction=c_copies_tail_fraction, static_b=static_b, c_copies_tile_limit=c_copies_tile_limit)
 
 
 def streamk_matmul_lt(a, b, c, selector, config=None, bias=None, sk_grid=None, a_scale=None, b_scale=None,
