@@ -186,3 +186,41 @@ def test_bench_matmul_csv_schema(tmp_path):
     cases = yaml.safe_load(open(bm.__file__.replace("bench_matmul.py", "shapes/baseline.yaml")))
     assert all({"m", "n", "k", "in_dtype", "out_dtype", "transA", "transB"} <= set(c) for c in cases)
     assert all(bm.str_to_dtype(c["in_dtype"]) is not None for c in cases)
+
+
+def _tile_rows(tile, tiles_m, tiles_n, group_m, block_m):
+    """First row of a tile in the kernel's launch order (groups of group_m tile rows, each swept column by column:
+    the reference's GROUP_SIZE_M order, kernels/stages/schedule.py:124-145)."""
+    width = group_m * tiles_n
+    group = tile // width
+    first_m = group * group_m
+    gsz = min(tiles_m - first_m, group_m)
+    return (first_m + (tile - group * width) % gsz) * block_m
+
+
+def test_tail_split_of_the_gathered_product_follows_the_tile_order():
+    """Splitting a product between epilogue pushes (tiles below `first_tile`) and row copies (rows from `first_row` on):
+    every tile below the limit lies wholly above the first copied row and every other tile wholly below it."""
+    import tritonblas_b200 as tb
+    for (m, n, k, group_m, frac) in [(8192, 2048, 8192, 0, 0.5), (8192, 1024, 8192, 0, 0.3), (4096, 512, 256, 4, 0.8),
+                                     (4096, 512, 256, 4, 0.3), (2304, 768, 512, 2, 0.5), (512, 512, 256, 0, 0.5)]:
+        layer = tbd.ColumnShardedGemm(torch.zeros(n, k, dtype=torch.bfloat16), matmul_fn=lambda *a: None)
+        sel = tb.OrigamiMatmulSelector(m, n, k, torch.bfloat16, torch.bfloat16, torch.bfloat16, torch.device("cpu"), max_halves=1)
+        if group_m:
+            sel.override(group_m=group_m)
+        layer._fused_selector = sel
+        a = torch.zeros(m, k, dtype=torch.bfloat16)
+        first_tile, first_row = layer._tail_split(a, layer.b_shard_t, frac)
+        cfg = sel.config_for(False, False)
+        tiles_m, tiles_n = -(-m // cfg.block_m), -(-n // (cfg.block_n * max(cfg.n_halves, 1)))
+        gm = cfg.group_m if cfg.group_m > 0 else 8
+        total = tiles_m * tiles_n
+        assert 0 < first_tile <= total and 0 < first_row <= m
+        for t in range(total):
+            r0 = _tile_rows(t, tiles_m, tiles_n, gm, cfg.block_m)
+            if t < first_tile:
+                assert r0 + cfg.block_m <= first_row or first_row == m, (m, n, t, r0, first_row)
+            else:
+                assert r0 >= first_row, (m, n, t, r0, first_row)
+        if -(-tiles_m // gm) >= 2:
+            assert first_tile < total and first_row < m        # something is left for the copies
