@@ -91,3 +91,16 @@ def test_ctypes_structures_mirror_the_header_field_for_field(tmp_path):
         assert int(out[cname]) == ctypes.sizeof(mirror), cname
         for fname, _ in mirror._fields_:
             assert int(out[f"{cname}.{fname}"]) == getattr(mirror, fname).offset, (cname, fname)
+
+
+def test_integration_stub_lists_the_same_fields_as_the_header():
+    """The reference-side ctypes stub shown in INTEGRATION.md names every field of tb_gemm_args and tb_config, in order."""
+    from tritonblas_b200 import _lib
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    args_block = text[text.index("class _Args(ctypes.Structure)"):]
+    args_block = args_block[:args_block.index("_DT = ")]
+    names = re.findall(r'\("(\w+)",\s*ctypes\.', args_block)
+    assert names == [f[0] for f in _lib.GemmArgs._fields_], names
+    cfg_block = text[text.index("class _Cfg(ctypes.Structure)"):text.index("class _Args(ctypes.Structure)")]
+    cfg_names = re.findall(r'"(\w+)"', cfg_block)
+    assert cfg_names == [f[0] for f in _lib.Config._fields_], cfg_names
