@@ -94,7 +94,8 @@ def test_ctypes_structures_mirror_the_header_field_for_field(tmp_path):
 
 
 def test_integration_stub_lists_the_same_fields_as_the_header():
-    """The reference-side ctypes stub shown in INTEGRATION.md names every field of tb_gemm_args and tb_config, in order."""
+    """The reference-side ctypes stub shown in the integration guide names every field of tb_gemm_args and tb_config, in
+    order."""
     from tritonblas_b200 import _lib
     text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
     args_block = text[text.index("class _Args(ctypes.Structure)"):]
